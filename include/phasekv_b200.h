@@ -1,0 +1,142 @@
+/*
+ * phasekv_b200 — C ABI of the B200 (sm_100a) implementation of PhaseKV's stage-B hot path:
+ * sub-byte quantise+pack, the three-tier split-K decode attention and its log-sum-exp merge.
+ *
+ * The reference has no FFI of its own: its boundary is a set of Python callables
+ * (src/phasekv/kernels/packing.py, attention_triton.py, launch_config.py).  Each entry
+ * point below names the reference function it stands behind.  Conventions:
+ *   - every pointer is a DEVICE pointer unless its comment says "host";
+ *   - float16 data is passed as `const void*` / `void*` (IEEE binary16, little endian);
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*), nothing synchronises;
+ *   - nothing is allocated and no pointer is retained after the call returns;
+ *   - the return value is 0 on success or a negative PKV_E_* code; pkv_strerror() names it.
+ */
+#ifndef PHASEKV_B200_H
+#define PHASEKV_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PKV_OK 0
+#define PKV_E_BITS (-1)      /* bit width not in {2, 4, 8} */
+#define PKV_E_SHAPE (-2)     /* negative / zero / inconsistent sizes */
+#define PKV_E_NULL (-3)      /* required pointer is NULL */
+#define PKV_E_LAYOUT (-4)    /* segment kind / group size not supported by the kernels */
+#define PKV_E_WORKSPACE (-5) /* scratch buffer too small */
+#define PKV_E_CUDA (-6)      /* a CUDA runtime call failed; see pkv_last_cuda_error() */
+#define PKV_E_LIMIT (-7)     /* a documented maximum was exceeded */
+
+typedef void* pkv_stream_t; /* cudaStream_t */
+
+int pkv_abi_version(void);
+const char* pkv_strerror(int code);
+/* cudaError_t value of the last failing CUDA call made by this library on the calling thread. */
+int pkv_last_cuda_error(void);
+/* attention_triton.py:599-601 (_device_sm_count) */
+int pkv_device_sm_count(int device, int* sm_count /* host */);
+
+/* ---------------------------------------------------------------- packing ---------- */
+
+/* packing.py:41-65 pack_low_bits: codes u8 [rows, len] -> out u8 [rows, ceil(len / (8/bits))];
+ * code i of a byte sits at bits [i*bits, (i+1)*bits); unused tail bits are zero. */
+int pkv_pack_low_bits(const uint8_t* codes, int64_t rows, int64_t len, int bits, uint8_t* out,
+                      pkv_stream_t stream);
+
+/* packing.py:67-79 unpack_low_bits: packed u8 [rows, row_bytes] -> out u8 [rows, len],
+ * len <= row_bytes * (8/bits). */
+int pkv_unpack_low_bits(const uint8_t* packed, int64_t rows, int64_t row_bytes, int64_t len,
+                        int bits, uint8_t* out, pkv_stream_t stream);
+
+/* packing.py:115-155 quantize_pack.  x is float16 viewed as [outer, axis_len, inner]; groups of
+ * `group` (1 <= group <= axis_len, already clamped as packing.py:130 does) run along axis_len.
+ * Outputs carry the axis last:  packed u8 [outer, inner, ceil(axis_len / (8/bits))],
+ * scale and mins float16 [outer, inner, ceil(axis_len / group)].
+ * K of a KV cache is (outer = B*Hkv, axis_len = S, inner = hd); V is (outer = B*Hkv*S,
+ * axis_len = hd, inner = 1). Codes, scales and zeros are bit-identical to the reference on CPU. */
+int pkv_quantize_pack(const void* x, int64_t outer, int64_t axis_len, int64_t inner, int bits,
+                      int64_t group, uint8_t* packed, void* scale, void* mins, pkv_stream_t stream);
+
+/* packing.py:158-175 unpack_dequantize: inverse of the above, out float16 [outer, axis_len, inner],
+ * computed as float32 code*scale then +mins (two roundings) then rounded to float16. */
+int pkv_unpack_dequantize(const uint8_t* packed, const void* scale, const void* mins, int64_t outer,
+                          int64_t axis_len, int64_t inner, int bits, int64_t group, void* out,
+                          pkv_stream_t stream);
+
+/* ---------------------------------------------------------------- decode ----------- */
+
+/* One stretch of cached tokens of one layer, all KV heads.  Three layouts: */
+#define PKV_SEG_KIVI 0     /* K packed along tokens:  k_packed u8 [Hkv, hd, ceil(S/kvpb)], k_scale/k_mins f16 [Hkv, hd, ceil(S/k_group)]
+                              V packed along dims:    v_packed u8 [Hkv, S, ceil(hd/vvpb)], v_scale/v_mins f16 [Hkv, S, ceil(hd/v_group)]
+                              (LayerTiers.prompt / prompt_extensions / cold, phasekv_cache.py:101-107) */
+#define PKV_SEG_PER_TOKEN 1 /* K and V both packed along dims (quantize_pack(x, bits, -1, gs) of [Hkv, S, hd]):
+                              *_packed u8 [Hkv, S, ceil(hd/vpb)], *_scale/_mins f16 [Hkv, S, ceil(hd/group)]
+                              (attention_triton.py:95-142, the published micro-benchmark layout) */
+#define PKV_SEG_FP16 2     /* k_packed / v_packed point at float16 [Hkv, >=S, hd] with `head_stride` elements
+                              between heads (LayerTiers.hot_views(), phasekv_cache.py:75-79) */
+
+typedef struct pkv_segment {
+    const void* k_packed;
+    const void* k_scale;
+    const void* k_mins;
+    const void* v_packed;
+    const void* v_scale;
+    const void* v_mins;
+    int64_t seq_len;     /* S: tokens in this segment (> 0) */
+    int64_t head_stride; /* PKV_SEG_FP16 only: elements between consecutive KV heads */
+    int32_t kind;        /* PKV_SEG_* */
+    int32_t k_bits, v_bits;   /* 2, 4 or 8 (ignored for PKV_SEG_FP16) */
+    int32_t k_group, v_group; /* quantisation group sizes (after clamping to the axis length) */
+    int32_t num_splits;       /* 0 = let the library choose; else as plan_kivi_decode(num_splits=...) */
+} pkv_segment_t;
+
+#define PKV_MAX_SEGMENTS 4096
+
+/* Scratch bytes pkv_decode_attention needs for these segments (host array). */
+int pkv_decode_workspace_bytes(const pkv_segment_t* segs /* host */, int n_segs, int num_q_heads,
+                               int num_kv_heads, int head_dim, int sm_count, size_t* bytes /* host */);
+
+/* attention_triton.py:643-669 fused_phasekv_decode (and :604-639 _kivi_layer_partial, :285-297
+ * _fp16_layer_partial, :487-511 fused_three_tier_decode, :95-142 / :269-276 decode_attention_packed[_splitk]):
+ * single-query attention of q float16 [Hq, hd] over the concatenation of `segs`, without ever
+ * writing dequantised K/V to memory.  One split-K launch covers all segments, one merge launch
+ * follows.  Outputs (each may be NULL):
+ *   out  float16 [Hq, hd]  = acc / l
+ *   m, l float32 [Hq], acc float32 [Hq, hd]: the un-normalised partial of attention_triton.py:257-266,
+ *   mergeable across segments, layers of a tier, or GPUs with pkv_merge_partials.
+ * `workspace` is device scratch of at least pkv_decode_workspace_bytes(); calls that share it must not overlap. */
+int pkv_decode_attention(const void* q, const pkv_segment_t* segs /* host */, int n_segs,
+                         int num_q_heads, int num_kv_heads, int head_dim, float sm_scale,
+                         int sm_count, void* workspace, size_t workspace_bytes, void* out, float* m,
+                         float* l, float* acc, pkv_stream_t stream);
+
+/* attention_triton.py:257-266 _reduce_splits and :300-307 _merge_partials:
+ * m, l float32 [n_parts, Hq] and acc float32 [n_parts, Hq, hd] (contiguous) are combined with
+ * M = max m, w = exp(m - M), L = sum w*l, A = sum w*acc.  out float16 [Hq, hd] = A / L;
+ * m_out/l_out/acc_out (optional) receive (M, L, A). */
+int pkv_merge_partials(const float* m, const float* l, const float* acc, int n_parts, int num_q_heads,
+                       int head_dim, void* out, float* m_out, float* l_out, float* acc_out,
+                       pkv_stream_t stream);
+
+/* ---------------------------------------------------------------- cold tier -------- */
+
+/* phasekv_cache.py:322-340 _cool_aged_tokens for one layer: among the oldest `aged` tokens of the
+ * hot buffers hot_k/hot_v float16 [rows, capacity, hd] (rows = B*Hkv), keep the `keep` tokens with the
+ * largest value L2 norm per row (ascending position order; all of them when keep == aged), quantise and
+ * pack them (K along tokens, V along dims, `bits`, `group`), and move the remaining hot_len - aged tokens
+ * to the start of the hot buffers.
+ *   k_packed u8 [rows, hd, ceil(keep/vpb)], k_scale/k_mins f16 [rows, hd, ceil(keep/min(group,keep))]
+ *   v_packed u8 [rows, keep, ceil(hd/vpb)], v_scale/v_mins f16 [rows, keep, ceil(hd/min(group,hd))]
+ *   indices int64 [rows, keep] (optional): the kept positions. */
+int pkv_cold_select_pack(void* hot_k, void* hot_v, int64_t rows, int64_t capacity, int head_dim,
+                         int64_t hot_len, int64_t aged, int64_t keep, int bits, int64_t group,
+                         uint8_t* k_packed, void* k_scale, void* k_mins, uint8_t* v_packed,
+                         void* v_scale, void* v_mins, int64_t* indices, pkv_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PHASEKV_B200_H */

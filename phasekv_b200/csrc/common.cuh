@@ -1,0 +1,43 @@
+// Shared helpers for the phasekv_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/phasekv_b200.h"
+
+namespace pkv {
+
+extern thread_local int g_last_cuda_error;
+
+inline int cuda_fail(cudaError_t e) {
+    g_last_cuda_error = static_cast<int>(e);
+    return PKV_E_CUDA;
+}
+
+#define PKV_CUDA_TRY(expr)                                   \
+    do {                                                     \
+        cudaError_t _e = (expr);                             \
+        if (_e != cudaSuccess) return ::pkv::cuda_fail(_e);  \
+    } while (0)
+
+#define PKV_LAUNCH_CHECK() PKV_CUDA_TRY(cudaGetLastError())
+
+inline bool valid_bits(int bits) { return bits == 2 || bits == 4 || bits == 8; }
+
+__host__ __device__ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+__device__ __forceinline__ float h2f(const __half h) { return __half2float(h); }
+
+// code i of a byte occupies bits [i*bits, (i+1)*bits)
+template <int BITS>
+__device__ __forceinline__ unsigned extract_code(unsigned byte, unsigned idx_in_byte) {
+    return (byte >> (idx_in_byte * BITS)) & ((1u << BITS) - 1u);
+}
+
+__device__ __forceinline__ unsigned extract_code_rt(unsigned byte, unsigned idx_in_byte, int bits) {
+    return (byte >> (idx_in_byte * bits)) & ((1u << bits) - 1u);
+}
+
+}  // namespace pkv

@@ -1,0 +1,404 @@
+// Three-tier split-K decode attention: host planning, the layout-generic kernel, the merge.
+//
+// One launch covers every segment of a layer (prompt, prompt extensions, every frozen cold
+// segment, the float16 hot buffer): a CTA owns (work item, KV head), where a work item is a
+// token range of one segment.  All query heads of the GQA group are served from one read of
+// the KV bytes; dequantisation happens in registers and nothing dense is written back.
+// Each CTA emits an un-normalised flash partial (m, l, acc) and the merge kernel combines them
+// (attention_triton.py:257-266 and :300-307 of the reference define the same algebra).
+#include <math.h>
+
+#include "common.cuh"
+#include "decode_plan.h"
+
+namespace pkv {
+namespace {
+
+constexpr int GMAX = 8;        // query heads served per CTA pass
+constexpr int kThreads = 128;  // threads per CTA of the generic kernel
+constexpr int kChunk = 128;    // tokens per inner step (= kThreads)
+constexpr int kMaxDimsPerThread = 2;  // head_dim <= 256
+
+struct DecodeArgs {
+    const __half* q;
+    float* pm;
+    float* pl;
+    float* pacc;
+    int Hq, Hkv, hd, G;
+    float sm_scale;
+    int n_segs;
+    int work_offset;  // global index of this launch's first work item
+    SegDev segs[kMaxInlineSegs];
+};
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__global__ void __launch_bounds__(kThreads)
+decode_generic_kernel(const __grid_constant__ DecodeArgs a) {
+    extern __shared__ float smem[];
+    const int hd = a.hd;
+    float* q_s = smem;                    // [GMAX][hd], pre-multiplied by sm_scale
+    float* p_s = q_s + GMAX * hd;         // [GMAX][kChunk]
+    float* alpha_s = p_s + GMAX * kChunk; // [GMAX]
+    float* m_s = alpha_s + GMAX;
+    float* l_s = m_s + GMAX;
+
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int w = blockIdx.x, kvh = blockIdx.y, hc = blockIdx.z;
+
+    int si = 0;
+    while (si + 1 < a.n_segs && w >= a.segs[si + 1].work_begin) ++si;
+    const SegDev& sg = a.segs[si];
+    const long long t0 = (long long)(w - sg.work_begin) * sg.split_len;
+    const long long t1 = min(sg.S, t0 + sg.split_len);
+
+    const int h0 = kvh * a.G + hc * GMAX;
+    const int nh = min(GMAX, a.G - hc * GMAX);
+    for (int i = tid; i < GMAX * hd; i += kThreads) {
+        const int h = i / hd, d = i % hd;
+        q_s[i] = h < nh ? __half2float(a.q[(size_t)(h0 + h) * hd + d]) * a.sm_scale : 0.f;
+    }
+    if (tid < GMAX) {
+        m_s[tid] = -INFINITY;
+        l_s[tid] = 0.f;
+    }
+    float acc[GMAX][kMaxDimsPerThread];
+#pragma unroll
+    for (int h = 0; h < GMAX; ++h)
+#pragma unroll
+        for (int k = 0; k < kMaxDimsPerThread; ++k) acc[h][k] = 0.f;
+    __syncthreads();
+
+    const int kvpb = 8 / sg.kbits, vvpb = 8 / sg.vbits;
+    const long long S = sg.S;
+
+    for (long long c0 = t0; c0 < t1; c0 += kChunk) {
+        // ---- phase 1: one token per thread, scores for all heads of the group
+        const long long n = c0 + tid;
+        float dot[GMAX];
+#pragma unroll
+        for (int h = 0; h < GMAX; ++h) dot[h] = 0.f;
+        if (n < t1) {
+            if (sg.kind == PKV_SEG_KIVI) {
+                const long long nbK = ceil_div(S, kvpb), ngK = ceil_div(S, sg.kgs);
+                const uint8_t* kp = sg.kp + (size_t)kvh * hd * nbK + n / kvpb;
+                const __half* ks = sg.ks + (size_t)kvh * hd * ngK + n / sg.kgs;
+                const __half* km = sg.km + (size_t)kvh * hd * ngK + n / sg.kgs;
+                const unsigned pos = (unsigned)(n % kvpb);
+                for (int d = 0; d < hd; ++d) {
+                    const float c = (float)extract_code_rt(kp[(size_t)d * nbK], pos, sg.kbits);
+                    const float kv = fmaf(c, __half2float(ks[(size_t)d * ngK]), __half2float(km[(size_t)d * ngK]));
+#pragma unroll
+                    for (int h = 0; h < GMAX; ++h) dot[h] = fmaf(q_s[h * hd + d], kv, dot[h]);
+                }
+            } else if (sg.kind == PKV_SEG_PER_TOKEN) {
+                const long long nbK = ceil_div(hd, kvpb), ngK = ceil_div(hd, sg.kgs);
+                const uint8_t* kp = sg.kp + ((size_t)kvh * S + n) * nbK;
+                const __half* ks = sg.ks + ((size_t)kvh * S + n) * ngK;
+                const __half* km = sg.km + ((size_t)kvh * S + n) * ngK;
+                for (int d = 0; d < hd; ++d) {
+                    const float c = (float)extract_code_rt(kp[d / kvpb], (unsigned)(d % kvpb), sg.kbits);
+                    const float kv = fmaf(c, __half2float(ks[d / sg.kgs]), __half2float(km[d / sg.kgs]));
+#pragma unroll
+                    for (int h = 0; h < GMAX; ++h) dot[h] = fmaf(q_s[h * hd + d], kv, dot[h]);
+                }
+            } else {
+                const __half* kr = reinterpret_cast<const __half*>(sg.kp) + (size_t)kvh * sg.head_stride + (size_t)n * hd;
+                for (int d = 0; d < hd; ++d) {
+                    const float kv = __half2float(kr[d]);
+#pragma unroll
+                    for (int h = 0; h < GMAX; ++h) dot[h] = fmaf(q_s[h * hd + d], kv, dot[h]);
+                }
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < GMAX; ++h) p_s[h * kChunk + tid] = n < t1 ? dot[h] : -INFINITY;
+        __syncthreads();
+
+        // ---- phase 2: online softmax bookkeeping, one warp per head
+        for (int h = wid; h < nh; h += kThreads / 32) {
+            float v[kChunk / 32];
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < kChunk / 32; ++i) {
+                v[i] = p_s[h * kChunk + lane + 32 * i];
+                mx = fmaxf(mx, v[i]);
+            }
+            mx = warp_max(mx);
+            const float m_old = m_s[h];
+            const float m_new = fmaxf(m_old, mx);
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < kChunk / 32; ++i) {
+                const float p = expf(v[i] - m_new);  // -inf -> 0
+                p_s[h * kChunk + lane + 32 * i] = p;
+                sum += p;
+            }
+            sum = warp_sum(sum);
+            if (lane == 0) {
+                const float alpha = expf(m_old - m_new);  // first chunk: exp(-inf) = 0
+                alpha_s[h] = alpha;
+                m_s[h] = m_new;
+                l_s[h] = l_s[h] * alpha + sum;
+            }
+        }
+        __syncthreads();
+
+        // ---- phase 3: one head_dim column per thread, acc += p * v
+        const int nvalid = (int)min((long long)kChunk, t1 - c0);
+#pragma unroll
+        for (int k = 0; k < kMaxDimsPerThread; ++k) {
+            const int d = tid + k * kThreads;
+            if (d < hd) {
+#pragma unroll
+                for (int h = 0; h < GMAX; ++h) acc[h][k] *= alpha_s[h];
+                if (sg.kind == PKV_SEG_FP16) {
+                    const __half* vr = reinterpret_cast<const __half*>(sg.vp) + (size_t)kvh * sg.head_stride + (size_t)c0 * hd + d;
+                    for (int i = 0; i < nvalid; ++i) {
+                        const float vv = __half2float(vr[(size_t)i * hd]);
+#pragma unroll
+                        for (int h = 0; h < GMAX; ++h) acc[h][k] = fmaf(p_s[h * kChunk + i], vv, acc[h][k]);
+                    }
+                } else {
+                    const long long nbV = ceil_div(hd, vvpb), ngV = ceil_div(hd, sg.vgs);
+                    const uint8_t* vp = sg.vp + ((size_t)kvh * S + c0) * nbV + d / vvpb;
+                    const __half* vs = sg.vs + ((size_t)kvh * S + c0) * ngV + d / sg.vgs;
+                    const __half* vm = sg.vm + ((size_t)kvh * S + c0) * ngV + d / sg.vgs;
+                    const unsigned pos = (unsigned)(d % vvpb);
+                    for (int i = 0; i < nvalid; ++i) {
+                        const float c = (float)extract_code_rt(vp[(size_t)i * nbV], pos, sg.vbits);
+                        const float vv = fmaf(c, __half2float(vs[(size_t)i * ngV]), __half2float(vm[(size_t)i * ngV]));
+#pragma unroll
+                        for (int h = 0; h < GMAX; ++h) acc[h][k] = fmaf(p_s[h * kChunk + i], vv, acc[h][k]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    const size_t widx = (size_t)(a.work_offset + w);
+    if (tid < nh) {
+        a.pm[widx * a.Hq + h0 + tid] = m_s[tid];
+        a.pl[widx * a.Hq + h0 + tid] = l_s[tid];
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxDimsPerThread; ++k) {
+        const int d = tid + k * kThreads;
+        if (d < hd) {
+#pragma unroll
+            for (int h = 0; h < GMAX; ++h)
+                if (h < nh) a.pacc[(widx * a.Hq + h0 + h) * hd + d] = acc[h][k];
+        }
+    }
+}
+
+// Log-sum-exp merge of n_parts partials for one query head per CTA.
+__global__ void __launch_bounds__(128)
+merge_partials_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
+                      const float* __restrict__ pacc, int n_parts, int Hq, int hd,
+                      __half* __restrict__ out, float* __restrict__ m_out,
+                      float* __restrict__ l_out, float* __restrict__ acc_out) {
+    __shared__ float red[4];
+    __shared__ float w_s[256];
+    const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+
+    float mx = -INFINITY;
+    for (int p = tid; p < n_parts; p += 128) mx = fmaxf(mx, pm[(size_t)p * Hq + h]);
+    mx = warp_max(mx);
+    if (lane == 0) red[wid] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    __syncthreads();
+
+    float ls = 0.f;
+    float a0 = 0.f, a1 = 0.f;  // head_dim <= 256: two columns per thread
+    for (int base = 0; base < n_parts; base += 256) {
+        const int cnt = min(256, n_parts - base);
+        for (int p = tid; p < cnt; p += 128) {
+            const float wgt = expf(pm[(size_t)(base + p) * Hq + h] - mx);
+            w_s[p] = wgt;
+            ls += wgt * pl[(size_t)(base + p) * Hq + h];
+        }
+        __syncthreads();
+        for (int p = 0; p < cnt; ++p) {
+            const float* row = pacc + ((size_t)(base + p) * Hq + h) * hd;
+            const float wgt = w_s[p];
+            if (tid < hd) a0 = fmaf(wgt, row[tid], a0);
+            if (tid + 128 < hd) a1 = fmaf(wgt, row[tid + 128], a1);
+        }
+        __syncthreads();
+    }
+    ls = warp_sum(ls);
+    if (lane == 0) red[wid] = ls;
+    __syncthreads();
+    ls = red[0] + red[1] + red[2] + red[3];
+
+    if (tid == 0) {
+        if (m_out) m_out[h] = mx;
+        if (l_out) l_out[h] = ls;
+    }
+    if (tid < hd) {
+        if (out) out[(size_t)h * hd + tid] = __float2half_rn(a0 / ls);
+        if (acc_out) acc_out[(size_t)h * hd + tid] = a0;
+    }
+    if (tid + 128 < hd) {
+        if (out) out[(size_t)h * hd + tid + 128] = __float2half_rn(a1 / ls);
+        if (acc_out) acc_out[(size_t)h * hd + tid + 128] = a1;
+    }
+}
+
+int check_segments(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int hd) {
+    if (!segs) return PKV_E_NULL;
+    if (n_segs <= 0 || n_segs > PKV_MAX_SEGMENTS) return PKV_E_LIMIT;
+    if (Hq <= 0 || Hkv <= 0 || hd <= 0 || Hq % Hkv) return PKV_E_SHAPE;
+    if (hd > kThreads * kMaxDimsPerThread) return PKV_E_LIMIT;
+    for (int i = 0; i < n_segs; ++i) {
+        const pkv_segment_t& s = segs[i];
+        if (s.seq_len <= 0) return PKV_E_SHAPE;
+        if (!s.k_packed || !s.v_packed) return PKV_E_NULL;
+        if (s.kind == PKV_SEG_FP16) {
+            if (s.head_stride < s.seq_len * hd) return PKV_E_SHAPE;
+            continue;
+        }
+        if (s.kind != PKV_SEG_KIVI && s.kind != PKV_SEG_PER_TOKEN) return PKV_E_LAYOUT;
+        if (!valid_bits(s.k_bits) || !valid_bits(s.v_bits)) return PKV_E_BITS;
+        if (s.k_group <= 0 || s.v_group <= 0) return PKV_E_LAYOUT;
+        if (!s.k_scale || !s.k_mins || !s.v_scale || !s.v_mins) return PKV_E_NULL;
+    }
+    return PKV_OK;
+}
+
+}  // namespace
+
+DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int hd, int sm_count) {
+    DecodePlan plan;
+    plan.segs.resize(n_segs);
+    const int G = Hq / Hkv;
+    const int head_chunks = (G + GMAX - 1) / GMAX;
+    long long total_tokens = 0;
+    for (int i = 0; i < n_segs; ++i) total_tokens += segs[i].seq_len;
+    // about four CTAs per SM over the whole layer
+    const long long target = std::max<long long>(1, (4LL * std::max(sm_count, 1)) / ((long long)Hkv * head_chunks));
+    int work = 0;
+    for (int i = 0; i < n_segs; ++i) {
+        const pkv_segment_t& s = segs[i];
+        SegDev& d = plan.segs[i];
+        d.kp = static_cast<const uint8_t*>(s.k_packed);
+        d.ks = static_cast<const __half*>(s.k_scale);
+        d.km = static_cast<const __half*>(s.k_mins);
+        d.vp = static_cast<const uint8_t*>(s.v_packed);
+        d.vs = static_cast<const __half*>(s.v_scale);
+        d.vm = static_cast<const __half*>(s.v_mins);
+        d.S = s.seq_len;
+        d.head_stride = s.head_stride;
+        d.kind = s.kind;
+        d.kbits = s.kind == PKV_SEG_FP16 ? 8 : s.k_bits;
+        d.vbits = s.kind == PKV_SEG_FP16 ? 8 : s.v_bits;
+        d.kgs = s.kind == PKV_SEG_FP16 ? 1 : s.k_group;
+        d.vgs = s.kind == PKV_SEG_FP16 ? 1 : s.v_group;
+        long long split_len;
+        if (s.num_splits > 0) {
+            // plan_kivi_decode's manual convention (launch_config.py:58-60)
+            split_len = ceil_div(s.seq_len, std::min<long long>(s.seq_len, s.num_splits));
+        } else {
+            long long share = (target * s.seq_len + total_tokens / 2) / total_tokens;
+            share = std::max<long long>(1, share);
+            split_len = ceil_div(ceil_div(s.seq_len, share), kChunk) * kChunk;
+        }
+        d.split_len = split_len;
+        d.n_splits = (int)ceil_div(s.seq_len, split_len);
+        d.work_begin = work;
+        work += d.n_splits;
+    }
+    plan.total_work = work;
+    (void)hd;
+    return plan;
+}
+
+}  // namespace pkv
+
+using namespace pkv;
+
+extern "C" {
+
+int pkv_decode_workspace_bytes(const pkv_segment_t* segs, int n_segs, int num_q_heads, int num_kv_heads,
+                               int head_dim, int sm_count, size_t* bytes) {
+    if (!bytes) return PKV_E_NULL;
+    const int rc = check_segments(segs, n_segs, num_q_heads, num_kv_heads, head_dim);
+    if (rc != PKV_OK) return rc;
+    const DecodePlan plan = plan_decode(segs, n_segs, num_q_heads, num_kv_heads, head_dim, sm_count);
+    *bytes = (size_t)plan.total_work * num_q_heads * (head_dim + 2) * sizeof(float);
+    return PKV_OK;
+}
+
+int pkv_decode_attention(const void* q, const pkv_segment_t* segs, int n_segs, int num_q_heads,
+                         int num_kv_heads, int head_dim, float sm_scale, int sm_count, void* workspace,
+                         size_t workspace_bytes, void* out, float* m, float* l, float* acc,
+                         pkv_stream_t stream) {
+    const int rc = check_segments(segs, n_segs, num_q_heads, num_kv_heads, head_dim);
+    if (rc != PKV_OK) return rc;
+    if (!q || !workspace) return PKV_E_NULL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const DecodePlan plan = plan_decode(segs, n_segs, num_q_heads, num_kv_heads, head_dim, sm_count);
+    const size_t W = (size_t)plan.total_work;
+    const size_t need = W * num_q_heads * (head_dim + 2) * sizeof(float);
+    if (workspace_bytes < need) return PKV_E_WORKSPACE;
+    float* pm = static_cast<float*>(workspace);
+    float* pl = pm + W * num_q_heads;
+    float* pacc = pl + W * num_q_heads;
+
+    const int G = num_q_heads / num_kv_heads;
+    const size_t smem = sizeof(float) * ((size_t)GMAX * head_dim + (size_t)GMAX * kChunk + 3 * GMAX);
+    for (int first = 0; first < n_segs; first += kMaxInlineSegs) {
+        const int cnt = std::min(kMaxInlineSegs, n_segs - first);
+        DecodeArgs a;
+        a.q = static_cast<const __half*>(q);
+        a.pm = pm;
+        a.pl = pl;
+        a.pacc = pacc;
+        a.Hq = num_q_heads;
+        a.Hkv = num_kv_heads;
+        a.hd = head_dim;
+        a.G = G;
+        a.sm_scale = sm_scale;
+        a.n_segs = cnt;
+        a.work_offset = plan.segs[first].work_begin;
+        int launch_work = 0;
+        for (int i = 0; i < cnt; ++i) {
+            a.segs[i] = plan.segs[first + i];
+            a.segs[i].work_begin -= a.work_offset;
+            launch_work += a.segs[i].n_splits;
+        }
+        dim3 grid((unsigned)launch_work, (unsigned)num_kv_heads, (unsigned)((G + GMAX - 1) / GMAX));
+        decode_generic_kernel<<<grid, kThreads, smem, s>>>(a);
+        PKV_LAUNCH_CHECK();
+    }
+    merge_partials_kernel<<<num_q_heads, 128, 0, s>>>(pm, pl, pacc, (int)W, num_q_heads, head_dim,
+                                                      static_cast<__half*>(out), m, l, acc);
+    PKV_LAUNCH_CHECK();
+    return PKV_OK;
+}
+
+int pkv_merge_partials(const float* m, const float* l, const float* acc, int n_parts, int num_q_heads,
+                       int head_dim, void* out, float* m_out, float* l_out, float* acc_out,
+                       pkv_stream_t stream) {
+    if (!m || !l || !acc) return PKV_E_NULL;
+    if (n_parts <= 0 || num_q_heads <= 0 || head_dim <= 0) return PKV_E_SHAPE;
+    if (head_dim > 256) return PKV_E_LIMIT;
+    merge_partials_kernel<<<num_q_heads, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        m, l, acc, n_parts, num_q_heads, head_dim, static_cast<__half*>(out), m_out, l_out, acc_out);
+    PKV_LAUNCH_CHECK();
+    return PKV_OK;
+}
+
+}  // extern "C"

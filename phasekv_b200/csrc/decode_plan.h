@@ -1,0 +1,37 @@
+// Host-side work decomposition shared by the decode kernels.
+#pragma once
+
+#include <algorithm>
+#include <vector>
+
+#include "common.cuh"
+
+namespace pkv {
+
+// Segments whose descriptors travel inside the kernel parameter block of one launch.
+constexpr int kMaxInlineSegs = 24;
+
+// Device-visible image of a pkv_segment_t plus its share of the split-K work list.
+struct SegDev {
+    const uint8_t* kp;
+    const __half* ks;
+    const __half* km;
+    const uint8_t* vp;
+    const __half* vs;
+    const __half* vm;
+    long long S;
+    long long head_stride;
+    long long split_len;  // tokens per work item
+    int kind, kbits, vbits, kgs, vgs;
+    int work_begin;  // index of the segment's first work item
+    int n_splits;    // work items of this segment
+};
+
+struct DecodePlan {
+    std::vector<SegDev> segs;
+    int total_work = 0;
+};
+
+DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int hd, int sm_count);
+
+}  // namespace pkv

@@ -1,0 +1,315 @@
+// Sub-byte packing and grouped asymmetric min-max quantisation.
+//
+// Arithmetic contract (what makes codes, scales and zeros bit-identical to the reference's
+// packing.py:115-155 executed on a CPU):
+//   scale32 = max(max - min, 1e-8f) / qmax          IEEE float division, never a reciprocal
+//   code    = clamp(rint((x - min) / scale32), 0, qmax)   round-half-to-even
+//   stored scale = float16(scale32), stored zero = float16(min)   (round-to-nearest-even)
+// The tail group is reduced over its real elements only: the reference pads it by repeating the
+// last element, which changes neither the minimum nor the maximum.
+#include "common.cuh"
+
+namespace pkv {
+
+thread_local int g_last_cuda_error = 0;
+
+namespace {
+
+constexpr int kThreads = 256;
+
+template <int BITS>
+__global__ void pack_low_bits_kernel(const uint8_t* __restrict__ codes, int64_t rows, int64_t len,
+                                     int64_t nb, uint8_t* __restrict__ out) {
+    constexpr int VPB = 8 / BITS;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * nb) return;
+    const int64_t r = i / nb, b = i % nb;
+    const uint8_t* c = codes + r * len + b * VPB;
+    unsigned v = 0;
+#pragma unroll
+    for (int k = 0; k < VPB; ++k)
+        if (b * VPB + k < len) v += (unsigned)c[k] << (k * BITS);
+    out[i] = (uint8_t)v;
+}
+
+template <int BITS>
+__global__ void unpack_low_bits_kernel(const uint8_t* __restrict__ packed, int64_t rows,
+                                       int64_t row_bytes, int64_t len, uint8_t* __restrict__ out) {
+    constexpr int VPB = 8 / BITS;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * len) return;
+    const int64_t r = i / len, j = i % len;
+    out[i] = (uint8_t)extract_code<BITS>(packed[r * row_bytes + j / VPB], (unsigned)(j % VPB));
+}
+
+// One thread quantises `run` consecutive positions of the axis for one (outer, inner) line.
+// `run` is a multiple of lcm(group, 8/BITS), so a thread owns whole groups and whole bytes.
+template <int BITS>
+__global__ void quantize_pack_kernel(const __half* __restrict__ x, int64_t outer, int64_t A,
+                                     int64_t inner, int64_t gs, int64_t run, int64_t n_runs,
+                                     int64_t nb, int64_t ng, uint8_t* __restrict__ packed,
+                                     __half* __restrict__ scale, __half* __restrict__ mins) {
+    constexpr int VPB = 8 / BITS;
+    constexpr float QMAX = (float)((1 << BITS) - 1);
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid >= outer * n_runs * inner) return;
+    const int64_t j = tid % inner;
+    const int64_t r = (tid / inner) % n_runs;
+    const int64_t o = tid / (inner * n_runs);
+    const int64_t a_begin = r * run;
+    const int64_t a_end = min(A, a_begin + run);
+    const __half* xp = x + o * A * inner + j;
+    const int64_t row = o * inner + j;
+    uint8_t* prow = packed + row * nb;
+
+    unsigned long long word = 0;  // up to 8 finished bytes waiting to be stored
+    int word_bytes = 0;
+    int64_t word_first = a_begin / VPB;  // byte index of the first byte held in `word`
+    unsigned cur = 0;
+
+    for (int64_t g0 = a_begin; g0 < a_end; g0 += gs) {
+        const int64_t g1 = min(g0 + gs, A);
+        float lo = __half2float(xp[g0 * inner]);
+        float hi = lo;
+        for (int64_t a = g0 + 1; a < g1; ++a) {
+            const float v = __half2float(xp[a * inner]);
+            lo = fminf(lo, v);
+            hi = fmaxf(hi, v);
+        }
+        const float sc = __fdiv_rn(fmaxf(__fsub_rn(hi, lo), 1e-8f), QMAX);
+        for (int64_t a = g0; a < g1; ++a) {
+            const float v = __half2float(xp[a * inner]);
+            float qv = rintf(__fdiv_rn(__fsub_rn(v, lo), sc));
+            qv = fminf(fmaxf(qv, 0.f), QMAX);
+            const int pos = (int)(a % VPB);
+            cur |= (unsigned)qv << (pos * BITS);
+            if (pos == VPB - 1 || a == A - 1) {
+                word |= (unsigned long long)cur << (8 * word_bytes);
+                cur = 0;
+                if (++word_bytes == 8) {
+                    uint8_t* dst = prow + word_first;
+                    if ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+                        *reinterpret_cast<unsigned long long*>(dst) = word;
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) dst[k] = (uint8_t)(word >> (8 * k));
+                    }
+                    word_first += 8;
+                    word = 0;
+                    word_bytes = 0;
+                }
+            }
+        }
+        scale[row * ng + g0 / gs] = __float2half_rn(sc);
+        mins[row * ng + g0 / gs] = __float2half_rn(lo);
+    }
+    for (int k = 0; k < word_bytes; ++k) prow[word_first + k] = (uint8_t)(word >> (8 * k));
+}
+
+// Fast path for the value layout: the axis is the contiguous last dimension (inner == 1), the
+// group is 32 elements and rows are multiples of 32 long.  One thread owns one group: four 16-byte
+// loads, register min/max, and one aligned store of the group's packed bytes.
+template <int BITS>
+__global__ void quantize_pack_lastdim32_kernel(const __half* __restrict__ x, int64_t n_groups,
+                                               uint8_t* __restrict__ packed,
+                                               __half* __restrict__ scale,
+                                               __half* __restrict__ mins) {
+    constexpr float QMAX = (float)((1 << BITS) - 1);
+    const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= n_groups) return;
+    const uint4* src = reinterpret_cast<const uint4*>(x + g * 32);
+    uint4 raw[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) raw[i] = __ldg(src + i);
+    const __half* h = reinterpret_cast<const __half*>(raw);
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __half2float(h[i]);
+    float lo = v[0], hi = v[0];
+#pragma unroll
+    for (int i = 1; i < 32; ++i) {
+        lo = fminf(lo, v[i]);
+        hi = fmaxf(hi, v[i]);
+    }
+    const float sc = __fdiv_rn(fmaxf(__fsub_rn(hi, lo), 1e-8f), QMAX);
+    unsigned w[BITS];  // 32 codes * BITS bits = BITS 32-bit words
+#pragma unroll
+    for (int i = 0; i < BITS; ++i) w[i] = 0;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        float qv = rintf(__fdiv_rn(__fsub_rn(v[i], lo), sc));
+        qv = fminf(fmaxf(qv, 0.f), QMAX);
+        w[(i * BITS) / 32] |= (unsigned)qv << ((i * BITS) % 32);
+    }
+    unsigned* dst = reinterpret_cast<unsigned*>(packed + g * (4 * BITS));
+    if constexpr (BITS == 2) {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < BITS; i += 4)
+            *reinterpret_cast<uint4*>(dst + i) = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
+    }
+    scale[g] = __float2half_rn(sc);
+    mins[g] = __float2half_rn(lo);
+}
+
+template <int BITS>
+__global__ void unpack_dequantize_kernel(const uint8_t* __restrict__ packed,
+                                         const __half* __restrict__ scale,
+                                         const __half* __restrict__ mins, int64_t outer, int64_t A,
+                                         int64_t inner, int64_t gs, int64_t nb, int64_t ng,
+                                         __half* __restrict__ out) {
+    constexpr int VPB = 8 / BITS;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= outer * A * inner) return;
+    const int64_t j = i % inner;
+    const int64_t a = (i / inner) % A;
+    const int64_t o = i / (inner * A);
+    const int64_t row = o * inner + j;
+    const float c = (float)extract_code<BITS>(packed[row * nb + a / VPB], (unsigned)(a % VPB));
+    const float s = __half2float(scale[row * ng + a / gs]);
+    const float m = __half2float(mins[row * ng + a / gs]);
+    out[i] = __float2half_rn(__fadd_rn(__fmul_rn(c, s), m));  // two roundings, as the reference
+}
+
+int64_t gcd64(int64_t a, int64_t b) {
+    while (b) {
+        const int64_t t = a % b;
+        a = b;
+        b = t;
+    }
+    return a;
+}
+
+inline unsigned blocks_for(int64_t n) { return (unsigned)((n + kThreads - 1) / kThreads); }
+
+}  // namespace
+}  // namespace pkv
+
+using namespace pkv;
+
+extern "C" {
+
+int pkv_abi_version(void) { return 1; }
+
+int pkv_last_cuda_error(void) { return g_last_cuda_error; }
+
+const char* pkv_strerror(int code) {
+    switch (code) {
+        case PKV_OK: return "ok";
+        case PKV_E_BITS: return "bit width must be 2, 4 or 8";
+        case PKV_E_SHAPE: return "invalid or inconsistent sizes";
+        case PKV_E_NULL: return "a required pointer is NULL";
+        case PKV_E_LAYOUT: return "segment layout or group size not supported";
+        case PKV_E_WORKSPACE: return "scratch buffer too small";
+        case PKV_E_CUDA: return "a CUDA runtime call failed";
+        case PKV_E_LIMIT: return "a documented size limit was exceeded";
+        default: return "unknown error";
+    }
+}
+
+int pkv_device_sm_count(int device, int* sm_count) {
+    if (!sm_count) return PKV_E_NULL;
+    int v = 0;
+    PKV_CUDA_TRY(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device));
+    *sm_count = v;
+    return PKV_OK;
+}
+
+int pkv_pack_low_bits(const uint8_t* codes, int64_t rows, int64_t len, int bits, uint8_t* out,
+                      pkv_stream_t stream) {
+    if (!valid_bits(bits)) return PKV_E_BITS;
+    if (rows < 0 || len < 0) return PKV_E_SHAPE;
+    const int64_t nb = ceil_div(len, 8 / bits);
+    if (rows * nb == 0) return PKV_OK;
+    if (!codes || !out) return PKV_E_NULL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned grid = blocks_for(rows * nb);
+    if (bits == 2) pack_low_bits_kernel<2><<<grid, kThreads, 0, s>>>(codes, rows, len, nb, out);
+    else if (bits == 4) pack_low_bits_kernel<4><<<grid, kThreads, 0, s>>>(codes, rows, len, nb, out);
+    else pack_low_bits_kernel<8><<<grid, kThreads, 0, s>>>(codes, rows, len, nb, out);
+    PKV_LAUNCH_CHECK();
+    return PKV_OK;
+}
+
+int pkv_unpack_low_bits(const uint8_t* packed, int64_t rows, int64_t row_bytes, int64_t len, int bits,
+                        uint8_t* out, pkv_stream_t stream) {
+    if (!valid_bits(bits)) return PKV_E_BITS;
+    if (rows < 0 || len < 0 || row_bytes < 0 || len > row_bytes * (8 / bits)) return PKV_E_SHAPE;
+    if (rows * len == 0) return PKV_OK;
+    if (!packed || !out) return PKV_E_NULL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned grid = blocks_for(rows * len);
+    if (bits == 2) unpack_low_bits_kernel<2><<<grid, kThreads, 0, s>>>(packed, rows, row_bytes, len, out);
+    else if (bits == 4) unpack_low_bits_kernel<4><<<grid, kThreads, 0, s>>>(packed, rows, row_bytes, len, out);
+    else unpack_low_bits_kernel<8><<<grid, kThreads, 0, s>>>(packed, rows, row_bytes, len, out);
+    PKV_LAUNCH_CHECK();
+    return PKV_OK;
+}
+
+int pkv_quantize_pack(const void* x, int64_t outer, int64_t axis_len, int64_t inner, int bits,
+                      int64_t group, uint8_t* packed, void* scale, void* mins, pkv_stream_t stream) {
+    if (!valid_bits(bits)) return PKV_E_BITS;
+    if (outer < 0 || inner < 0 || axis_len <= 0 || group <= 0 || group > axis_len) return PKV_E_SHAPE;
+    if (outer * inner == 0) return PKV_OK;
+    if (!x || !packed || !scale || !mins) return PKV_E_NULL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int vpb = 8 / bits;
+    const int64_t nb = ceil_div(axis_len, vpb), ng = ceil_div(axis_len, group);
+    const __half* xh = static_cast<const __half*>(x);
+    __half* sc = static_cast<__half*>(scale);
+    __half* mn = static_cast<__half*>(mins);
+
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) &&
+                         ((reinterpret_cast<uintptr_t>(packed) & 15u) == 0);
+    if (inner == 1 && group == 32 && axis_len % 32 == 0 && aligned) {
+        const int64_t n_groups = outer * (axis_len / 32);
+        const unsigned grid = (unsigned)ceil_div(n_groups, 128);
+        if (bits == 2) quantize_pack_lastdim32_kernel<2><<<grid, 128, 0, s>>>(xh, n_groups, packed, sc, mn);
+        else if (bits == 4) quantize_pack_lastdim32_kernel<4><<<grid, 128, 0, s>>>(xh, n_groups, packed, sc, mn);
+        else quantize_pack_lastdim32_kernel<8><<<grid, 128, 0, s>>>(xh, n_groups, packed, sc, mn);
+        PKV_LAUNCH_CHECK();
+        return PKV_OK;
+    }
+
+    // a thread's run: whole groups, whole bytes, and (when it costs nothing) >= 32 packed bytes
+    const int64_t unit = group / gcd64(group, vpb) * vpb;
+    int64_t per_thread = 1;
+    while (unit * per_thread * bits < 32 * 8 && unit * per_thread < axis_len) per_thread *= 2;
+    const int64_t run = unit * per_thread;
+    const int64_t n_runs = ceil_div(axis_len, run);
+    const unsigned grid = blocks_for(outer * n_runs * inner);
+    if (bits == 2)
+        quantize_pack_kernel<2><<<grid, kThreads, 0, s>>>(xh, outer, axis_len, inner, group, run, n_runs, nb, ng, packed, sc, mn);
+    else if (bits == 4)
+        quantize_pack_kernel<4><<<grid, kThreads, 0, s>>>(xh, outer, axis_len, inner, group, run, n_runs, nb, ng, packed, sc, mn);
+    else
+        quantize_pack_kernel<8><<<grid, kThreads, 0, s>>>(xh, outer, axis_len, inner, group, run, n_runs, nb, ng, packed, sc, mn);
+    PKV_LAUNCH_CHECK();
+    return PKV_OK;
+}
+
+int pkv_unpack_dequantize(const uint8_t* packed, const void* scale, const void* mins, int64_t outer,
+                          int64_t axis_len, int64_t inner, int bits, int64_t group, void* out,
+                          pkv_stream_t stream) {
+    if (!valid_bits(bits)) return PKV_E_BITS;
+    if (outer < 0 || inner < 0 || axis_len <= 0 || group <= 0) return PKV_E_SHAPE;
+    if (outer * inner == 0) return PKV_OK;
+    if (!packed || !scale || !mins || !out) return PKV_E_NULL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t nb = ceil_div(axis_len, 8 / bits), ng = ceil_div(axis_len, group);
+    const unsigned grid = blocks_for(outer * axis_len * inner);
+    const __half* sc = static_cast<const __half*>(scale);
+    const __half* mn = static_cast<const __half*>(mins);
+    __half* o = static_cast<__half*>(out);
+    if (bits == 2)
+        unpack_dequantize_kernel<2><<<grid, kThreads, 0, s>>>(packed, sc, mn, outer, axis_len, inner, group, nb, ng, o);
+    else if (bits == 4)
+        unpack_dequantize_kernel<4><<<grid, kThreads, 0, s>>>(packed, sc, mn, outer, axis_len, inner, group, nb, ng, o);
+    else
+        unpack_dequantize_kernel<8><<<grid, kThreads, 0, s>>>(packed, sc, mn, outer, axis_len, inner, group, nb, ng, o);
+    PKV_LAUNCH_CHECK();
+    return PKV_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,282 @@
+"""Single-pass mixed-precision split-K decode attention over the three-tier KV cache (CUDA).
+
+Entry points keep the names, argument order, defaults, return types and ``ValueError`` behaviour
+of the reference's ``src/phasekv/kernels/attention_triton.py``:
+
+  decode_attention_packed (:95), decode_attention_packed_splitk (:269),
+  fused_three_tier_decode (:487), fused_three_tier_decode_single (:414),
+  _kivi_layer_partial (:604), _fp16_layer_partial (:285), _reduce_splits (:257),
+  _merge_partials (:300), fused_phasekv_decode (:643)
+
+Differences by design: every call is ONE split-K launch over all segments of the layer (prompt,
+prompt extensions, each frozen cold segment and the float16 hot buffer) plus one merge launch,
+and each KV byte is read once for the whole GQA group instead of once per query head.
+``block_n``/``num_warps`` are accepted, validated and otherwise advisory.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import replace
+from functools import lru_cache
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import _native as nv
+from .launch_config import plan_kivi_decode
+from .packing import PackedTensor, _vals_per_byte
+
+
+@lru_cache(maxsize=32)
+def _device_sm_count(device: torch.device) -> int:
+    return nv.sm_count(device)
+
+
+# --------------------------------------------------------------------------- segments
+def _packed_segment(key: PackedTensor, value: PackedTensor, num_splits: Optional[int]) -> Tuple[nv.Segment, list]:
+    """Describe one packed K/V pair with ``orig_shape == (Hkv, S, hd)`` to the kernels."""
+    if len(key.orig_shape) != 3 or tuple(value.orig_shape) != tuple(key.orig_shape):
+        raise ValueError("packed K/V must share an original shape [Hkv, S, hd]")
+    if key.axis == 1 and value.axis == 2:
+        kind = nv.PKV_SEG_KIVI
+    elif key.axis == 2 and value.axis == 2:
+        kind = nv.PKV_SEG_PER_TOKEN
+    else:
+        raise ValueError("K must be packed along tokens or head_dim, V along head_dim")
+    _vals_per_byte(key.bits), _vals_per_byte(value.bits)
+    keep = [key.packed.contiguous(), key.scale.contiguous(), key.mins.contiguous(),
+            value.packed.contiguous(), value.scale.contiguous(), value.mins.contiguous()]
+    seg = nv.Segment(*(t.data_ptr() for t in keep), int(key.orig_shape[1]), 0, kind,
+                     int(key.bits), int(value.bits), int(key.group_size), int(value.group_size),
+                     int(num_splits or 0))
+    return seg, keep
+
+
+def _fp16_segment(hot_k: torch.Tensor, hot_v: torch.Tensor) -> Tuple[nv.Segment, list]:
+    """``hot_k``/``hot_v`` are ``[Hkv, hot, hd]`` views; only the token and dim strides must be dense."""
+    if hot_k.dtype != torch.float16 or hot_v.dtype != torch.float16:
+        hot_k, hot_v = hot_k.to(torch.float16), hot_v.to(torch.float16)
+    hd = hot_k.shape[-1]
+
+    def dense_rows(t):
+        return t.stride(-1) == 1 and t.stride(-2) == hd
+    if not (dense_rows(hot_k) and dense_rows(hot_v) and hot_k.stride(0) == hot_v.stride(0)):
+        hot_k, hot_v = hot_k.contiguous(), hot_v.contiguous()
+    head_stride = hot_k.stride(0) if hot_k.shape[0] > 1 else hot_k.shape[1] * hd
+    seg = nv.Segment(hot_k.data_ptr(), None, None, hot_v.data_ptr(), None, None,
+                     int(hot_k.shape[1]), int(head_stride), nv.PKV_SEG_FP16, 8, 8, 1, 1, 0)
+    return seg, [hot_k, hot_v]
+
+
+_WORKSPACES: dict = {}
+
+
+def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    """Scratch for split-K partials, cached per (device, stream) and grown on demand."""
+    key = (device.index, stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def _run_decode(q: torch.Tensor, segments: Sequence[nv.Segment], keep: list, num_attention_heads: int,
+                num_kv_heads: int, want_out: bool, want_partial: bool):
+    hq, hd = q.shape
+    dev = q.device
+    n = len(segments)
+    arr = (nv.Segment * n)(*segments)
+    L = nv.lib()
+    sms = _device_sm_count(dev)
+    need = ctypes.c_size_t(0)
+    nv.check(L.pkv_decode_workspace_bytes(arr, n, hq, num_kv_heads, hd, sms, ctypes.byref(need)))
+    out = torch.empty((hq, hd), dtype=torch.float16, device=dev) if want_out else None
+    m = l = acc = None
+    if want_partial:
+        m = torch.empty((hq,), dtype=torch.float32, device=dev)
+        l = torch.empty((hq,), dtype=torch.float32, device=dev)
+        acc = torch.empty((hq, hd), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        stream = nv.stream_of(dev)
+        ws = _workspace(dev, stream, need.value)
+        nv.check(L.pkv_decode_attention(q.data_ptr(), arr, n, hq, num_kv_heads, hd, 1.0 / (hd ** 0.5), sms,
+                                        ws.data_ptr(), ws.numel(), nv.ptr(out), nv.ptr(m), nv.ptr(l),
+                                        nv.ptr(acc), stream))
+    del keep
+    return out, (m, l, acc)
+
+
+def _check_query(q: torch.Tensor, num_attention_heads: int, hd: int, hkv: int) -> torch.Tensor:
+    nv.require_cuda(q, "q")
+    if tuple(q.shape) != (num_attention_heads, hd):
+        raise ValueError(f"q must be [Hq={num_attention_heads}, hd={hd}], got {tuple(q.shape)}")
+    if q.dtype != torch.float16:
+        raise ValueError("query must be [Hq, head_dim] float16")
+    if num_attention_heads % hkv != 0:
+        raise ValueError(f"Hq {num_attention_heads} is not a multiple of Hkv {hkv}")
+    return q.contiguous()
+
+
+# --------------------------------------------------------------------------- per-token layout
+def decode_attention_packed(q: torch.Tensor, packed_k: PackedTensor, packed_v: PackedTensor,
+                            num_attention_heads: int, block_n: int = 64) -> torch.Tensor:
+    """Packed-KV decode attention, per-token layout (both K and V from
+    ``quantize_pack(x, bits, -1, gs)`` of ``[Hkv, S, hd]``), without splitting the sequence."""
+    return decode_attention_packed_splitk(q, packed_k, packed_v, num_attention_heads, 1, block_n)
+
+
+def decode_attention_packed_splitk(q: torch.Tensor, packed_k: PackedTensor, packed_v: PackedTensor,
+                                   num_attention_heads: int, num_splits: int = 8,
+                                   block_n: int = 64) -> torch.Tensor:
+    """Split-K flash-decoding over one per-token-layout segment."""
+    hkv, S, hd = packed_k.orig_shape
+    q = _check_query(q, num_attention_heads, hd, hkv)
+    vpb, gs = _vals_per_byte(packed_k.bits), packed_k.group_size
+    if hd % vpb != 0 or hd % gs != 0:
+        raise ValueError(f"head_dim({hd}) must be divisible by vpb({vpb}) and group_size({gs})")
+    seg, keep = _packed_segment(packed_k, packed_v, max(1, min(int(num_splits), S)))
+    out, _ = _run_decode(q, [seg], keep, num_attention_heads, hkv, True, False)
+    return out
+
+
+def _three_tier_segments(kv, num_splits: int):
+    segs, keep, hkv, hd = [], [], None, None
+    for k, v in ((kv.prompt_k, kv.prompt_v), (kv.cold_k, kv.cold_v)):
+        if k is not None:
+            s, kp = _packed_segment(k, v, max(1, min(int(num_splits), k.orig_shape[1])))
+            segs.append(s), keep.extend(kp)
+            hkv, _, hd = k.orig_shape
+    if kv.hot_k is not None and kv.hot_k.shape[-2] > 0:
+        s, kp = _fp16_segment(kv.hot_k, kv.hot_v)
+        segs.append(s), keep.extend(kp)
+        hkv, hd = kv.hot_k.shape[0], kv.hot_k.shape[-1]
+    if not segs:
+        raise ValueError("all three tiers are empty, nothing to attend to")
+    return segs, keep, hkv, hd
+
+
+def fused_three_tier_decode(q, kv, num_attention_heads, num_splits: int = 8, block_n: int = 64):
+    """One attention over [packed prompt] + [packed cold] + [float16 hot] (per-token layout,
+    ``kv`` a ``ThreeTierKV`` with ``[Hkv, len, hd]`` tiers).  Returns ``[Hq, hd]`` float16."""
+    segs, keep, hkv, hd = _three_tier_segments(kv, num_splits)
+    q = _check_query(q, num_attention_heads, hd, hkv)
+    out, _ = _run_decode(q, segs, keep, num_attention_heads, hkv, True, False)
+    return out
+
+
+def fused_three_tier_decode_single(q, kv, num_attention_heads, num_splits: int = 32, block_n: int = 64):
+    """Same result as :func:`fused_three_tier_decode`.  In the reference this is the (slower)
+    one-launch variant; here every entry point already is a single split-K launch, with the
+    tier chosen per work item rather than per lane."""
+    return fused_three_tier_decode(q, kv, num_attention_heads, num_splits, block_n)
+
+
+# --------------------------------------------------------------------------- partial algebra
+def _reduce_splits(pm: torch.Tensor, pl: torch.Tensor, pacc: torch.Tensor):
+    """Merge split partials laid out as the reference does, ``pm, pl [Hq, splits]`` and
+    ``pacc [Hq, splits, hd]``, into one un-normalised partial ``(m [Hq], l [Hq], acc [Hq, hd])``."""
+    return _merge_stacked(pm.t().contiguous().float(), pl.t().contiguous().float(),
+                          pacc.transpose(0, 1).contiguous().float(), want_out=False)[1]
+
+
+def _merge_stacked(m: torch.Tensor, l: torch.Tensor, acc: torch.Tensor, want_out: bool):
+    """m, l ``[parts, Hq]``, acc ``[parts, Hq, hd]`` float32 contiguous."""
+    nv.require_cuda(acc, "partials")
+    parts, hq, hd = acc.shape
+    dev = acc.device
+    out = torch.empty((hq, hd), dtype=torch.float16, device=dev) if want_out else None
+    mo = torch.empty((hq,), dtype=torch.float32, device=dev)
+    lo = torch.empty((hq,), dtype=torch.float32, device=dev)
+    ao = torch.empty((hq, hd), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        nv.check(nv.lib().pkv_merge_partials(m.data_ptr(), l.data_ptr(), acc.data_ptr(), parts, hq, hd,
+                                             nv.ptr(out), mo.data_ptr(), lo.data_ptr(), ao.data_ptr(),
+                                             nv.stream_of(dev)))
+    return out, (mo, lo, ao)
+
+
+def _merge_partials(partials) -> torch.Tensor:
+    """Log-sum-exp merge of a list of ``(m, l, acc)`` partials into the final ``[Hq, hd]`` float16."""
+    m = torch.stack([p[0] for p in partials]).contiguous().float()
+    l = torch.stack([p[1] for p in partials]).contiguous().float()
+    acc = torch.stack([p[2] for p in partials]).contiguous().float()
+    return _merge_stacked(m, l, acc, want_out=True)[0]
+
+
+def _fp16_layer_partial(q, hot_k, hot_v, num_attention_heads):
+    """Un-normalised partial of the float16 hot tier, ``hot_k``/``hot_v`` ``[Hkv, hot, hd]``."""
+    hkv, hot, hd = hot_k.shape
+    q = _check_query(q, num_attention_heads, hd, hkv)
+    seg, keep = _fp16_segment(hot_k, hot_v)
+    return _run_decode(q, [seg], keep, num_attention_heads, hkv, False, True)[1]
+
+
+def _kivi_layer_partial(q, key: PackedTensor, value: PackedTensor, num_attention_heads: int,
+                        num_splits: Optional[int] = None, block_n: Optional[int] = None,
+                        num_warps: Optional[int] = None):
+    """Read one real PhaseKV packed segment (K along tokens, V along head_dim, batch removed) and
+    return the softmax partial ``(m, l, acc)`` that can be merged across segments."""
+    if key.axis != 1 or value.axis != 2 or len(key.orig_shape) != 3:
+        raise ValueError("K must be packed along the token axis and V along head_dim, with batch removed")
+    hkv, seq_len, head_dim = key.orig_shape
+    if tuple(value.orig_shape) != tuple(key.orig_shape) or seq_len <= 0:
+        raise ValueError("packed K/V shapes differ or are empty")
+    if tuple(q.shape) != (num_attention_heads, head_dim) or q.dtype != torch.float16:
+        raise ValueError("query must be [Hq, head_dim] float16")
+    if num_attention_heads % hkv or head_dim & (head_dim - 1):
+        raise ValueError("Hq must be a multiple of Hkv and head_dim a power of two")
+    if q.device != key.packed.device or q.device != value.packed.device:
+        raise ValueError("query and packed K/V must be on the same device")
+    nv.require_cuda(q, "q")
+    # validates num_splits / block_n / num_warps exactly as the reference planner does
+    plan_kivi_decode(seq_len, num_attention_heads, head_dim, _device_sm_count(q.device),
+                     num_splits, block_n, num_warps)
+    seg, keep = _packed_segment(key, value, num_splits)
+    return _run_decode(q.contiguous(), [seg], keep, num_attention_heads, hkv, False, True)[1]
+
+
+# --------------------------------------------------------------------------- the decode entry point
+def _remove_batch(pt: PackedTensor) -> PackedTensor:
+    if pt.orig_shape[0] != 1:
+        raise ValueError("the PhaseKV decode path supports batch=1 only")
+    return replace(pt, packed=pt.packed[0], scale=pt.scale[0], mins=pt.mins[0],
+                   orig_shape=tuple(pt.orig_shape[1:]), axis=pt.axis - 1)
+
+
+def layer_segments(tiers, num_splits: Optional[int] = None):
+    """Segment descriptors for every tier of a ``LayerTiers`` (batch 1), in prompt, extensions,
+    cold, hot order, plus the tensors that must stay alive while they are in use."""
+    segs: List[nv.Segment] = []
+    keep: list = []
+    hkv = hd = None
+    for segment in [tiers.prompt, *tiers.prompt_extensions, *tiers.cold]:
+        key, value = _remove_batch(segment.key), _remove_batch(segment.value)
+        if key.axis != 1 or value.axis != 2:
+            raise ValueError("K must be packed along the token axis and V along head_dim")
+        s, kp = _packed_segment(key, value, num_splits)
+        segs.append(s), keep.extend(kp)
+        hkv, _, hd = key.orig_shape
+    if tiers.hot_len:
+        hot_k, hot_v = tiers.hot_views()
+        if hot_k.shape[0] != 1:
+            raise ValueError("the PhaseKV decode path supports batch=1 only")
+        s, kp = _fp16_segment(hot_k[0], hot_v[0])
+        segs.append(s), keep.extend(kp)
+    return segs, keep, hkv, hd
+
+
+def fused_phasekv_decode(q: torch.Tensor, tiers, num_attention_heads: int,
+                         num_splits: Optional[int] = None, block_n: Optional[int] = None,
+                         num_warps: Optional[int] = None) -> torch.Tensor:
+    """Batch-1 PhaseKV decode attention for one query token: ``q`` ``[Hq, hd]`` float16 against
+    ``tiers`` (what ``PhaseKVCache.layer_tiers`` returns).  The packed tiers are never expanded in
+    memory; all segments, however many cold segments have been frozen, go through one launch."""
+    segs, keep, hkv, hd = layer_segments(tiers, num_splits)
+    q = _check_query(q, num_attention_heads, hd, hkv)
+    if hd & (hd - 1):
+        raise ValueError("head_dim must be a power of two")
+    plan_kivi_decode(max(1, tiers.prompt.length), num_attention_heads, hd, _device_sm_count(q.device),
+                     num_splits, block_n, num_warps)
+    out, _ = _run_decode(q, segs, keep, num_attention_heads, hkv, True, False)
+    return out

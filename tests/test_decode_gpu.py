@@ -1,0 +1,205 @@
+"""Parity of the CUDA decode attention (through the C ABI) with the oracle and the golden fixtures.
+
+The bar for attention is max-abs <= 2e-3 and max-abs / max|ref| <= 1e-2 against the
+dequantise-then-attend semantics (conftest.attention_close)."""
+import pytest
+import torch
+
+from conftest import attention_close, from_f16, load_packed
+from util import make_tiers, remove_batch, to_gpu_packed
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def attn():
+    from phasekv_b200.kernels import attention_triton
+    return attention_triton
+
+
+def _pack_tiers(oracle, shape, prompt, pbits, cold_lens, cbits, hot, seed, gsk=32, gsv=32):
+    """Dense seeded tiers -> oracle-packed segments (CPU) in prompt, cold... order plus hot."""
+    from phasekv_b200 import workloads
+    gen = torch.Generator().manual_seed(seed)
+    segs = []
+    for length, bits in [(prompt, pbits)] + [(c, cbits) for c in cold_lens]:
+        k, v = workloads.make_kv(gen, shape.num_kv_heads, length, shape.head_dim)
+        segs.append((oracle.quantize_pack(k, bits, -2, gsk), oracle.quantize_pack(v, bits, -1, gsv)))
+    hk = hv = None
+    if hot:
+        hk, hv = workloads.make_kv(gen, shape.num_kv_heads, hot, shape.head_dim)
+    q = workloads.make_query(gen, shape.num_q_heads, shape.head_dim)
+    return segs, hk, hv, q
+
+
+def test_golden_c1_plumbing_case(golden, attn):
+    z = golden("attention_c1.npz")
+    segs = [(load_packed(z, "prompt_k"), load_packed(z, "prompt_v")),
+            (load_packed(z, "cold_k"), load_packed(z, "cold_v"))]
+    hk, hv = from_f16(z["hot_k"]), from_f16(z["hot_v"])
+    tiers = make_tiers(segs, hk, hv, hot_len=hk.shape[2])
+    q = from_f16(z["q"])
+    out = attn.fused_phasekv_decode(q[0, :, 0, :].cuda(), tiers, q.shape[1])
+    assert out.shape == (14, 64) and out.dtype == torch.float16
+    attention_close(out, from_f16(z["out"])[0, :, 0, :])
+
+
+def test_golden_small_ragged_cases(golden, attn):
+    z = golden("attention_small.npz")
+    for i in range(int(z["n_cases"][0])):
+        segs = []
+        for tier in ("prompt", "cold"):
+            if f"a{i}.{tier}_k.meta" in z:
+                segs.append((load_packed(z, f"a{i}.{tier}_k"), load_packed(z, f"a{i}.{tier}_v")))
+        hk = hv = None
+        if f"a{i}.hot_k" in z:
+            hk, hv = from_f16(z[f"a{i}.hot_k"]), from_f16(z[f"a{i}.hot_v"])
+        q = from_f16(z[f"a{i}.q"])
+        if not segs:
+            continue
+        tiers = make_tiers(segs, hk, hv, hot_len=0 if hk is None else hk.shape[2])
+        out = attn.fused_phasekv_decode(q[0, :, 0, :].cuda(), tiers, q.shape[1])
+        attention_close(out, from_f16(z[f"a{i}.out"])[0, :, 0, :])
+
+
+@pytest.mark.parametrize("length,heads,dim,kb,vb", [
+    (1, 4, 8, 2, 4), (10, 4, 64, 8, 8), (127, 12, 128, 4, 4), (513, 12, 128, 2, 2),
+    (8193, 12, 128, 4, 4), (28672, 12, 128, 4, 4), (129, 4, 256, 8, 4)])
+def test_kivi_layer_partial_shapes_of_the_reference_test(oracle, attn, length, heads, dim, kb, vb):
+    """The seven shapes and three launch options of the reference's
+    tests/test_phasekv_launch_config.py:64-79, with its own tolerance (atol 3e-4, rtol 1e-3)
+    against a float32 dense-quantised softmax built in the test."""
+    gen = torch.Generator().manual_seed(42)
+    q = torch.randn(heads, dim, generator=gen).half()
+    kd = torch.randn(2, length, dim, generator=gen).half()
+    vd = torch.randn(2, length, dim, generator=gen).half()
+    k, v = oracle.quantize_pack(kd, kb, 1, 32), oracle.quantize_pack(vd, vb, 2, 32)
+
+    def dense_float(pt):
+        codes = oracle.unpack_low_bits(pt.packed, pt.bits, pt.axis_len).float()
+        groups = torch.arange(pt.axis_len) // pt.group_size
+        return (codes * pt.scale.float()[..., groups] + pt.mins.float()[..., groups]).movedim(-1, pt.axis)
+
+    dk = dense_float(k).repeat_interleave(heads // 2, dim=0)
+    dv = dense_float(v).repeat_interleave(heads // 2, dim=0)
+    probs = torch.softmax(torch.einsum("hd,hsd->hs", q.float(), dk) / dim ** 0.5, dim=-1)
+    expected = torch.einsum("hs,hsd->hd", probs, dv)
+    kg, vg = to_gpu_packed(k), to_gpu_packed(v)
+    for options in ({}, {"num_splits": 8, "block_n": 64, "num_warps": 4}, {"num_splits": 3}):
+        m, total, acc = attn._kivi_layer_partial(q.cuda(), kg, vg, heads, **options)
+        assert m.shape == (heads,) and acc.shape == (heads, dim)
+        torch.testing.assert_close((acc / total[:, None]).cpu(), expected, atol=3e-4, rtol=1e-3)
+
+
+@pytest.mark.parametrize("prompt", [4096, 8192, 16384, 32768, 131072])
+def test_qwen7b_single_layer_contexts(oracle, attn, prompt):
+    """2-bit prompt of 4K..128K tokens + 256 cold tokens at 4 bits + 128 hot tokens (7B shape)."""
+    from phasekv_b200 import workloads
+    shape = workloads.QWEN2_5_7B
+    segs, hk, hv, q = _pack_tiers(oracle, shape, prompt, 2, [256], 4, 128, seed=prompt)
+    ref = oracle.segments_decode_reference(q[0, :, 0, :], segs, hk, hv, shape.num_q_heads)
+    tiers = make_tiers(segs, hk, hv, hot_len=128)
+    out = attn.fused_phasekv_decode(q[0, :, 0, :].cuda(), tiers, shape.num_q_heads)
+    attention_close(out, ref)
+
+
+def test_many_cold_segments_and_hot_capacity(oracle, attn):
+    """cold = 8 frozen segments of 64 tokens, hot buffer with spare capacity (only hot_len valid)."""
+    from phasekv_b200 import workloads
+    shape = workloads.QWEN2_5_7B
+    segs, hk, hv, q = _pack_tiers(oracle, shape, 1000, 2, [64] * 8, 4, 77, seed=99)
+    ref = oracle.segments_decode_reference(q[0, :, 0, :], segs, hk, hv, shape.num_q_heads)
+    cap_k = torch.full((1, 4, 192, 128), float("nan"), dtype=torch.float16)
+    cap_v = torch.full((1, 4, 192, 128), float("nan"), dtype=torch.float16)
+    cap_k[:, :, :77], cap_v[:, :, :77] = hk, hv
+    tiers = make_tiers(segs, cap_k, cap_v, hot_len=77)
+    out = attn.fused_phasekv_decode(q[0, :, 0, :].cuda(), tiers, shape.num_q_heads)
+    assert torch.isfinite(out).all()
+    attention_close(out, ref)
+    # more segments than one launch carries inline
+    segs2, hk2, hv2, q2 = _pack_tiers(oracle, workloads.QWEN2_0_5B, 300, 2, [32] * 40, 4, 9, seed=98)
+    ref2 = oracle.segments_decode_reference(q2[0, :, 0, :], segs2, hk2, hv2, 14)
+    out2 = attn.fused_phasekv_decode(q2[0, :, 0, :].cuda(), make_tiers(segs2, hk2, hv2, hot_len=9), 14)
+    attention_close(out2, ref2)
+
+
+def test_split_count_does_not_change_the_result(oracle, attn):
+    from phasekv_b200 import workloads
+    shape = workloads.QWEN2_5_7B
+    segs, hk, hv, q = _pack_tiers(oracle, shape, 5000, 2, [], 4, 0, seed=7)
+    kg, vg = remove_batch(to_gpu_packed(segs[0][0])), remove_batch(to_gpu_packed(segs[0][1]))
+    outs = []
+    for ns in (1, 2, 7, 64, 128, None):
+        m, l, acc = attn._kivi_layer_partial(q[0, :, 0, :].cuda(), kg, vg, 28, num_splits=ns)
+        outs.append((acc / l[:, None]).cpu())
+    for o in outs[1:]:
+        torch.testing.assert_close(o, outs[0], atol=2e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+def test_per_token_layout_entry_points(oracle, attn, bits):
+    """decode_attention_packed[_splitk] and fused_three_tier_decode take K and V both packed along
+    head_dim (the layout of the reference's published micro-benchmark)."""
+    from phasekv_b200.kernels.tiers import ThreeTierKV
+    gen = torch.Generator().manual_seed(1234)
+    hkv, hq, hd, S = 4, 28, 128, 1500
+    K, V = torch.randn(hkv, S, hd, generator=gen).half(), torch.randn(hkv, S, hd, generator=gen).half()
+    Kc, Vc = torch.randn(hkv, 90, hd, generator=gen).half(), torch.randn(hkv, 90, hd, generator=gen).half()
+    Kh, Vh = torch.randn(hkv, 33, hd, generator=gen).half(), torch.randn(hkv, 33, hd, generator=gen).half()
+    q = torch.randn(hq, hd, generator=gen).half()
+    pk, pv = oracle.quantize_pack(K, bits, -1, 32), oracle.quantize_pack(V, bits, -1, 32)
+    ck, cv = oracle.quantize_pack(Kc, 4, -1, 32), oracle.quantize_pack(Vc, 4, -1, 32)
+    ref1 = oracle.attention_dense(q, oracle.unpack_dequantize(pk), oracle.unpack_dequantize(pv), hq)
+    out_single = attn.decode_attention_packed(q.cuda(), to_gpu_packed(pk), to_gpu_packed(pv), hq)
+    out_split = attn.decode_attention_packed_splitk(q.cuda(), to_gpu_packed(pk), to_gpu_packed(pv), hq, num_splits=16)
+    attention_close(out_single, ref1)
+    attention_close(out_split, ref1)
+    kv_o = oracle.ThreeTierKV(pk, pv, ck, cv, Kh, Vh)
+    k_all, v_all = oracle._dequant_concat(kv_o)
+    ref3 = oracle.attention_dense(q, k_all, v_all, hq)
+    kv = ThreeTierKV(to_gpu_packed(pk), to_gpu_packed(pv), to_gpu_packed(ck), to_gpu_packed(cv), Kh.cuda(), Vh.cuda())
+    attention_close(attn.fused_three_tier_decode(q.cuda(), kv, hq), ref3)
+    attention_close(attn.fused_three_tier_decode_single(q.cuda(), kv, hq), ref3)
+
+
+def test_partials_merge_like_the_reference_algebra(oracle, attn):
+    """_fp16_layer_partial + _kivi_layer_partial + _merge_partials == one fused call; _reduce_splits
+    accepts the reference's [Hq, splits] layout."""
+    from phasekv_b200 import workloads
+    shape = workloads.QWEN2_0_5B
+    segs, hk, hv, q = _pack_tiers(oracle, shape, 700, 2, [100], 4, 50, seed=5)
+    qg = q[0, :, 0, :].cuda()
+    parts = [attn._kivi_layer_partial(qg, remove_batch(to_gpu_packed(k)), remove_batch(to_gpu_packed(v)), 14)
+             for k, v in segs]
+    parts.append(attn._fp16_layer_partial(qg, hk[0].cuda(), hv[0].cuda(), 14))
+    merged = attn._merge_partials(parts)
+    fused = attn.fused_phasekv_decode(qg, make_tiers(segs, hk, hv, hot_len=50), 14)
+    torch.testing.assert_close(merged.float(), fused.float(), atol=1e-3, rtol=1e-3)
+    attention_close(merged, oracle.segments_decode_reference(q[0, :, 0, :], segs, hk, hv, 14))
+    pm = torch.stack([p[0] for p in parts], dim=1)
+    pl = torch.stack([p[1] for p in parts], dim=1)
+    pacc = torch.stack([p[2] for p in parts], dim=1)
+    m, l, acc = attn._reduce_splits(pm, pl, pacc)
+    torch.testing.assert_close((acc / l[:, None]).half().float(), merged.float(), atol=1e-3, rtol=1e-3)
+
+
+def test_argument_errors(oracle, attn):
+    from phasekv_b200 import workloads
+    segs, hk, hv, q = _pack_tiers(oracle, workloads.QWEN2_0_5B, 64, 2, [], 4, 0, seed=1)
+    k, v = remove_batch(to_gpu_packed(segs[0][0])), remove_batch(to_gpu_packed(segs[0][1]))
+    qg = q[0, :, 0, :].cuda()
+    with pytest.raises(ValueError):
+        attn._kivi_layer_partial(qg.float(), k, v, 14)          # query must be float16
+    with pytest.raises(ValueError):
+        attn._kivi_layer_partial(qg[:13], k, v, 13)             # 13 heads over 2 KV heads
+    with pytest.raises(ValueError):
+        attn._kivi_layer_partial(qg, v, v, 14)                  # K packed along the wrong axis
+    with pytest.raises(ValueError):
+        attn._kivi_layer_partial(qg, k, v, 14, num_splits=0)
+    with pytest.raises(ValueError):
+        attn._kivi_layer_partial(qg, k, v, 14, block_n=3)
+    batched = to_gpu_packed(segs[0][0])
+    batched.orig_shape = (2,) + tuple(batched.orig_shape[1:])
+    from phasekv_b200.kernels.tiers import LayerTiers, PackedKVSegment
+    with pytest.raises(ValueError):
+        attn.fused_phasekv_decode(qg, LayerTiers(PackedKVSegment(batched, batched)), 14)

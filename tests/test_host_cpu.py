@@ -1,0 +1,96 @@
+"""Host-side logic that needs no GPU: the planner, the C-ABI library's exports, argument checks."""
+import ctypes
+import json
+import os
+import re
+
+import pytest
+import torch
+
+from conftest import GOLDEN, ROOT
+
+
+def test_planner_matches_reference_outputs():
+    from phasekv_b200.kernels.launch_config import plan_kivi_decode
+    rows = json.load(open(os.path.join(GOLDEN, "planner.json")))
+    assert len(rows) > 100
+    for r in rows:
+        c = plan_kivi_decode(*r["args"], **r["kwargs"])
+        assert [c.num_splits, c.split_len, c.block_n, c.num_warps] == r["plan"], r
+
+
+def test_planner_invariants_and_errors():
+    """tests/test_phasekv_launch_config.py:9-47 of the reference."""
+    from phasekv_b200.kernels.launch_config import plan_kivi_decode
+    for length in (1, 7, 31, 127, 128, 129, 511, 512, 8193, 28672):
+        for heads, dim, sms in ((12, 128, 46), (4, 8, 1), (32, 256, 132), (28, 128, 148)):
+            c = plan_kivi_decode(length, heads, dim, sms)
+            assert 1 <= c.num_splits <= 128
+            assert (c.num_splits - 1) * c.split_len < length <= c.num_splits * c.split_len
+            assert c.split_len % c.block_n == 0 and c.block_n * dim <= 1024
+    old = plan_kivi_decode(8192, 12, 128, 46, 8, 64, 4)
+    assert (old.num_splits, old.split_len, old.block_n, old.num_warps) == (8, 1024, 64, 4)
+    uneven = plan_kivi_decode(10, 12, 128, 46, num_splits=8)
+    assert (uneven.num_splits, uneven.split_len) == (5, 2)
+    assert plan_kivi_decode(1, 12, 128, 46, num_splits=100).num_splits == 1
+    assert plan_kivi_decode(32768, 28, 128, 148) == plan_kivi_decode(32768, 28, 128, 148)
+    for kwargs in ({"num_splits": 0}, {"block_n": 0}, {"block_n": 3}, {"num_warps": 3}):
+        with pytest.raises(ValueError):
+            plan_kivi_decode(128, 12, 128, 46, **kwargs)
+    with pytest.raises(ValueError):
+        plan_kivi_decode(0, 12, 128, 46)
+    with pytest.raises(ValueError):
+        plan_kivi_decode(16, 12, 96, 46)
+
+
+def test_library_exports_every_declared_symbol():
+    from phasekv_b200 import _native, build
+    build.build()
+    header = open(os.path.join(ROOT, "include", "phasekv_b200.h")).read()
+    declared = set(re.findall(r"\b(pkv_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations parsed"
+    lib = ctypes.CDLL(_native.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    assert declared == set(_native.EXPORTED_SYMBOLS), declared ^ set(_native.EXPORTED_SYMBOLS)
+    L = _native.lib()
+    assert L.pkv_abi_version() >= 1
+    assert L.pkv_strerror(0) == b"ok" and b"bit width" in L.pkv_strerror(-1)
+    assert ctypes.sizeof(_native.Segment) == 6 * 8 + 2 * 8 + 6 * 4
+
+
+def test_abi_rejects_bad_arguments_without_touching_a_gpu():
+    from phasekv_b200 import _native
+    L = _native.lib()
+    assert L.pkv_pack_low_bits(None, 4, 4, 3, None, None) == _native.PKV_E_BITS
+    assert L.pkv_pack_low_bits(None, 4, 4, 2, None, None) == _native.PKV_E_NULL
+    assert L.pkv_quantize_pack(None, 1, 0, 1, 2, 1, None, None, None, None) == _native.PKV_E_SHAPE
+    assert L.pkv_quantize_pack(None, 1, 8, 1, 2, 9, None, None, None, None) == _native.PKV_E_SHAPE
+    assert L.pkv_merge_partials(None, None, None, 1, 1, 8, None, None, None, None, None) == _native.PKV_E_NULL
+    need = ctypes.c_size_t(0)
+    seg = _native.Segment(1, 1, 1, 1, 1, 1, 4096, 0, _native.PKV_SEG_KIVI, 2, 2, 32, 32, 0)
+    arr = (_native.Segment * 1)(seg)
+    assert L.pkv_decode_workspace_bytes(arr, 1, 28, 4, 128, 148, ctypes.byref(need)) == 0
+    assert need.value > 0 and need.value % (28 * 130 * 4) == 0
+    assert L.pkv_decode_workspace_bytes(arr, 1, 28, 5, 128, 148, ctypes.byref(need)) == _native.PKV_E_SHAPE
+    seg.k_bits = 3
+    arr = (_native.Segment * 1)(seg)
+    assert L.pkv_decode_workspace_bytes(arr, 1, 28, 4, 128, 148, ctypes.byref(need)) == _native.PKV_E_BITS
+
+
+def test_cpu_tensors_are_refused():
+    from phasekv_b200.kernels import packing
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        packing.quantize_pack(torch.zeros(2, 8, dtype=torch.float16), 2, -1, 4)
+    with pytest.raises(ValueError):
+        packing.quantize_pack(torch.zeros(2, 8, dtype=torch.float16), 3, -1, 4)
+    with pytest.raises(ValueError):
+        packing._vals_per_byte(16)
+
+
+def test_algorithmic_bytes_table():
+    from phasekv_b200 import workloads as w
+    s = w.QWEN2_5_7B
+    assert w.decode_algorithmic_bytes(s, 4096, 2, 256, 4, 128) == 2_013_184
+    assert w.decode_algorithmic_bytes(s, 32768, 2, 256, 4, 128) == 13_023_232
+    assert w.decode_algorithmic_bytes(s, 131072, 2, 256, 4, 128) == 50_771_968
