@@ -1,0 +1,440 @@
+"""Decode-attention benchmark of the three-tier packed KV path (Qwen2.5-7B attention shape).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--prompt S]
+
+One *step* is one decode token's attention over all 28 layers of one sequence: per layer a 2-bit
+packed prompt tier of ``--prompt`` tokens (default 32768), a 4-bit cold tier of 256 tokens and a
+float16 hot tier of 128 tokens, batch 1, 28 query / 4 KV heads, head_dim 128.  The 28 layers own
+distinct KV buffers (364 MB at 32768 tokens, larger than the 126 MB L2), so a step streams its
+bytes from HBM.  ``value`` is algorithmic bytes per second with everything resident in HBM and
+the step replayed as a CUDA graph; ``e2e`` is the same step through the public Python entry
+point with q copied from pinned host memory and the output copied back, every step.
+
+With more than one GPU (launched by torch.distributed.run) every rank decodes its own sequence
+(batch sharding, no collective); the reported time is the maximum over ranks.
+
+``--impl reference`` times the CPU restatement of the reference's dequantise-then-attend
+(oracle/) on the host cores for the same layer shape, one layer per step.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+COLD_LEN, HOT_LEN, PROMPT_BITS, COLD_BITS, GROUP = 256, 128, 2, 4, 32
+METRIC = "decode_attn_hbm_GBps"
+UNIT = "GB/s"
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch at 32768 prompt tokens,
+# from the ncu capture summarised under profiles/ (None until a capture exists).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--prompt", type=int, default=32768, help="prompt-tier tokens per layer")
+    ap.add_argument("--layers", type=int, default=28)
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the context sweep, the SDPA baselines and the CPU baseline")
+    return ap.parse_args()
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self._stop = index, [], threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
+                                     timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=10)
+
+    def summary(self):
+        mhz = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        reasons = []
+        for i, name in enumerate(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), 2):
+            if any(len(r) > i and r[i].lower().startswith("active") for r in self.rows):
+                reasons.append(name)
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+# ----------------------------------------------------------------------------- workload
+class LayerSet:
+    """Packed three-tier KV of `layers` layers resident on one GPU, plus per-layer q and outputs."""
+
+    def __init__(self, torch, device, prompt_len, layers, seed):
+        from phasekv_b200 import workloads
+        from phasekv_b200.kernels import packing
+        from phasekv_b200.kernels.tiers import LayerTiers, PackedKVSegment
+        self.shape = shape = workloads.QWEN2_5_7B
+        self.prompt_len, self.layers = prompt_len, layers
+        gen = torch.Generator(device=device).manual_seed(seed)
+
+        def kv(length):
+            k = torch.randn(1, shape.num_kv_heads, length, shape.head_dim, generator=gen, device=device).half()
+            v = torch.randn(1, shape.num_kv_heads, length, shape.head_dim, generator=gen, device=device).half()
+            for c in workloads.OUTLIER_CHANNELS[shape.head_dim]:
+                k[..., c] *= workloads.OUTLIER_GAIN
+            return k, v
+
+        def pack(k, v, bits):
+            return PackedKVSegment(packing.quantize_pack(k, bits, -2, GROUP), packing.quantize_pack(v, bits, -1, GROUP))
+
+        self.tiers, self.q = [], []
+        for _ in range(layers):
+            pk, pv = kv(prompt_len)
+            ck, cv = kv(COLD_LEN)
+            hk, hv = kv(HOT_LEN)
+            self.tiers.append(LayerTiers(prompt=pack(pk, pv, PROMPT_BITS), cold=[pack(ck, cv, COLD_BITS)],
+                                         hot_k=hk, hot_v=hv, hot_len=HOT_LEN))
+            self.q.append(torch.randn(shape.num_q_heads, shape.head_dim, generator=gen, device=device).half())
+            del pk, pv
+        self.bytes_per_layer = workloads.decode_algorithmic_bytes(shape, prompt_len, PROMPT_BITS, COLD_LEN,
+                                                                 COLD_BITS, HOT_LEN, GROUP, GROUP)
+        self.kv_bytes_resident = sum(t.prompt.nbytes + t.cold[0].nbytes + 2 * t.hot_k.numel() * 2 for t in self.tiers)
+
+
+class NativeStep:
+    """The step as direct C-ABI calls (descriptor arrays built once), for CUDA-graph capture."""
+
+    def __init__(self, torch, ls: LayerSet, device):
+        from phasekv_b200 import _native as nv
+        from phasekv_b200.kernels.attention_cuda import layer_segments
+        self.nv, self.torch, self.ls, self.device = nv, torch, ls, device
+        self.L = nv.lib()
+        self.sms = nv.sm_count(device)
+        self.calls, self.keep = [], []
+        need_max = 0
+        for t in ls.tiers:
+            segs, keep, hkv, hd = layer_segments(t)
+            arr = (nv.Segment * len(segs))(*segs)
+            need = ctypes.c_size_t(0)
+            nv.check(self.L.pkv_decode_workspace_bytes(arr, len(segs), ls.shape.num_q_heads, hkv, hd, self.sms,
+                                                       ctypes.byref(need)))
+            need_max = max(need_max, need.value)
+            self.calls.append((arr, len(segs)))
+            self.keep.append(keep)
+        self.ws = torch.empty(need_max, dtype=torch.uint8, device=device)
+        self.out = [torch.empty_like(q) for q in ls.q]
+        self.launches_per_step = 2 * ls.layers
+
+    def run(self):
+        s, ls = self.ls.shape, self.ls
+        stream = self.nv.stream_of(self.device)
+        for i, (arr, n) in enumerate(self.calls):
+            self.nv.check(self.L.pkv_decode_attention(
+                ls.q[i].data_ptr(), arr, n, s.num_q_heads, s.num_kv_heads, s.head_dim,
+                1.0 / (s.head_dim ** 0.5), self.sms, self.ws.data_ptr(), self.ws.numel(),
+                self.out[i].data_ptr(), None, None, None, stream))
+
+
+def time_graph(torch, fn, steps, warmup, barrier=None, sampler=None, min_samples=5):
+    """Capture fn() into a CUDA graph, replay it `warmup` untimed then `steps` timed times.
+    Returns the mean milliseconds per step (CUDA events on the replay stream).  When a clock
+    sampler is given it runs during the timed replays; if they end before it has `min_samples`
+    readings, the same graph keeps replaying (untimed) until it has them, so the clocks are read
+    under the load that was timed."""
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        fn()  # lazy initialisation outside the capture
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            fn()
+        for _ in range(warmup):
+            graph.replay()
+        stream.synchronize()
+        if barrier:
+            barrier()
+        if sampler is not None:
+            sampler.__enter__()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            graph.replay()
+        e1.record(stream)
+        e1.synchronize()
+        torch.cuda.synchronize()
+        if sampler is not None:
+            t_end = time.time() + 3.0
+            while len(sampler.rows) < min_samples and time.time() < t_end:
+                for _ in range(50):
+                    graph.replay()
+                stream.synchronize()
+            sampler.__exit__(None, None, None)
+        if barrier:
+            barrier()
+    return e0.elapsed_time(e1) / steps
+
+
+def time_e2e(torch, ls: LayerSet, device, steps, warmup):
+    """Public API per layer with host buffers: q from pinned memory, output back to pinned memory."""
+    from phasekv_b200.kernels.attention_triton import fused_phasekv_decode
+    s = ls.shape
+    q_host = [q.cpu().pin_memory() for q in ls.q]
+    o_host = [torch.empty_like(q).pin_memory() for q in q_host]
+    q_dev = [torch.empty_like(q) for q in ls.q]
+
+    def step():
+        for i in range(ls.layers):
+            q_dev[i].copy_(q_host[i], non_blocking=True)
+            o = fused_phasekv_decode(q_dev[i], ls.tiers[i], s.num_q_heads)
+            o_host[i].copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    e1.synchronize()
+    per_step_bytes = ls.layers * s.num_q_heads * s.head_dim * 2
+    return e0.elapsed_time(e1) / steps, per_step_bytes, per_step_bytes, o_host
+
+
+def sdpa_baselines(torch, device, prompt_len, layers, steps, warmup):
+    """FP16 scaled_dot_product_attention over the same logical context on the same GPU:
+    (i) K/V expanded to the 28 query heads as the reference's micro-benchmark does
+    (scripts/bench_decode_kernel.py:75-78) and (ii) GQA-aware, reading each KV head once."""
+    import torch.nn.functional as F
+    from phasekv_b200 import workloads
+    s = workloads.QWEN2_5_7B
+    S = prompt_len + COLD_LEN + HOT_LEN
+    G = s.num_q_heads // s.num_kv_heads
+    gen = torch.Generator(device=device).manual_seed(77)
+    K = [torch.randn(1, s.num_kv_heads, S, s.head_dim, generator=gen, device=device).half() for _ in range(layers)]
+    V = [torch.randn(1, s.num_kv_heads, S, s.head_dim, generator=gen, device=device).half() for _ in range(layers)]
+    q = torch.randn(1, s.num_q_heads, 1, s.head_dim, generator=gen, device=device).half()
+    qg = q.view(1, s.num_kv_heads, G, s.head_dim)
+
+    def gqa():
+        for k, v in zip(K, V):
+            F.scaled_dot_product_attention(qg, k, v)
+    res = {"gqa_aware_ms_per_step": time_graph(torch, gqa, steps, warmup)}
+    if S * layers * s.num_q_heads * s.head_dim * 4 < 40e9:
+        Ke = [k.repeat_interleave(G, 1) for k in K]
+        Ve = [v.repeat_interleave(G, 1) for v in V]
+
+        def expanded():
+            for k, v in zip(Ke, Ve):
+                F.scaled_dot_product_attention(q, k, v)
+        res["expanded_ms_per_step"] = time_graph(torch, expanded, steps, warmup)
+    res["fp16_kv_bytes_per_layer"] = S * s.num_kv_heads * s.head_dim * 4
+    return res
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_layer_inputs(prompt_len, seed=0):
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import pkv_oracle as oracle
+    from phasekv_b200 import workloads
+    s = workloads.QWEN2_5_7B
+    (pk, pv), (ck, cv), (hk, hv), q = workloads.three_tier_dense(seed, s, prompt_len, COLD_LEN, HOT_LEN)
+    segs = [(oracle.quantize_pack(pk, PROMPT_BITS, -2, GROUP), oracle.quantize_pack(pv, PROMPT_BITS, -1, GROUP)),
+            (oracle.quantize_pack(ck, COLD_BITS, -2, GROUP), oracle.quantize_pack(cv, COLD_BITS, -1, GROUP))]
+    return oracle, s, segs, hk, hv, q[0, :, 0, :]
+
+
+def time_cpu_layers(prompt_len, layers_per_step, steps, warmup):
+    """Seconds per step of the CPU dequantise-then-attend for `layers_per_step` layers."""
+    oracle, s, segs, hk, hv, q = cpu_layer_inputs(prompt_len)
+    def step():
+        for _ in range(layers_per_step):
+            oracle.segments_decode_reference(q, segs, hk, hv, s.num_q_heads)
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    return (time.perf_counter() - t0) / steps, oracle.num_threads()
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from phasekv_b200 import workloads
+    bytes_per_layer = workloads.decode_algorithmic_bytes(workloads.QWEN2_5_7B, args.prompt, PROMPT_BITS, COLD_LEN,
+                                                         COLD_BITS, HOT_LEN, GROUP, GROUP)
+    steps, warmup = min(args.steps, 20), min(max(args.warmup, 1), 3)
+    sec, cores = time_cpu_layers(args.prompt, 1, steps, warmup)
+    value = bytes_per_layer / sec / 1e9
+    sample = f"1 of {args.layers} layers per step (dequantise-then-attend of one layer at {args.prompt} prompt tokens)"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(args):
+    return {"workload": f"qwen2.5-7b decode attention, {args.layers} layers x ({args.prompt} prompt tok @2-bit KIVI + "
+                        f"{COLD_LEN} cold tok @4-bit + {HOT_LEN} hot tok fp16), batch 1 per GPU, 28q/4kv heads, hd 128, gs 32",
+            "prompt_tokens": args.prompt, "layers": args.layers, "l2_policy": "inputs larger than L2 (distinct KV per layer)",
+            "parallelism": "batch-sharded, no collective"}
+
+
+# ----------------------------------------------------------------------------- main arm
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: phasekv_b200 has no CPU path")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    barrier = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        barrier = lambda: (dist.barrier(), torch.cuda.synchronize())  # noqa: E731
+
+    ls = LayerSet(torch, device, args.prompt, args.layers, seed=1234 + rank)
+    native = NativeStep(torch, ls, device)
+    torch.cuda.synchronize()
+
+    clocks = ClockSampler(local_rank)
+    ms = time_graph(torch, native.run, args.steps, max(args.warmup, 3), barrier, sampler=clocks)
+    ms_e2e, h2d, d2h, o_host = time_e2e(torch, ls, device, max(3, min(args.steps, 20)), 3)
+
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+
+    step_bytes = ls.bytes_per_layer * ls.layers * world
+    value = step_bytes / (ms * 1e-3) / 1e9
+    e2e_value = step_bytes / (ms_e2e * 1e-3) / 1e9
+    peak, peak_kind = measured_peak()
+    per_launch_ms = ms / ls.layers
+    achieved = ls.bytes_per_layer / (per_launch_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 codes x f16, f32 accumulate", "data": "synthetic",
+        "config": workload_config(args),
+        "us_per_layer": per_launch_ms * 1e3,
+        "pct_of_8TBps": 100.0 * achieved / 8000.0,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ms_e2e},
+        "gpu_launches": native.launches_per_step * args.steps,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": f"of {peak_kind}",
+                     "kernel": "split-K decode + merge, per layer", "algorithmic_bytes_per_launch": ls.bytes_per_layer},
+        "clocks": clocks.summary(),
+    }
+
+    if rank == 0 and world == 1 and not args.no_extras:
+        # parity spot check of the timed configuration against the CPU oracle (layer built from CPU bits)
+        oracle, s, segs, hk, hv, q = cpu_layer_inputs(args.prompt)
+        from phasekv_b200.kernels.attention_triton import fused_phasekv_decode
+        from phasekv_b200.kernels.packing import PackedTensor
+        from phasekv_b200.kernels.tiers import LayerTiers, PackedKVSegment
+
+        def gpu(pt):
+            return PackedTensor(pt.packed.to(device), pt.scale.to(device), pt.mins.to(device), pt.bits, pt.axis,
+                                pt.group_size, pt.orig_shape, pt.axis_len)
+        tiers = LayerTiers(prompt=PackedKVSegment(gpu(segs[0][0]), gpu(segs[0][1])),
+                           cold=[PackedKVSegment(gpu(segs[1][0]), gpu(segs[1][1]))],
+                           hot_k=hk.to(device), hot_v=hv.to(device), hot_len=HOT_LEN)
+        out = fused_phasekv_decode(q.to(device), tiers, s.num_q_heads).float().cpu()
+        t0 = time.perf_counter()
+        ref = oracle.segments_decode_reference(q, segs, hk, hv, s.num_q_heads).float()
+        line["parity"] = {"max_abs_err_vs_oracle": float((out - ref).abs().max()), "max_abs_ref": float(ref.abs().max())}
+        # CPU baseline on a bounded sample
+        n_cpu = 8
+        sec, cores = time_cpu_layers(args.prompt, 1, n_cpu, 1)
+        line["cpu_baseline"] = {"value": ls.bytes_per_layer / sec / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": f"{n_cpu} single-layer calls of the CPU dequantise-then-attend at {args.prompt} prompt tokens",
+                                "ms_per_layer": sec * 1e3}
+        # FP16 SDPA on the same GPU
+        del native, ls
+        torch.cuda.empty_cache()
+        sd = sdpa_baselines(torch, device, args.prompt, args.layers, 20, 3)
+        sd["speedup_vs_gqa_aware"] = sd["gqa_aware_ms_per_step"] / ms
+        if "expanded_ms_per_step" in sd:
+            sd["speedup_vs_expanded"] = sd["expanded_ms_per_step"] / ms
+        line["sdpa_fp16"] = sd
+        # context sweep 4K .. 128K
+        sweep = {}
+        for S in (4096, 8192, 16384, 32768, 131072):
+            if S == args.prompt:
+                sweep[str(S)] = {"us_per_layer": per_launch_ms * 1e3, "GBps": achieved, "frac_of_peak": achieved / peak}
+                continue
+            l2 = LayerSet(torch, device, S, args.layers, seed=99 + S)
+            n2 = NativeStep(torch, l2, device)
+            m2 = time_graph(torch, n2.run, 20, 3)
+            a2 = l2.bytes_per_layer / (m2 / l2.layers * 1e-3) / 1e9
+            sweep[str(S)] = {"us_per_layer": m2 / l2.layers * 1e3, "GBps": a2, "frac_of_peak": a2 / peak,
+                             "kv_bytes_resident": l2.kv_bytes_resident}
+            del l2, n2
+            torch.cuda.empty_cache()
+        line["contexts"] = sweep
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

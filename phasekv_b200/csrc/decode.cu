@@ -10,6 +10,7 @@
 
 #include "common.cuh"
 #include "decode_plan.h"
+#include "decode_mma.cuh"
 
 namespace pkv {
 namespace {
@@ -282,17 +283,24 @@ int check_segments(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int h
 
 DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int hd, int sm_count) {
     DecodePlan plan;
-    plan.segs.resize(n_segs);
     const int G = Hq / Hkv;
     const int head_chunks = (G + GMAX - 1) / GMAX;
-    long long total_tokens = 0;
-    for (int i = 0; i < n_segs; ++i) total_tokens += segs[i].seq_len;
-    // about four CTAs per SM over the whole layer
-    const long long target = std::max<long long>(1, (4LL * std::max(sm_count, 1)) / ((long long)Hkv * head_chunks));
-    int work = 0;
+    sm_count = std::max(sm_count, 1);
+    long long generic_tokens = 0;
+    double fast_cost = 0.0;
+    std::vector<char> is_fast(n_segs);
+    for (int i = 0; i < n_segs; ++i) {
+        is_fast[i] = mma::eligible(segs[i], Hq, Hkv, hd);
+        if (is_fast[i]) fast_cost += (double)segs[i].seq_len * segs[i].k_bits;
+        else generic_tokens += segs[i].seq_len;
+    }
+    // generic kernel: about four CTAs per SM over its share of the layer
+    const long long target = std::max<long long>(1, (4LL * sm_count) / ((long long)Hkv * head_chunks));
+    // tensor-core kernel: one CTA per SM (it owns the SM's shared memory), one wave
+    const double fast_ctas_per_head = std::max(1.0, (double)sm_count / Hkv);
     for (int i = 0; i < n_segs; ++i) {
         const pkv_segment_t& s = segs[i];
-        SegDev& d = plan.segs[i];
+        SegDev d;
         d.kp = static_cast<const uint8_t*>(s.k_packed);
         d.ks = static_cast<const __half*>(s.k_scale);
         d.km = static_cast<const __half*>(s.k_mins);
@@ -306,22 +314,35 @@ DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, i
         d.vbits = s.kind == PKV_SEG_FP16 ? 8 : s.v_bits;
         d.kgs = s.kind == PKV_SEG_FP16 ? 1 : s.k_group;
         d.vgs = s.kind == PKV_SEG_FP16 ? 1 : s.v_group;
-        long long split_len;
-        if (s.num_splits > 0) {
-            // plan_kivi_decode's manual convention (launch_config.py:58-60)
-            split_len = ceil_div(s.seq_len, std::min<long long>(s.seq_len, s.num_splits));
+        if (is_fast[i]) {
+            const long long tiles = s.seq_len / mma::tile_tokens(s.k_bits);
+            long long ctas;
+            if (s.num_splits > 0) {
+                ctas = std::min<long long>(tiles, s.num_splits);
+            } else {
+                ctas = (long long)(fast_ctas_per_head * ((double)s.seq_len * s.k_bits) / fast_cost);
+                ctas = std::max<long long>(1, std::min(ctas, tiles));
+            }
+            d.split_len = ceil_div(tiles, ctas);
+            d.n_splits = (int)ceil_div(tiles, d.split_len);
+            d.work_begin = plan.fast_work;
+            plan.fast_work += d.n_splits;
+            plan.fast.push_back(d);
         } else {
-            long long share = (target * s.seq_len + total_tokens / 2) / total_tokens;
-            share = std::max<long long>(1, share);
-            split_len = ceil_div(ceil_div(s.seq_len, share), kChunk) * kChunk;
+            if (s.num_splits > 0) {
+                // plan_kivi_decode's manual convention (launch_config.py:58-60 of the reference)
+                d.split_len = ceil_div(s.seq_len, std::min<long long>(s.seq_len, s.num_splits));
+            } else {
+                long long share = (target * s.seq_len + generic_tokens / 2) / generic_tokens;
+                share = std::max<long long>(1, share);
+                d.split_len = ceil_div(ceil_div(s.seq_len, share), kChunk) * kChunk;
+            }
+            d.n_splits = (int)ceil_div(s.seq_len, d.split_len);
+            d.work_begin = plan.generic_work;
+            plan.generic_work += d.n_splits;
+            plan.generic.push_back(d);
         }
-        d.split_len = split_len;
-        d.n_splits = (int)ceil_div(s.seq_len, split_len);
-        d.work_begin = work;
-        work += d.n_splits;
     }
-    plan.total_work = work;
-    (void)hd;
     return plan;
 }
 
@@ -337,7 +358,7 @@ int pkv_decode_workspace_bytes(const pkv_segment_t* segs, int n_segs, int num_q_
     const int rc = check_segments(segs, n_segs, num_q_heads, num_kv_heads, head_dim);
     if (rc != PKV_OK) return rc;
     const DecodePlan plan = plan_decode(segs, n_segs, num_q_heads, num_kv_heads, head_dim, sm_count);
-    *bytes = (size_t)plan.total_work * num_q_heads * (head_dim + 2) * sizeof(float);
+    *bytes = (size_t)plan.total_work() * num_q_heads * (head_dim + 2) * sizeof(float);
     return PKV_OK;
 }
 
@@ -350,17 +371,41 @@ int pkv_decode_attention(const void* q, const pkv_segment_t* segs, int n_segs, i
     if (!q || !workspace) return PKV_E_NULL;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const DecodePlan plan = plan_decode(segs, n_segs, num_q_heads, num_kv_heads, head_dim, sm_count);
-    const size_t W = (size_t)plan.total_work;
+    const size_t W = (size_t)plan.total_work();
     const size_t need = W * num_q_heads * (head_dim + 2) * sizeof(float);
     if (workspace_bytes < need) return PKV_E_WORKSPACE;
     float* pm = static_cast<float*>(workspace);
     float* pl = pm + W * num_q_heads;
     float* pacc = pl + W * num_q_heads;
-
     const int G = num_q_heads / num_kv_heads;
+
+    // tensor-core kernel over the aligned KIVI segments
+    for (size_t first = 0; first < plan.fast.size(); first += kMaxInlineSegs) {
+        const int cnt = (int)std::min<size_t>(kMaxInlineSegs, plan.fast.size() - first);
+        mma::MmaArgs a;
+        a.q = static_cast<const __half*>(q);
+        a.pm = pm;
+        a.pl = pl;
+        a.pacc = pacc;
+        a.Hq = num_q_heads;
+        a.Hkv = num_kv_heads;
+        a.G = G;
+        a.sm_scale = sm_scale;
+        a.n_segs = cnt;
+        a.work_offset = plan.fast[first].work_begin;
+        int launch_work = 0;
+        for (int i = 0; i < cnt; ++i) {
+            a.segs[i] = plan.fast[first + i];
+            a.segs[i].work_begin -= a.work_offset;
+            launch_work += a.segs[i].n_splits;
+        }
+        const int rc2 = mma::launch(a, launch_work, num_kv_heads, s);
+        if (rc2 != PKV_OK) return rc2;
+    }
+    // layout-generic kernel over everything else (float16 hot tier, per-token layout, ragged shapes)
     const size_t smem = sizeof(float) * ((size_t)GMAX * head_dim + (size_t)GMAX * kChunk + 3 * GMAX);
-    for (int first = 0; first < n_segs; first += kMaxInlineSegs) {
-        const int cnt = std::min(kMaxInlineSegs, n_segs - first);
+    for (size_t first = 0; first < plan.generic.size(); first += kMaxInlineSegs) {
+        const int cnt = (int)std::min<size_t>(kMaxInlineSegs, plan.generic.size() - first);
         DecodeArgs a;
         a.q = static_cast<const __half*>(q);
         a.pm = pm;
@@ -372,11 +417,11 @@ int pkv_decode_attention(const void* q, const pkv_segment_t* segs, int n_segs, i
         a.G = G;
         a.sm_scale = sm_scale;
         a.n_segs = cnt;
-        a.work_offset = plan.segs[first].work_begin;
+        a.work_offset = plan.fast_work + plan.generic[first].work_begin;
         int launch_work = 0;
         for (int i = 0; i < cnt; ++i) {
-            a.segs[i] = plan.segs[first + i];
-            a.segs[i].work_begin -= a.work_offset;
+            a.segs[i] = plan.generic[first + i];
+            a.segs[i].work_begin -= plan.generic[first].work_begin;
             launch_work += a.segs[i].n_splits;
         }
         dim3 grid((unsigned)launch_work, (unsigned)num_kv_heads, (unsigned)((G + GMAX - 1) / GMAX));

@@ -1,0 +1,345 @@
+// Tensor-core split-K decode kernel for KIVI-packed segments; see decode_mma.cuh for the scheme.
+#include <math.h>
+
+#include "decode_mma.cuh"
+
+namespace pkv {
+namespace mma {
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct WarpState {
+    float m[2];        // running max (log2 domain) of heads 2t, 2t+1
+    float l[2];        // this lane's share of the running sum of exp
+    float o[4][2][4];  // out accumulators: [dim group][M-tile][C fragment]
+    float pm[4];       // sum_n p * v_zero, rows = dim groups (lanes g < 4)
+};
+
+// ---- cp.async of one tile into a stage, with the shared-memory layouts the compute loop wants:
+//   key codes   [word of the row][channel]          (transposed: a lane reads 4 channels in 16 B)
+//   key scale   [group pair][channel]  (same for zeros)
+//   value codes [token (swizzled)][word-in-group][dim group]
+//   value scale [token][4]             (same for zeros)
+template <int BITS>
+__device__ __forceinline__ void issue_tile(const SegDev& sg, int kvh, long long tile, unsigned sa, int lane) {
+    using C = Cfg<BITS>;
+    const long long S = sg.S;
+    const long long nbK = S * BITS / 8, ngK = S / 32;
+    const uint8_t* kp = sg.kp + (size_t)kvh * HD * nbK + tile * (C::T * BITS / 8);
+#pragma unroll 4
+    for (int it = 0; it < HD * C::KWPR / 32; ++it) {
+        const int idx = it * 32 + lane, c = idx / C::KWPR, w = idx % C::KWPR;
+        cp_async4(sa + 4 * (C::OFF_KC + w * C::KC_STRIDE + c), kp + (size_t)c * nbK + 4 * w);
+    }
+    const __half* ks = sg.ks + (size_t)kvh * HD * ngK + tile * C::NG;
+    const __half* km = sg.km + (size_t)kvh * HD * ngK + tile * C::NG;
+#pragma unroll
+    for (int it = 0; it < HD * C::KS_PAIRS / 32; ++it) {
+        const int idx = it * 32 + lane, c = idx / C::KS_PAIRS, pr = idx % C::KS_PAIRS;
+        cp_async4(sa + 4 * (C::OFF_KS + pr * C::KS_STRIDE + c), ks + (size_t)c * ngK + 2 * pr);
+        cp_async4(sa + 4 * (C::OFF_KM + pr * C::KS_STRIDE + c), km + (size_t)c * ngK + 2 * pr);
+    }
+    const uint8_t* vp = sg.vp + ((size_t)kvh * S + tile * C::T) * (C::VWPT * 4);
+#pragma unroll 4
+    for (int it = 0; it < C::T * C::VWPT / 32; ++it) {
+        const int idx = it * 32 + lane, tok = idx / C::VWPT, nw = idx % C::VWPT;
+        const int ptok = tok ^ ((tok >> 3) & (C::VROWS_PER_128B - 1));
+        cp_async4(sa + 4 * (C::OFF_VC + ptok * C::VWPT + (nw % BITS) * 4 + nw / BITS), vp + 4 * (size_t)idx);
+    }
+    const char* vs = reinterpret_cast<const char*>(sg.vs + ((size_t)kvh * S + tile * C::T) * 4);
+    const char* vm = reinterpret_cast<const char*>(sg.vm + ((size_t)kvh * S + tile * C::T) * 4);
+#pragma unroll
+    for (int it = 0; it < C::T / 64; ++it) {
+        const int idx = it * 32 + lane;
+        cp_async16(sa + 4 * C::OFF_VS + 16 * idx, vs + 16 * idx);
+        cp_async16(sa + 4 * C::OFF_VM + 16 * idx, vm + 16 * idx);
+    }
+    cp_async_commit();
+}
+
+template <int BITS>
+__device__ __forceinline__ void compute_tile(unsigned sa, const unsigned (&qf)[8][2], float c_qk,
+                                             WarpState& st, const LaneSel<BITS>& ls, int lane) {
+    using C = Cfg<BITS>;
+    const int g = lane >> 2, t = lane & 3;
+    const unsigned sel_lo = 0x5410u, sel_hi = 0x7632u;
+
+    // ---------------- scores: S^T tile-by-tile, M = 16 tokens, N = 8 heads, K = channels
+    float sacc[C::NG * 2][4];
+#pragma unroll
+    for (int i = 0; i < C::NG * 2; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
+    float bacc[4] = {0.f, 0.f, 0.f, 0.f};
+    const int mpr = min(g >> 1, C::KS_PAIRS - 1);
+    const unsigned msel = (g & 1) ? sel_hi : sel_lo;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+        const int chan = 16 * kk + 4 * t;
+        {   // sum_d q[h,d] * zero[d,G]: rows = groups of the tile (lanes g < NG carry data)
+            const uint4 mr = lds128(sa + 4 * (C::OFF_KM + mpr * C::KS_STRIDE + chan));
+            unsigned a0 = prmt(mr.x, mr.y, msel), a2 = prmt(mr.z, mr.w, msel);
+            if (g >= C::NG) a0 = a2 = 0u;
+            mma16816(bacc, a0, 0u, a2, 0u, qf[kk][0], qf[kk][1]);
+        }
+#pragma unroll
+        for (int pr = 0; pr < C::KS_PAIRS; ++pr) {
+            const uint4 sr = lds128(sa + 4 * (C::OFF_KS + pr * C::KS_STRIDE + chan));
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int G = 2 * pr + e;
+                const unsigned sel = e ? sel_hi : sel_lo;
+                const unsigned b0 = hmul2(qf[kk][0], prmt(sr.x, sr.y, sel));
+                const unsigned b1 = hmul2(qf[kk][1], prmt(sr.z, sr.w, sel));
+                const uint4 kc = lds128(sa + 4 * (C::OFF_KC + (G * BITS + ls.word) * C::KC_STRIDE + chan));
+                unsigned ra[4], rb[4];
+                extract4<BITS>(kc.x, kc.y, ls, ra);
+                extract4<BITS>(kc.z, kc.w, ls, rb);
+                mma16816(sacc[2 * G + 0], ra[0], ra[1], rb[0], rb[1], b0, b1);
+                mma16816(sacc[2 * G + 1], ra[2], ra[3], rb[2], rb[3], b0, b1);
+            }
+        }
+    }
+
+    // ---------------- online softmax in the log2 domain
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int G = 0; G < C::NG; ++G) {
+        const float bias0 = __shfl_sync(0xffffffffu, bacc[0], 4 * G + t);
+        const float bias1 = __shfl_sync(0xffffffffu, bacc[1], 4 * G + t);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            float* s = sacc[2 * G + j];
+            s[0] = (s[0] * unscale<BITS>(2 * j) + bias0) * c_qk;
+            s[1] = (s[1] * unscale<BITS>(2 * j) + bias1) * c_qk;
+            s[2] = (s[2] * unscale<BITS>(2 * j + 1) + bias0) * c_qk;
+            s[3] = (s[3] * unscale<BITS>(2 * j + 1) + bias1) * c_qk;
+            mx[0] = fmaxf(mx[0], fmaxf(s[0], s[2]));
+            mx[1] = fmaxf(mx[1], fmaxf(s[1], s[3]));
+        }
+    }
+#pragma unroll
+    for (int o = 4; o <= 16; o <<= 1) {
+        mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+        mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
+    }
+    const float m0 = fmaxf(st.m[0], mx[0]), m1 = fmaxf(st.m[1], mx[1]);
+    const float al0 = ex2(st.m[0] - m0), al1 = ex2(st.m[1] - m1);  // first tile: ex2(-inf) = 0
+    st.m[0] = m0;
+    st.m[1] = m1;
+    float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < C::NG * 2; ++i) {
+        sacc[i][0] = ex2(sacc[i][0] - m0);
+        sacc[i][1] = ex2(sacc[i][1] - m1);
+        sacc[i][2] = ex2(sacc[i][2] - m0);
+        sacc[i][3] = ex2(sacc[i][3] - m1);
+        ls0 += sacc[i][0] + sacc[i][2];
+        ls1 += sacc[i][1] + sacc[i][3];
+    }
+    st.l[0] = st.l[0] * al0 + ls0;
+    st.l[1] = st.l[1] * al1 + ls1;
+#pragma unroll
+    for (int d = 0; d < 4; ++d)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            st.o[d][j][0] *= al0;
+            st.o[d][j][1] *= al1;
+            st.o[d][j][2] *= al0;
+            st.o[d][j][3] *= al1;
+        }
+    st.pm[0] *= al0;
+    st.pm[1] *= al1;
+    st.pm[2] *= al0;
+    st.pm[3] *= al1;
+
+    // ---------------- out^T += V^T P: M = 16 dims, N = 8 heads, K = the 16 tokens of one score tile
+    const unsigned vsel = (g & 1) ? sel_hi : sel_lo;
+#pragma unroll
+    for (int G = 0; G < C::NG; ++G) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float* p = sacc[2 * G + j];
+            const unsigned pb0 = movmatrix_trans(pack_half2(p[0], p[1]));  // tokens of rows 2t, 2t+1; head g
+            const unsigned pb1 = movmatrix_trans(pack_half2(p[2], p[3]));  // tokens of rows 2t+8, 2t+9
+            int tok[4];
+            tok[0] = 32 * G + 8 * t + 2 * j;
+            tok[1] = tok[0] + 4;
+            tok[2] = tok[0] + 1;
+            tok[3] = tok[1] + 1;
+            uint2 vs[4], vm[4];
+            unsigned vw[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                vs[i] = lds64(sa + 4 * (C::OFF_VS + tok[i] * 2));
+                vm[i] = lds64(sa + 4 * (C::OFF_VM + tok[i] * 2));
+                const int ptok = tok[i] ^ ((tok[i] >> 3) & (C::VROWS_PER_128B - 1));
+                const uint4 w4 = lds128(sa + 4 * (C::OFF_VC + ptok * C::VWPT + 4 * ls.word));
+                vw[i][0] = w4.x;
+                vw[i][1] = w4.y;
+                vw[i][2] = w4.z;
+                vw[i][3] = w4.w;
+            }
+            {   // sum_n p[h,n] * zero[n,D]: rows = dim groups (lanes g < 4 carry data)
+                unsigned a0 = prmt((g & 2) ? vm[0].y : vm[0].x, (g & 2) ? vm[1].y : vm[1].x, vsel);
+                unsigned a2 = prmt((g & 2) ? vm[2].y : vm[2].x, (g & 2) ? vm[3].y : vm[3].x, vsel);
+                if (g >= 4) a0 = a2 = 0u;
+                mma16816(st.pm, a0, 0u, a2, 0u, pb0, pb1);
+            }
+#pragma unroll
+            for (int d = 0; d < 4; ++d) {
+                const unsigned sel = (d & 1) ? sel_hi : sel_lo;
+                const unsigned s01 = prmt((d & 2) ? vs[0].y : vs[0].x, (d & 2) ? vs[1].y : vs[1].x, sel);
+                const unsigned s23 = prmt((d & 2) ? vs[2].y : vs[2].x, (d & 2) ? vs[3].y : vs[3].x, sel);
+                const unsigned b0 = hmul2(pb0, s01), b1 = hmul2(pb1, s23);
+                unsigned ra[4], rb[4];
+                extract4<BITS>(vw[0][d], vw[1][d], ls, ra);
+                extract4<BITS>(vw[2][d], vw[3][d], ls, rb);
+                mma16816(st.o[d][0], ra[0], ra[1], rb[0], rb[1], b0, b1);
+                mma16816(st.o[d][1], ra[2], ra[3], rb[2], rb[3], b0, b1);
+            }
+        }
+    }
+}
+
+template <int BITS>
+__device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int split, int kvh, float* smem_f) {
+    using C = Cfg<BITS>;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const unsigned smem_base = (unsigned)__cvta_generic_to_shared(smem_f);
+    const long long n_tiles = sg.S / C::T;
+    const long long tile0 = (long long)split * sg.split_len;
+    const long long tile1 = min(n_tiles, tile0 + sg.split_len);
+    const int h0 = kvh * a.G;
+
+    WarpState st;
+    st.m[0] = st.m[1] = -INFINITY;
+    st.l[0] = st.l[1] = 0.f;
+#pragma unroll
+    for (int d = 0; d < 4; ++d)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) st.o[d][j][0] = st.o[d][j][1] = st.o[d][j][2] = st.o[d][j][3] = 0.f;
+    st.pm[0] = st.pm[1] = st.pm[2] = st.pm[3] = 0.f;
+
+    if (wid < C::ACTIVE_WARPS) {
+        // q as the B operand: lane (g, t) holds head g, channels 16k + 4t .. +3
+        unsigned qf[8][2];
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+            uint2 v = make_uint2(0u, 0u);
+            if (g < a.G) v = *reinterpret_cast<const uint2*>(a.q + (size_t)(h0 + g) * HD + 16 * kk + 4 * t);
+            qf[kk][0] = v.x;
+            qf[kk][1] = v.y;
+        }
+        const LaneSel<BITS> ls(g);
+        const float c_qk = a.sm_scale * kLog2e;
+        const unsigned ring = smem_base + wid * (NSTAGE * C::STAGE_WORDS * 4);
+        const long long first = tile0 + wid;
+        const int n_my = first < tile1 ? (int)((tile1 - first + C::ACTIVE_WARPS - 1) / C::ACTIVE_WARPS) : 0;
+        if (n_my > 0) issue_tile<BITS>(sg, kvh, first, ring, lane);
+        if (n_my > 1) issue_tile<BITS>(sg, kvh, first + C::ACTIVE_WARPS, ring + C::STAGE_WORDS * 4, lane);
+        for (int i = 0; i < n_my; ++i) {
+            if (i + 1 < n_my) cp_async_wait<1>(); else cp_async_wait<0>();
+            __syncwarp();
+            compute_tile<BITS>(ring + (i & 1) * C::STAGE_WORDS * 4, qf, c_qk, st, ls, lane);
+            __syncwarp();
+            if (i + 2 < n_my)
+                issue_tile<BITS>(sg, kvh, first + (long long)(i + 2) * C::ACTIVE_WARPS,
+                                 ring + (i & 1) * C::STAGE_WORDS * 4, lane);
+        }
+    }
+
+    // ---------------- per-warp epilogue: undo the power-of-two code scaling, add the zero terms
+#pragma unroll
+    for (int o = 4; o <= 16; o <<= 1) {
+        st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], o);
+        st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], o);
+    }
+    __syncthreads();  // every ring is idle: reuse shared memory for the cross-warp merge
+    float* o_s = smem_f + wid * (8 * HD + 16);  // [head 8][dim 128], then m[8], l[8]
+#pragma unroll
+    for (int d = 0; d < 4; ++d) {
+        const float z0 = __shfl_sync(0xffffffffu, st.pm[0], 4 * d + t);
+        const float z1 = __shfl_sync(0xffffffffu, st.pm[1], 4 * d + t);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int dim = 32 * d + 4 * g + 2 * j;
+            o_s[(2 * t) * HD + dim] = st.o[d][j][0] * unscale<BITS>(2 * j) + z0;
+            o_s[(2 * t + 1) * HD + dim] = st.o[d][j][1] * unscale<BITS>(2 * j) + z1;
+            o_s[(2 * t) * HD + dim + 1] = st.o[d][j][2] * unscale<BITS>(2 * j + 1) + z0;
+            o_s[(2 * t + 1) * HD + dim + 1] = st.o[d][j][3] * unscale<BITS>(2 * j + 1) + z1;
+        }
+    }
+    if (g == 0) {
+        o_s[8 * HD + 2 * t] = st.m[0];
+        o_s[8 * HD + 2 * t + 1] = st.m[1];
+        o_s[8 * HD + 8 + 2 * t] = st.l[0];
+        o_s[8 * HD + 8 + 2 * t + 1] = st.l[1];
+    }
+    __syncthreads();
+
+    // ---------------- merge the warps' states into one partial per CTA
+    const size_t widx = (size_t)a.work_offset + blockIdx.x;
+    const int dim = tid & (HD - 1), hh = tid >> 7;  // 256 threads: two head halves
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int h = hh * 4 + k;
+        if (h >= a.G) continue;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, smem_f[w * (8 * HD + 16) + 8 * HD + h]);
+        float acc = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) {
+            const float* ws = smem_f + w * (8 * HD + 16);
+            const float wgt = ex2(ws[8 * HD + h] - M);
+            acc = fmaf(wgt, ws[h * HD + dim], acc);
+            l = fmaf(wgt, ws[8 * HD + 8 + h], l);
+        }
+        a.pacc[(widx * a.Hq + h0 + h) * HD + dim] = acc;
+        if (dim == 0) {
+            a.pm[widx * a.Hq + h0 + h] = M * (1.0f / kLog2e);  // back to the natural-log domain
+            a.pl[widx * a.Hq + h0 + h] = l;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(NTHREADS, 1) decode_mma_kernel(const __grid_constant__ MmaArgs a) {
+    extern __shared__ __align__(16) float smem_f[];
+    const int w = blockIdx.x, kvh = blockIdx.y;
+    int si = 0;
+    while (si + 1 < a.n_segs && w >= a.segs[si + 1].work_begin) ++si;
+    const SegDev& sg = a.segs[si];
+    const int split = w - sg.work_begin;
+    if (sg.kbits == 2) run_cta<2>(a, sg, split, kvh, smem_f);
+    else if (sg.kbits == 4) run_cta<4>(a, sg, split, kvh, smem_f);
+    else run_cta<8>(a, sg, split, kvh, smem_f);
+}
+
+}  // namespace
+
+bool eligible(const pkv_segment_t& s, int Hq, int Hkv, int hd) {
+    if (s.kind != PKV_SEG_KIVI || hd != HD || Hq / Hkv > 8) return false;
+    if (s.k_bits != s.v_bits || s.k_group != 32 || s.v_group != 32) return false;
+    if (s.seq_len % tile_tokens(s.k_bits) != 0) return false;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(s.k_packed) | reinterpret_cast<uintptr_t>(s.k_scale) |
+                           reinterpret_cast<uintptr_t>(s.k_mins) | reinterpret_cast<uintptr_t>(s.v_packed) |
+                           reinterpret_cast<uintptr_t>(s.v_scale) | reinterpret_cast<uintptr_t>(s.v_mins);
+    return (bits & 15u) == 0;
+}
+
+int launch(const MmaArgs& a, int work, int Hkv, cudaStream_t stream) {
+    static thread_local bool configured[64] = {};
+    int dev = 0;
+    PKV_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 64 && !configured[dev]) {
+        PKV_CUDA_TRY(cudaFuncSetAttribute(decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        configured[dev] = true;
+    }
+    decode_mma_kernel<<<dim3((unsigned)work, (unsigned)Hkv), NTHREADS, kSmemBytes, stream>>>(a);
+    PKV_LAUNCH_CHECK();
+    return PKV_OK;
+}
+
+}  // namespace mma
+}  // namespace pkv

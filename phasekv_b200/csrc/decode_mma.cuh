@@ -1,0 +1,196 @@
+// Tensor-core split-K decode over KIVI-packed segments (head_dim 128, group 32, GQA group <= 8).
+//
+// Idea.  The packed codes are never converted to numbers by arithmetic.  A b-bit code c sitting at
+// bit position p (p + b <= 10) of a 16-bit lane IS the float16 subnormal c * 2^(p-24), and
+// mma.sync multiplies float16 subnormals exactly, so one AND with a mask turns two packed bytes into
+// a half2 MMA operand.  The affine dequantisation is moved onto the small operands:
+//   score(n,h) = sum_d (q[h,d] * ks[d,G]) * kc[n,d]  +  sum_d q[h,d] * km[d,G]      (G = group of n)
+//   out(h,e)   = sum_n (p[h,n] * vs[n,D]) * vc[n,e]  +  sum_n p[h,n] * vm[n,D]      (D = group of e)
+// i.e. the f16 products q*ks and p*vs are the B operands, the raw codes are the A operands, the two
+// "zero" terms are one extra MMA each, and the power of two 2^(24-p) is applied to the accumulator.
+// K is packed along tokens but contracted along channels (V the other way round); the PRMT that
+// builds the half2 from two bytes of two neighbouring channel rows (token rows) does that transpose.
+//
+// Work split: a CTA owns a token range of one (segment, KV head); its warps take tiles of the range
+// round-robin, each warp streaming its own tiles through a private 2-stage cp.async ring (no CTA
+// barrier in the loop), with a private online-softmax state that is merged through shared memory at
+// the end into ONE un-normalised partial (m, l, acc) per CTA.
+#pragma once
+
+#include "common.cuh"
+#include "decode_plan.h"
+
+namespace pkv {
+namespace mma {
+
+constexpr int HD = 128;
+constexpr int NWARPS = 8;
+constexpr int NSTAGE = 2;
+constexpr int NTHREADS = NWARPS * 32;
+
+template <int BITS>
+struct Cfg {
+    static constexpr int T = BITS == 2 ? 128 : 64;  // tokens per tile
+    static constexpr int NG = T / 32;               // key groups per tile
+    static constexpr int KWPR = T * BITS / 32;      // key code words per channel row of a tile
+    static constexpr int KC_STRIDE = HD + 4;        // words between word-rows of the transposed key tile
+    static constexpr int KC_WORDS = KWPR * KC_STRIDE;
+    static constexpr int KS_PAIRS = NG / 2;         // 32-bit words (two groups of f16) per channel
+    static constexpr int KS_STRIDE = HD + 16;
+    static constexpr int KS_WORDS = KS_PAIRS * KS_STRIDE;
+    static constexpr int VWPT = HD * BITS / 32;     // value code words per token
+    static constexpr int VC_WORDS = T * VWPT;
+    static constexpr int VS_WORDS = T * 2;          // four f16 per token
+    static constexpr int OFF_KC = 0;
+    static constexpr int OFF_KS = OFF_KC + KC_WORDS;
+    static constexpr int OFF_KM = OFF_KS + KS_WORDS;
+    static constexpr int OFF_VC = OFF_KM + KS_WORDS;
+    static constexpr int OFF_VS = OFF_VC + VC_WORDS;
+    static constexpr int OFF_VM = OFF_VS + VS_WORDS;
+    static constexpr int STAGE_WORDS = OFF_VM + VS_WORDS;
+    // warps that stream tiles (the 8-bit stage is too large for eight rings in 227 KB)
+    static constexpr int ACTIVE_WARPS = BITS == 8 ? 6 : 8;
+    static constexpr int SMEM_BYTES = STAGE_WORDS * 4 * NSTAGE * ACTIVE_WARPS;
+    static constexpr int VROWS_PER_128B = 128 / (VWPT * 4) > 0 ? 128 / (VWPT * 4) : 1;  // 4, 2, 1
+};
+
+constexpr int kMergeBytes = NWARPS * (8 * HD + 16) * 4;  // per-warp O[8][128] + m[8] + l[8]
+constexpr int kSmemBytes = 225792;  // max over bit widths (8-bit: 18816 * 2 * 6)
+static_assert(Cfg<2>::SMEM_BYTES <= kSmemBytes && Cfg<4>::SMEM_BYTES <= kSmemBytes &&
+              Cfg<8>::SMEM_BYTES <= kSmemBytes && kMergeBytes <= kSmemBytes, "shared memory budget");
+
+inline int tile_tokens(int bits) { return bits == 2 ? 128 : 64; }
+inline int active_warps(int bits) { return bits == 8 ? 6 : 8; }
+
+struct MmaArgs {
+    const __half* q;
+    float* pm;
+    float* pl;
+    float* pacc;
+    int Hq, Hkv, G;
+    float sm_scale;
+    int n_segs;
+    int work_offset;
+    SegDev segs[kMaxInlineSegs];  // split_len counts TILES here
+};
+
+// ------------------------------------------------------------------ small PTX helpers
+__device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned prmt(unsigned a, unsigned b, unsigned sel) {
+    unsigned r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
+    unsigned r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(a));
+    return r;
+}
+__device__ __forceinline__ unsigned hmul2(unsigned a, unsigned b) {
+    unsigned r;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned pack_half2(float lo, float hi) {
+    unsigned r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ float ex2(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void cp_async4(unsigned smem_addr, const void* g) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_addr), "l"(g));
+}
+__device__ __forceinline__ void cp_async16(unsigned smem_addr, const void* g) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(g));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ uint4 lds128(unsigned addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(unsigned addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
+// For lane row g: which word of a 32-element group holds its four codes, and the PRMT selectors that
+// bring the byte(s) holding them to byte 0 (from the first source) and byte 2 (from the second).
+template <int BITS>
+struct LaneSel {
+    unsigned word;    // word index inside the group
+    unsigned sel[4];  // selectors (as many as the width needs)
+    __device__ explicit LaneSel(int g) {
+        auto mk = [](unsigned k) { return k | (k << 4) | ((4u + k) << 8) | ((4u + k) << 12); };
+        if (BITS == 2) {
+            word = g >> 2;
+            sel[0] = mk(g & 3);
+            sel[1] = sel[2] = sel[3] = sel[0];
+        } else if (BITS == 4) {
+            word = g >> 1;
+            sel[0] = mk(2 * (g & 1));
+            sel[1] = mk(2 * (g & 1) + 1);
+            sel[2] = sel[3] = sel[0];
+        } else {
+            word = g;
+            for (unsigned k = 0; k < 4; ++k) sel[k] = mk(k);
+        }
+    }
+};
+
+// r[i] = half2(code_i of wa, code_i of wb) as float16 subnormals, i = 0..3 (the lane's four codes).
+// The value of r[i] is code * 2^(pos<BITS>(i) - 24).
+template <int BITS>
+__device__ __forceinline__ void extract4(unsigned wa, unsigned wb, const LaneSel<BITS>& ls, unsigned (&r)[4]) {
+    if (BITS == 2) {
+        const unsigned x = prmt(wa, wb, ls.sel[0]);
+        r[0] = x & 0x00030003u;
+        r[1] = x & 0x000C000Cu;
+        r[2] = x & 0x00300030u;
+        r[3] = x & 0x00C000C0u;
+    } else if (BITS == 4) {
+        const unsigned x0 = prmt(wa, wb, ls.sel[0]);
+        const unsigned x1 = prmt(wa, wb, ls.sel[1]);
+        r[0] = x0 & 0x000F000Fu;
+        r[1] = x0 & 0x00F000F0u;
+        r[2] = x1 & 0x000F000Fu;
+        r[3] = x1 & 0x00F000F0u;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) r[i] = prmt(wa, wb, ls.sel[i]) & 0x00FF00FFu;
+    }
+}
+// 2^(24 - bit position of code i)
+template <int BITS>
+__device__ __forceinline__ constexpr float unscale(int i) {
+    return BITS == 2 ? (i == 0 ? 16777216.f : i == 1 ? 4194304.f : i == 2 ? 1048576.f : 262144.f)
+         : BITS == 4 ? ((i & 1) ? 1048576.f : 16777216.f)
+                     : 16777216.f;
+}
+
+}  // namespace mma
+}  // namespace pkv
+
+namespace pkv {
+namespace mma {
+// Whether the tensor-core kernel can take this segment (otherwise the generic kernel does).
+bool eligible(const pkv_segment_t& s, int Hq, int Hkv, int hd);
+// Launch over `work` CTAs per KV head; a.segs[*].work_begin is relative to this launch.
+int launch(const MmaArgs& a, int work, int Hkv, cudaStream_t stream);
+}  // namespace mma
+}  // namespace pkv

@@ -27,9 +27,15 @@ struct SegDev {
     int n_splits;    // work items of this segment
 };
 
+// Segments are routed to one of two kernels: the tensor-core kernel (`fast`, split_len counts
+// tiles) or the layout-generic kernel (`generic`, split_len counts tokens).  Work items are
+// numbered fast first, generic after; work_begin is relative to the start of each list.
 struct DecodePlan {
-    std::vector<SegDev> segs;
-    int total_work = 0;
+    std::vector<SegDev> fast;
+    std::vector<SegDev> generic;
+    int fast_work = 0;
+    int generic_work = 0;
+    int total_work() const { return fast_work + generic_work; }
 };
 
 DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int hd, int sm_count);
