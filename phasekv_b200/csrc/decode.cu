@@ -281,6 +281,11 @@ int check_segments(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int h
 
 }  // namespace
 
+// bytes-proportional cost of streaming a segment
+static double seg_cost(const pkv_segment_t& s) {
+    return (double)s.seq_len * (s.kind == PKV_SEG_FP16 ? 16 : s.k_bits);
+}
+
 DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int hd, int sm_count) {
     DecodePlan plan;
     const int G = Hq / Hkv;
@@ -291,7 +296,7 @@ DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, i
     std::vector<char> is_fast(n_segs);
     for (int i = 0; i < n_segs; ++i) {
         is_fast[i] = mma::eligible(segs[i], Hq, Hkv, hd);
-        if (is_fast[i]) fast_cost += (double)segs[i].seq_len * segs[i].k_bits;
+        if (is_fast[i]) fast_cost += seg_cost(segs[i]);
         else generic_tokens += segs[i].seq_len;
     }
     // generic kernel: about four CTAs per SM over its share of the layer
@@ -315,12 +320,12 @@ DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, i
         d.kgs = s.kind == PKV_SEG_FP16 ? 1 : s.k_group;
         d.vgs = s.kind == PKV_SEG_FP16 ? 1 : s.v_group;
         if (is_fast[i]) {
-            const long long tiles = s.seq_len / mma::tile_tokens(s.k_bits);
+            const long long tiles = mma::tiles_of(s);
             long long ctas;
             if (s.num_splits > 0) {
                 ctas = std::min<long long>(tiles, s.num_splits);
             } else {
-                ctas = (long long)(fast_ctas_per_head * ((double)s.seq_len * s.k_bits) / fast_cost);
+                ctas = (long long)(fast_ctas_per_head * seg_cost(s) / fast_cost);
                 ctas = std::max<long long>(1, std::min(ctas, tiles));
             }
             d.split_len = ceil_div(tiles, ctas);

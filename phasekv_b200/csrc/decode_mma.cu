@@ -201,55 +201,13 @@ __device__ __forceinline__ void compute_tile(unsigned sa, const unsigned (&qf)[8
     }
 }
 
+// Per-warp epilogue and cross-warp merge.  BITS > 0: packed tile accumulators (undo the power-of-two
+// code scaling, add the zero terms).  BITS == 0: float16 tile accumulators (plain).
 template <int BITS>
-__device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int split, int kvh, float* smem_f) {
-    using C = Cfg<BITS>;
+__device__ __forceinline__ void finish_cta(const MmaArgs& a, WarpState& st, int kvh, float* smem_f) {
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const unsigned smem_base = (unsigned)__cvta_generic_to_shared(smem_f);
-    const long long n_tiles = sg.S / C::T;
-    const long long tile0 = (long long)split * sg.split_len;
-    const long long tile1 = min(n_tiles, tile0 + sg.split_len);
     const int h0 = kvh * a.G;
-
-    WarpState st;
-    st.m[0] = st.m[1] = -INFINITY;
-    st.l[0] = st.l[1] = 0.f;
-#pragma unroll
-    for (int d = 0; d < 4; ++d)
-#pragma unroll
-        for (int j = 0; j < 2; ++j) st.o[d][j][0] = st.o[d][j][1] = st.o[d][j][2] = st.o[d][j][3] = 0.f;
-    st.pm[0] = st.pm[1] = st.pm[2] = st.pm[3] = 0.f;
-
-    if (wid < C::ACTIVE_WARPS) {
-        // q as the B operand: lane (g, t) holds head g, channels 16k + 4t .. +3
-        unsigned qf[8][2];
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-            uint2 v = make_uint2(0u, 0u);
-            if (g < a.G) v = *reinterpret_cast<const uint2*>(a.q + (size_t)(h0 + g) * HD + 16 * kk + 4 * t);
-            qf[kk][0] = v.x;
-            qf[kk][1] = v.y;
-        }
-        const LaneSel<BITS> ls(g);
-        const float c_qk = a.sm_scale * kLog2e;
-        const unsigned ring = smem_base + wid * (NSTAGE * C::STAGE_WORDS * 4);
-        const long long first = tile0 + wid;
-        const int n_my = first < tile1 ? (int)((tile1 - first + C::ACTIVE_WARPS - 1) / C::ACTIVE_WARPS) : 0;
-        if (n_my > 0) issue_tile<BITS>(sg, kvh, first, ring, lane);
-        if (n_my > 1) issue_tile<BITS>(sg, kvh, first + C::ACTIVE_WARPS, ring + C::STAGE_WORDS * 4, lane);
-        for (int i = 0; i < n_my; ++i) {
-            if (i + 1 < n_my) cp_async_wait<1>(); else cp_async_wait<0>();
-            __syncwarp();
-            compute_tile<BITS>(ring + (i & 1) * C::STAGE_WORDS * 4, qf, c_qk, st, ls, lane);
-            __syncwarp();
-            if (i + 2 < n_my)
-                issue_tile<BITS>(sg, kvh, first + (long long)(i + 2) * C::ACTIVE_WARPS,
-                                 ring + (i & 1) * C::STAGE_WORDS * 4, lane);
-        }
-    }
-
-    // ---------------- per-warp epilogue: undo the power-of-two code scaling, add the zero terms
 #pragma unroll
     for (int o = 4; o <= 16; o <<= 1) {
         st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], o);
@@ -257,18 +215,32 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
     }
     __syncthreads();  // every ring is idle: reuse shared memory for the cross-warp merge
     float* o_s = smem_f + wid * (8 * HD + 16);  // [head 8][dim 128], then m[8], l[8]
+    if (BITS > 0) {
+        constexpr int B = BITS > 0 ? BITS : 2;
 #pragma unroll
-    for (int d = 0; d < 4; ++d) {
-        const float z0 = __shfl_sync(0xffffffffu, st.pm[0], 4 * d + t);
-        const float z1 = __shfl_sync(0xffffffffu, st.pm[1], 4 * d + t);
+        for (int d = 0; d < 4; ++d) {
+            const float z0 = __shfl_sync(0xffffffffu, st.pm[0], 4 * d + t);
+            const float z1 = __shfl_sync(0xffffffffu, st.pm[1], 4 * d + t);
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int dim = 32 * d + 4 * g + 2 * j;
-            o_s[(2 * t) * HD + dim] = st.o[d][j][0] * unscale<BITS>(2 * j) + z0;
-            o_s[(2 * t + 1) * HD + dim] = st.o[d][j][1] * unscale<BITS>(2 * j) + z1;
-            o_s[(2 * t) * HD + dim + 1] = st.o[d][j][2] * unscale<BITS>(2 * j + 1) + z0;
-            o_s[(2 * t + 1) * HD + dim + 1] = st.o[d][j][3] * unscale<BITS>(2 * j + 1) + z1;
+            for (int j = 0; j < 2; ++j) {
+                const int dim = 32 * d + 4 * g + 2 * j;
+                o_s[(2 * t) * HD + dim] = st.o[d][j][0] * unscale<B>(2 * j) + z0;
+                o_s[(2 * t + 1) * HD + dim] = st.o[d][j][1] * unscale<B>(2 * j) + z1;
+                o_s[(2 * t) * HD + dim + 1] = st.o[d][j][2] * unscale<B>(2 * j + 1) + z0;
+                o_s[(2 * t + 1) * HD + dim + 1] = st.o[d][j][3] * unscale<B>(2 * j + 1) + z1;
+            }
         }
+    } else {
+#pragma unroll
+        for (int d = 0; d < 4; ++d)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int dim = 16 * (2 * d + j) + g;
+                o_s[(2 * t) * HD + dim] = st.o[d][j][0];
+                o_s[(2 * t + 1) * HD + dim] = st.o[d][j][1];
+                o_s[(2 * t) * HD + dim + 8] = st.o[d][j][2];
+                o_s[(2 * t + 1) * HD + dim + 8] = st.o[d][j][3];
+            }
     }
     if (g == 0) {
         o_s[8 * HD + 2 * t] = st.m[0];
@@ -304,6 +276,199 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
     }
 }
 
+__device__ __forceinline__ void init_state(WarpState& st) {
+    st.m[0] = st.m[1] = -INFINITY;
+    st.l[0] = st.l[1] = 0.f;
+#pragma unroll
+    for (int d = 0; d < 4; ++d)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) st.o[d][j][0] = st.o[d][j][1] = st.o[d][j][2] = st.o[d][j][3] = 0.f;
+    st.pm[0] = st.pm[1] = st.pm[2] = st.pm[3] = 0.f;
+}
+
+// ---------------------------------------------------------------- float16 (hot tier) tiles
+// 32 tokens per tile, K and V rows padded to 272 bytes so that ldmatrix row addresses spread over
+// all banks.  Tokens past the segment end are zero-filled by cp.async and masked to -inf.
+constexpr int TH = 32;
+constexpr int HROW = HD + 8;                      // halves per padded row
+constexpr int HOT_TILE_BYTES = TH * HROW * 2;     // one of K or V
+constexpr int HOT_RING_BYTES = 2 * HOT_TILE_BYTES;
+
+__device__ __forceinline__ void cp_async16_zfill(unsigned smem_addr, const void* g, unsigned src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr), "l"(g), "r"(src_bytes));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+__device__ __forceinline__ void issue_hot_tile(const SegDev& sg, int kvh, long long tile, unsigned sa, int lane) {
+    const __half* kb = reinterpret_cast<const __half*>(sg.kp) + (size_t)kvh * sg.head_stride;
+    const __half* vb = reinterpret_cast<const __half*>(sg.vp) + (size_t)kvh * sg.head_stride;
+#pragma unroll 4
+    for (int it = 0; it < TH * 16 / 32; ++it) {
+        const int idx = it * 32 + lane, tok = idx >> 4, ch = idx & 15;
+        const long long gt = tile * TH + tok;
+        const unsigned nbytes = gt < sg.S ? 16u : 0u;
+        const size_t off = (size_t)min(gt, sg.S - 1) * HD + ch * 8;
+        cp_async16_zfill(sa + (tok * HROW + ch * 8) * 2, kb + off, nbytes);
+        cp_async16_zfill(sa + HOT_TILE_BYTES + (tok * HROW + ch * 8) * 2, vb + off, nbytes);
+    }
+    cp_async_commit();
+}
+
+__device__ __forceinline__ void compute_hot_tile(unsigned sa, const unsigned (&qh)[8][2], float c_qk, WarpState& st,
+                                                 int valid, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const int mi = lane >> 3, mr = lane & 7;  // ldmatrix: this lane addresses row mr of matrix mi
+    float sacc[2][4];
+#pragma unroll
+    for (int m = 0; m < 2; ++m) sacc[m][0] = sacc[m][1] = sacc[m][2] = sacc[m][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk)
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            unsigned a0, a1, a2, a3;
+            ldmatrix_x4(sa + ((16 * m + (mi & 1) * 8 + mr) * HROW + 16 * kk + (mi >> 1) * 8) * 2, a0, a1, a2, a3);
+            mma16816(sacc[m], a0, a1, a2, a3, qh[kk][0], qh[kk][1]);
+        }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        const bool v0 = 16 * m + g < valid, v1 = 16 * m + g + 8 < valid;
+        sacc[m][0] = v0 ? sacc[m][0] * c_qk : -INFINITY;
+        sacc[m][1] = v0 ? sacc[m][1] * c_qk : -INFINITY;
+        sacc[m][2] = v1 ? sacc[m][2] * c_qk : -INFINITY;
+        sacc[m][3] = v1 ? sacc[m][3] * c_qk : -INFINITY;
+        mx[0] = fmaxf(mx[0], fmaxf(sacc[m][0], sacc[m][2]));
+        mx[1] = fmaxf(mx[1], fmaxf(sacc[m][1], sacc[m][3]));
+    }
+#pragma unroll
+    for (int o = 4; o <= 16; o <<= 1) {
+        mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+        mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
+    }
+    const float m0 = fmaxf(st.m[0], mx[0]), m1 = fmaxf(st.m[1], mx[1]);
+    const float al0 = ex2(st.m[0] - m0), al1 = ex2(st.m[1] - m1);
+    st.m[0] = m0;
+    st.m[1] = m1;
+    float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        sacc[m][0] = ex2(sacc[m][0] - m0);
+        sacc[m][1] = ex2(sacc[m][1] - m1);
+        sacc[m][2] = ex2(sacc[m][2] - m0);
+        sacc[m][3] = ex2(sacc[m][3] - m1);
+        ls0 += sacc[m][0] + sacc[m][2];
+        ls1 += sacc[m][1] + sacc[m][3];
+    }
+    st.l[0] = st.l[0] * al0 + ls0;
+    st.l[1] = st.l[1] * al1 + ls1;
+#pragma unroll
+    for (int d = 0; d < 4; ++d)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            st.o[d][j][0] *= al0;
+            st.o[d][j][1] *= al1;
+            st.o[d][j][2] *= al0;
+            st.o[d][j][3] *= al1;
+        }
+    const unsigned va = sa + HOT_TILE_BYTES;
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        const unsigned pb0 = movmatrix_trans(pack_half2(sacc[m][0], sacc[m][1]));
+        const unsigned pb1 = movmatrix_trans(pack_half2(sacc[m][2], sacc[m][3]));
+#pragma unroll
+        for (int dt = 0; dt < 8; ++dt) {
+            unsigned a0, a1, a2, a3;
+            ldmatrix_x4_trans(va + ((16 * m + (mi >> 1) * 8 + mr) * HROW + 16 * dt + (mi & 1) * 8) * 2, a0, a1, a2, a3);
+            mma16816(st.o[dt >> 1][dt & 1], a0, a1, a2, a3, pb0, pb1);
+        }
+    }
+}
+
+__device__ __forceinline__ void run_cta_fp16(const MmaArgs& a, const SegDev& sg, int split, int kvh, float* smem_f) {
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const unsigned smem_base = (unsigned)__cvta_generic_to_shared(smem_f);
+    const long long n_tiles = (sg.S + TH - 1) / TH;
+    const long long tile0 = (long long)split * sg.split_len;
+    const long long tile1 = min(n_tiles, tile0 + sg.split_len);
+    const int h0 = kvh * a.G;
+    WarpState st;
+    init_state(st);
+    // q as the B operand in natural channel order: k = 2t, 2t+1 | 2t+8, 2t+9 of each 16-channel step
+    unsigned qh[8][2];
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+        qh[kk][0] = qh[kk][1] = 0u;
+        if (g < a.G) {
+            const __half* qp = a.q + (size_t)(h0 + g) * HD + 16 * kk + 2 * t;
+            qh[kk][0] = *reinterpret_cast<const unsigned*>(qp);
+            qh[kk][1] = *reinterpret_cast<const unsigned*>(qp + 8);
+        }
+    }
+    const float c_qk = a.sm_scale * kLog2e;
+    const unsigned ring = smem_base + wid * HOT_RING_BYTES;
+    for (long long tile = tile0 + wid; tile < tile1; tile += NWARPS) {
+        issue_hot_tile(sg, kvh, tile, ring, lane);
+        cp_async_wait<0>();
+        __syncwarp();
+        compute_hot_tile(ring, qh, c_qk, st, (int)min((long long)TH, sg.S - tile * TH), lane);
+        __syncwarp();
+    }
+    finish_cta<0>(a, st, kvh, smem_f);
+}
+
+template <int BITS>
+__device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int split, int kvh, float* smem_f) {
+    using C = Cfg<BITS>;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const unsigned smem_base = (unsigned)__cvta_generic_to_shared(smem_f);
+    const long long n_tiles = sg.S / C::T;
+    const long long tile0 = (long long)split * sg.split_len;
+    const long long tile1 = min(n_tiles, tile0 + sg.split_len);
+    const int h0 = kvh * a.G;
+
+    WarpState st;
+    init_state(st);
+
+    if (wid < C::ACTIVE_WARPS) {
+        // q as the B operand: lane (g, t) holds head g, channels 16k + 4t .. +3
+        unsigned qf[8][2];
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+            uint2 v = make_uint2(0u, 0u);
+            if (g < a.G) v = *reinterpret_cast<const uint2*>(a.q + (size_t)(h0 + g) * HD + 16 * kk + 4 * t);
+            qf[kk][0] = v.x;
+            qf[kk][1] = v.y;
+        }
+        const LaneSel<BITS> ls(g);
+        const float c_qk = a.sm_scale * kLog2e;
+        const unsigned ring = smem_base + wid * (NSTAGE * C::STAGE_WORDS * 4);
+        const long long first = tile0 + wid;
+        const int n_my = first < tile1 ? (int)((tile1 - first + C::ACTIVE_WARPS - 1) / C::ACTIVE_WARPS) : 0;
+        if (n_my > 0) issue_tile<BITS>(sg, kvh, first, ring, lane);
+        if (n_my > 1) issue_tile<BITS>(sg, kvh, first + C::ACTIVE_WARPS, ring + C::STAGE_WORDS * 4, lane);
+        for (int i = 0; i < n_my; ++i) {
+            if (i + 1 < n_my) cp_async_wait<1>(); else cp_async_wait<0>();
+            __syncwarp();
+            compute_tile<BITS>(ring + (i & 1) * C::STAGE_WORDS * 4, qf, c_qk, st, ls, lane);
+            __syncwarp();
+            if (i + 2 < n_my)
+                issue_tile<BITS>(sg, kvh, first + (long long)(i + 2) * C::ACTIVE_WARPS,
+                                 ring + (i & 1) * C::STAGE_WORDS * 4, lane);
+        }
+    }
+
+    finish_cta<BITS>(a, st, kvh, smem_f);
+}
+
 __global__ void __launch_bounds__(NTHREADS, 1) decode_mma_kernel(const __grid_constant__ MmaArgs a) {
     extern __shared__ __align__(16) float smem_f[];
     const int w = blockIdx.x, kvh = blockIdx.y;
@@ -311,7 +476,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_mma_kernel(const __grid_co
     while (si + 1 < a.n_segs && w >= a.segs[si + 1].work_begin) ++si;
     const SegDev& sg = a.segs[si];
     const int split = w - sg.work_begin;
-    if (sg.kbits == 2) run_cta<2>(a, sg, split, kvh, smem_f);
+    if (sg.kind == PKV_SEG_FP16) run_cta_fp16(a, sg, split, kvh, smem_f);
+    else if (sg.kbits == 2) run_cta<2>(a, sg, split, kvh, smem_f);
     else if (sg.kbits == 4) run_cta<4>(a, sg, split, kvh, smem_f);
     else run_cta<8>(a, sg, split, kvh, smem_f);
 }
@@ -319,13 +485,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_mma_kernel(const __grid_co
 }  // namespace
 
 bool eligible(const pkv_segment_t& s, int Hq, int Hkv, int hd) {
-    if (s.kind != PKV_SEG_KIVI || hd != HD || Hq / Hkv > 8) return false;
+    if (hd != HD || Hq / Hkv > 8) return false;
+    if (s.kind == PKV_SEG_FP16) {
+        const uintptr_t bits = reinterpret_cast<uintptr_t>(s.k_packed) | reinterpret_cast<uintptr_t>(s.v_packed);
+        return (bits & 15u) == 0 && s.head_stride % 8 == 0;
+    }
+    if (s.kind != PKV_SEG_KIVI) return false;
     if (s.k_bits != s.v_bits || s.k_group != 32 || s.v_group != 32) return false;
     if (s.seq_len % tile_tokens(s.k_bits) != 0) return false;
     const uintptr_t bits = reinterpret_cast<uintptr_t>(s.k_packed) | reinterpret_cast<uintptr_t>(s.k_scale) |
                            reinterpret_cast<uintptr_t>(s.k_mins) | reinterpret_cast<uintptr_t>(s.v_packed) |
                            reinterpret_cast<uintptr_t>(s.v_scale) | reinterpret_cast<uintptr_t>(s.v_mins);
     return (bits & 15u) == 0;
+}
+
+// Tiles of a segment as the tensor-core kernel counts them.
+long long tiles_of(const pkv_segment_t& s) {
+    if (s.kind == PKV_SEG_FP16) return (s.seq_len + TH - 1) / TH;
+    return s.seq_len / tile_tokens(s.k_bits);
 }
 
 int launch(const MmaArgs& a, int work, int Hkv, cudaStream_t stream) {

@@ -190,6 +190,7 @@ namespace pkv {
 namespace mma {
 // Whether the tensor-core kernel can take this segment (otherwise the generic kernel does).
 bool eligible(const pkv_segment_t& s, int Hq, int Hkv, int hd);
+long long tiles_of(const pkv_segment_t& s);
 // Launch over `work` CTAs per KV head; a.segs[*].work_begin is relative to this launch.
 int launch(const MmaArgs& a, int work, int Hkv, cudaStream_t stream);
 }  // namespace mma
