@@ -107,7 +107,8 @@ int pkv_decode_workspace_bytes(const pkv_segment_t* segs /* host */, int n_segs,
  *   out  float16 [Hq, hd]  = acc / l
  *   m, l float32 [Hq], acc float32 [Hq, hd]: the un-normalised partial of attention_triton.py:257-266,
  *   mergeable across segments, layers of a tier, or GPUs with pkv_merge_partials.
- * `workspace` is device scratch of at least pkv_decode_workspace_bytes(); calls that share it must not overlap. */
+ * `workspace` is device scratch of at least pkv_decode_workspace_bytes() (16-byte aligned; its contents need
+ * no initialisation); calls that share it must not overlap. */
 int pkv_decode_attention(const void* q, const pkv_segment_t* segs /* host */, int n_segs,
                          int num_q_heads, int num_kv_heads, int head_dim, float sm_scale,
                          int sm_count, void* workspace, size_t workspace_bytes, void* out, float* m,

@@ -7,6 +7,7 @@
 // Each CTA emits an un-normalised flash partial (m, l, acc) and the merge kernel combines them
 // (attention_triton.py:257-266 and :300-307 of the reference define the same algebra).
 #include <math.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "decode_plan.h"
@@ -203,58 +204,81 @@ decode_generic_kernel(const __grid_constant__ DecodeArgs a) {
     }
 }
 
-// Log-sum-exp merge of n_parts partials for one query head per CTA.
-__global__ void __launch_bounds__(128)
+// Log-sum-exp merge of n_parts partials, one query head per CTA of 256 threads.
+// Warp w owns parts p = w (mod 8) and lane owns four consecutive dims (float4; head_dim <= 256 means
+// up to two float4 per lane), so every load of a thread is independent of the others and of the
+// weights: they are all issued before the first use, one memory round trip for the whole merge.
+constexpr int kMergeThreads = 256;
+constexpr int kMergeMaxInflight = 6;  // parts per thread held in registers at once
+
+__global__ void __launch_bounds__(kMergeThreads)
 merge_partials_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
                       const float* __restrict__ pacc, int n_parts, int Hq, int hd,
                       __half* __restrict__ out, float* __restrict__ m_out,
                       float* __restrict__ l_out, float* __restrict__ acc_out) {
-    __shared__ float red[4];
-    __shared__ float w_s[256];
+    __shared__ float red_m[8];
+    __shared__ float red_l[8];
+    __shared__ __align__(16) float red_acc[8][256];
     const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int nvec = hd >> 2;  // float4 per row (hd % 4 == 0 is checked on the host)
+    const bool v0 = lane < nvec, v1 = lane + 32 < nvec;
 
+    // global max over all parts (each thread looks at a strided subset; loads independent)
     float mx = -INFINITY;
-    for (int p = tid; p < n_parts; p += 128) mx = fmaxf(mx, pm[(size_t)p * Hq + h]);
+    for (int p = tid; p < n_parts; p += kMergeThreads) mx = fmaxf(mx, __ldg(pm + (size_t)p * Hq + h));
     mx = warp_max(mx);
-    if (lane == 0) red[wid] = mx;
+    if (lane == 0) red_m[wid] = mx;
     __syncthreads();
-    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-    __syncthreads();
+    mx = red_m[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red_m[w]);
 
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
     float ls = 0.f;
-    float a0 = 0.f, a1 = 0.f;  // head_dim <= 256: two columns per thread
-    for (int base = 0; base < n_parts; base += 256) {
-        const int cnt = min(256, n_parts - base);
-        for (int p = tid; p < cnt; p += 128) {
-            const float wgt = expf(pm[(size_t)(base + p) * Hq + h] - mx);
-            w_s[p] = wgt;
-            ls += wgt * pl[(size_t)(base + p) * Hq + h];
+    for (int base = wid; base < n_parts; base += 8 * kMergeMaxInflight) {
+        float4 r0[kMergeMaxInflight], r1[kMergeMaxInflight];
+        float wm[kMergeMaxInflight], wl[kMergeMaxInflight];
+#pragma unroll
+        for (int u = 0; u < kMergeMaxInflight; ++u) {
+            const int p = base + 8 * u;
+            r0[u] = r1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            wm[u] = -INFINITY;
+            wl[u] = 0.f;
+            if (p < n_parts) {
+                const float4* row = reinterpret_cast<const float4*>(pacc + ((size_t)p * Hq + h) * hd);
+                if (v0) r0[u] = __ldg(row + lane);
+                if (v1) r1[u] = __ldg(row + lane + 32);
+                wm[u] = __ldg(pm + (size_t)p * Hq + h);
+                wl[u] = __ldg(pl + (size_t)p * Hq + h);
+            }
         }
-        __syncthreads();
-        for (int p = 0; p < cnt; ++p) {
-            const float* row = pacc + ((size_t)(base + p) * Hq + h) * hd;
-            const float wgt = w_s[p];
-            if (tid < hd) a0 = fmaf(wgt, row[tid], a0);
-            if (tid + 128 < hd) a1 = fmaf(wgt, row[tid + 128], a1);
+#pragma unroll
+        for (int u = 0; u < kMergeMaxInflight; ++u) {
+            const float wgt = expf(wm[u] - mx);  // -inf -> 0
+            ls = fmaf(wgt, wl[u], ls);
+            a0.x = fmaf(wgt, r0[u].x, a0.x); a0.y = fmaf(wgt, r0[u].y, a0.y);
+            a0.z = fmaf(wgt, r0[u].z, a0.z); a0.w = fmaf(wgt, r0[u].w, a0.w);
+            a1.x = fmaf(wgt, r1[u].x, a1.x); a1.y = fmaf(wgt, r1[u].y, a1.y);
+            a1.z = fmaf(wgt, r1[u].z, a1.z); a1.w = fmaf(wgt, r1[u].w, a1.w);
         }
-        __syncthreads();
     }
-    ls = warp_sum(ls);
-    if (lane == 0) red[wid] = ls;
+    if (v0) *reinterpret_cast<float4*>(&red_acc[wid][4 * lane]) = a0;
+    if (v1) *reinterpret_cast<float4*>(&red_acc[wid][4 * (lane + 32)]) = a1;
+    if (lane == 0) red_l[wid] = ls;  // every lane of a warp holds the same sum
     __syncthreads();
-    ls = red[0] + red[1] + red[2] + red[3];
-
+    float L = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) L += red_l[w];
+    if (tid < hd) {
+        float A = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) A += red_acc[w][tid];
+        if (out) out[(size_t)h * hd + tid] = __float2half_rn(A / L);
+        if (acc_out) acc_out[(size_t)h * hd + tid] = A;
+    }
     if (tid == 0) {
         if (m_out) m_out[h] = mx;
-        if (l_out) l_out[h] = ls;
-    }
-    if (tid < hd) {
-        if (out) out[(size_t)h * hd + tid] = __float2half_rn(a0 / ls);
-        if (acc_out) acc_out[(size_t)h * hd + tid] = a0;
-    }
-    if (tid + 128 < hd) {
-        if (out) out[(size_t)h * hd + tid + 128] = __float2half_rn(a1 / ls);
-        if (acc_out) acc_out[(size_t)h * hd + tid + 128] = a1;
+        if (l_out) l_out[h] = L;
     }
 }
 
@@ -263,6 +287,7 @@ int check_segments(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int h
     if (n_segs <= 0 || n_segs > PKV_MAX_SEGMENTS) return PKV_E_LIMIT;
     if (Hq <= 0 || Hkv <= 0 || hd <= 0 || Hq % Hkv) return PKV_E_SHAPE;
     if (hd > kThreads * kMaxDimsPerThread) return PKV_E_LIMIT;
+    if (hd % 4) return PKV_E_LAYOUT;
     for (int i = 0; i < n_segs; ++i) {
         const pkv_segment_t& s = segs[i];
         if (s.seq_len <= 0) return PKV_E_SHAPE;
@@ -379,9 +404,20 @@ int pkv_decode_attention(const void* q, const pkv_segment_t* segs, int n_segs, i
     const size_t W = (size_t)plan.total_work();
     const size_t need = W * num_q_heads * (head_dim + 2) * sizeof(float);
     if (workspace_bytes < need) return PKV_E_WORKSPACE;
-    float* pm = static_cast<float*>(workspace);
+    // acc rows first: they are read as float4 and must start on 16 bytes
+    float* pacc = reinterpret_cast<float*>(static_cast<char*>(workspace));
+    float* pm = pacc + W * num_q_heads * head_dim;
     float* pl = pm + W * num_q_heads;
-    float* pacc = pl + W * num_q_heads;
+    // one tensor-core launch and nothing else: its last CTAs do the merge themselves
+    static const bool carve = getenv("PKV_NO_CARVEOUT") == nullptr;
+    static thread_local bool carved = false;
+    if (carve && !carved) {
+        // keep the SM's shared-memory split where the tensor-core kernel wants it, so alternating kernels do not
+        // force a reconfiguration between launches
+        cudaFuncSetAttribute(merge_partials_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        carved = true;
+    }
     const int G = num_q_heads / num_kv_heads;
 
     // tensor-core kernel over the aligned KIVI segments
@@ -404,6 +440,8 @@ int pkv_decode_attention(const void* q, const pkv_segment_t* segs, int n_segs, i
             a.segs[i].work_begin -= a.work_offset;
             launch_work += a.segs[i].n_splits;
         }
+        static const int dbg2 = getenv("PKV_DEBUG_SKIP") ? atoi(getenv("PKV_DEBUG_SKIP")) : 0;
+        if (dbg2 & 2) continue;
         const int rc2 = mma::launch(a, launch_work, num_kv_heads, s);
         if (rc2 != PKV_OK) return rc2;
     }
@@ -433,7 +471,9 @@ int pkv_decode_attention(const void* q, const pkv_segment_t* segs, int n_segs, i
         decode_generic_kernel<<<grid, kThreads, smem, s>>>(a);
         PKV_LAUNCH_CHECK();
     }
-    merge_partials_kernel<<<num_q_heads, 128, 0, s>>>(pm, pl, pacc, (int)W, num_q_heads, head_dim,
+    static const int dbg = getenv("PKV_DEBUG_SKIP") ? atoi(getenv("PKV_DEBUG_SKIP")) : 0;
+    if (dbg & 1) return PKV_OK;
+    merge_partials_kernel<<<num_q_heads, kMergeThreads, 0, s>>>(pm, pl, pacc, (int)W, num_q_heads, head_dim,
                                                       static_cast<__half*>(out), m, l, acc);
     PKV_LAUNCH_CHECK();
     return PKV_OK;
@@ -445,7 +485,8 @@ int pkv_merge_partials(const float* m, const float* l, const float* acc, int n_p
     if (!m || !l || !acc) return PKV_E_NULL;
     if (n_parts <= 0 || num_q_heads <= 0 || head_dim <= 0) return PKV_E_SHAPE;
     if (head_dim > 256) return PKV_E_LIMIT;
-    merge_partials_kernel<<<num_q_heads, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+    if (head_dim % 4 || (reinterpret_cast<uintptr_t>(acc) & 15u)) return PKV_E_LAYOUT;
+    merge_partials_kernel<<<num_q_heads, kMergeThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         m, l, acc, n_parts, num_q_heads, head_dim, static_cast<__half*>(out), m_out, l_out, acc_out);
     PKV_LAUNCH_CHECK();
     return PKV_OK;

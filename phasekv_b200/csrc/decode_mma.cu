@@ -16,50 +16,74 @@ struct WarpState {
     float pm[4];       // sum_n p * v_zero, rows = dim groups (lanes g < 4)
 };
 
-// ---- cp.async of one tile into a stage, with the shared-memory layouts the compute loop wants:
-//   key codes   [word of the row][channel]          (transposed: a lane reads 4 channels in 16 B)
-//   key scale   [group pair][channel]  (same for zeros)
-//   value codes [token (swizzled)][word-in-group][dim group]
-//   value scale [token][4]             (same for zeros)
+// ---- cp.async of one tile into a stage.  Shared-memory layouts are the memory layouts, so every code
+// byte moves in 16-byte copies (4-byte copies throttled the load/store unit):
+//   key codes   [channel][T*BITS/8 bytes]
+//   key scale   [channel] words of two f16 (the tile's two groups); same for zeros   (4-byte copies)
+//   value codes [token row, one pad row per 8 tokens][hd*BITS/8 bytes]
+//   value scale [token][4 f16]          (same for zeros)
+// All address arithmetic that does not depend on the tile is done once per CTA (TileSrc).
 template <int BITS>
-__device__ __forceinline__ void issue_tile(const SegDev& sg, int kvh, long long tile, unsigned sa, int lane) {
+struct TileSrc {
     using C = Cfg<BITS>;
-    const long long S = sg.S;
-    const long long nbK = S * BITS / 8, ngK = S / 32;
-    const uint8_t* kp = sg.kp + (size_t)kvh * HD * nbK + tile * (C::T * BITS / 8);
-#pragma unroll 4
-    for (int it = 0; it < HD * C::KWPR / 32; ++it) {
-        const int idx = it * 32 + lane, c = idx / C::KWPR, w = idx % C::KWPR;
-        cp_async4(sa + 4 * (C::OFF_KC + w * C::KC_STRIDE + c), kp + (size_t)c * nbK + 4 * w);
+    static constexpr int CPR = C::KRB / 16;      // 16-byte chunks per key row of a tile
+    static constexpr int CPT = C::VWPT / 4;      // 16-byte chunks per value token row
+    static constexpr int TPI = 32 / CPT;         // tokens covered by one warp instruction
+    const uint8_t* kc;
+    const __half* ks;
+    const __half* km;
+    const uint8_t* vc;
+    const char* vs;
+    const char* vm;
+    long long kc_step, ks_step;
+    unsigned d_vc;  // lane offset of its value chunk inside the stage (bytes)
+    int lane;
+
+    __device__ TileSrc(const SegDev& sg, int kvh, int lane_) : lane(lane_) {
+        const long long S = sg.S, nbK = S * BITS / 8, ngK = S / 32;
+        kc = sg.kp + ((size_t)kvh * HD + lane / CPR) * nbK + 16 * (lane % CPR);
+        kc_step = (32 / CPR) * nbK;
+        ks = sg.ks + ((size_t)kvh * HD + lane) * ngK;
+        km = sg.km + ((size_t)kvh * HD + lane) * ngK;
+        ks_step = 32 * ngK;
+        vc = sg.vp + (size_t)kvh * S * (C::VWPT * 4) + 16 * lane;
+        const int lt = lane / CPT;
+        d_vc = 4 * C::OFF_VC + (lt + lt / 8) * (C::VWPT * 4) + 16 * (lane % CPT);
+        vs = reinterpret_cast<const char*>(sg.vs + (size_t)kvh * S * 4) + 16 * lane;
+        vm = reinterpret_cast<const char*>(sg.vm + (size_t)kvh * S * 4) + 16 * lane;
     }
-    const __half* ks = sg.ks + (size_t)kvh * HD * ngK + tile * C::NG;
-    const __half* km = sg.km + (size_t)kvh * HD * ngK + tile * C::NG;
+
+    __device__ __forceinline__ void issue(long long tile, unsigned sa) const {
+        const uint8_t* p = kc + tile * C::KRB;
 #pragma unroll
-    for (int it = 0; it < HD * C::KS_PAIRS / 32; ++it) {
-        const int idx = it * 32 + lane, c = idx / C::KS_PAIRS, pr = idx % C::KS_PAIRS;
-        cp_async4(sa + 4 * (C::OFF_KS + pr * C::KS_STRIDE + c), ks + (size_t)c * ngK + 2 * pr);
-        cp_async4(sa + 4 * (C::OFF_KM + pr * C::KS_STRIDE + c), km + (size_t)c * ngK + 2 * pr);
-    }
-    const uint8_t* vp = sg.vp + ((size_t)kvh * S + tile * C::T) * (C::VWPT * 4);
-#pragma unroll 4
-    for (int it = 0; it < C::T * C::VWPT / 32; ++it) {
-        const int idx = it * 32 + lane, tok = idx / C::VWPT, nw = idx % C::VWPT;
-        const int ptok = tok ^ ((tok >> 3) & (C::VROWS_PER_128B - 1));
-        cp_async4(sa + 4 * (C::OFF_VC + ptok * C::VWPT + (nw % BITS) * 4 + nw / BITS), vp + 4 * (size_t)idx);
-    }
-    const char* vs = reinterpret_cast<const char*>(sg.vs + ((size_t)kvh * S + tile * C::T) * 4);
-    const char* vm = reinterpret_cast<const char*>(sg.vm + ((size_t)kvh * S + tile * C::T) * 4);
+        for (int it = 0; it < HD * CPR / 32; ++it) {
+            cp_async16_ca(sa + 4 * C::OFF_KC + 16 * (it * 32 + lane), p);
+            p += kc_step;
+        }
+        const __half* s = ks + tile * C::NG;
+        const __half* m = km + tile * C::NG;
 #pragma unroll
-    for (int it = 0; it < C::T / 64; ++it) {
-        const int idx = it * 32 + lane;
-        cp_async16(sa + 4 * C::OFF_VS + 16 * idx, vs + 16 * idx);
-        cp_async16(sa + 4 * C::OFF_VM + 16 * idx, vm + 16 * idx);
+        for (int it = 0; it < HD / 32; ++it) {
+            cp_async4(sa + 4 * C::OFF_KS + 4 * lane + 128 * it, s);
+            cp_async4(sa + 4 * C::OFF_KM + 4 * lane + 128 * it, m);
+            s += ks_step;
+            m += ks_step;
+        }
+        const uint8_t* v = vc + tile * (C::T * C::VWPT * 4);
+#pragma unroll
+        for (int it = 0; it < C::T / TPI; ++it) {
+            const int tok0 = it * TPI;
+            cp_async16(sa + d_vc + (tok0 + tok0 / 8) * (C::VWPT * 4), v + 512 * it);
+        }
+        const long long off = tile * (C::T * 8);
+        cp_async16(sa + 4 * C::OFF_VS + 16 * lane, vs + off);
+        cp_async16(sa + 4 * C::OFF_VM + 16 * lane, vm + off);
+        cp_async_commit();
     }
-    cp_async_commit();
-}
+};
 
 template <int BITS>
-__device__ __forceinline__ void compute_tile(unsigned sa, const unsigned (&qf)[8][2], float c_qk,
+__device__ __forceinline__ void compute_tile(unsigned sa, unsigned q_lane, float c_qk,
                                              WarpState& st, const LaneSel<BITS>& ls, int lane) {
     using C = Cfg<BITS>;
     const int g = lane >> 2, t = lane & 3;
@@ -70,27 +94,34 @@ __device__ __forceinline__ void compute_tile(unsigned sa, const unsigned (&qf)[8
 #pragma unroll
     for (int i = 0; i < C::NG * 2; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
     float bacc[4] = {0.f, 0.f, 0.f, 0.f};
-    const int mpr = min(g >> 1, C::KS_PAIRS - 1);
     const unsigned msel = (g & 1) ? sel_hi : sel_lo;
+    // k-step kk contracts channels 16kk + {2t, 2t+1, 2t+8, 2t+9} in this lane (the natural MMA order)
+    const unsigned k_lane = sa + 4 * C::OFF_KC + 2 * t * C::KRB + 4 * ls.word;
+    const unsigned s_lane = sa + 4 * (C::OFF_KS + 2 * t);
+    const unsigned m_lane = sa + 4 * (C::OFF_KM + 2 * t);
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
-        const int chan = 16 * kk + 4 * t;
+        const unsigned qf0 = lds32(q_lane + 32 * kk);       // head g, channels 16kk + 2t, +1
+        const unsigned qf1 = lds32(q_lane + 32 * kk + 16);  // channels 16kk + 2t + 8, +9
         {   // sum_d q[h,d] * zero[d,G]: rows = groups of the tile (lanes g < NG carry data)
-            const uint4 mr = lds128(sa + 4 * (C::OFF_KM + mpr * C::KS_STRIDE + chan));
-            unsigned a0 = prmt(mr.x, mr.y, msel), a2 = prmt(mr.z, mr.w, msel);
+            const uint2 m01 = lds64(m_lane + 64 * kk), m23 = lds64(m_lane + 64 * kk + 32);
+            unsigned a0 = prmt(m01.x, m01.y, msel), a2 = prmt(m23.x, m23.y, msel);
             if (g >= C::NG) a0 = a2 = 0u;
-            mma16816(bacc, a0, 0u, a2, 0u, qf[kk][0], qf[kk][1]);
+            mma16816(bacc, a0, 0u, a2, 0u, qf0, qf1);
         }
-#pragma unroll
-        for (int pr = 0; pr < C::KS_PAIRS; ++pr) {
-            const uint4 sr = lds128(sa + 4 * (C::OFF_KS + pr * C::KS_STRIDE + chan));
+        {
+            const uint2 s01 = lds64(s_lane + 64 * kk), s23 = lds64(s_lane + 64 * kk + 32);
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const int G = 2 * pr + e;
+                const int G = e;
                 const unsigned sel = e ? sel_hi : sel_lo;
-                const unsigned b0 = hmul2(qf[kk][0], prmt(sr.x, sr.y, sel));
-                const unsigned b1 = hmul2(qf[kk][1], prmt(sr.z, sr.w, sel));
-                const uint4 kc = lds128(sa + 4 * (C::OFF_KC + (G * BITS + ls.word) * C::KC_STRIDE + chan));
+                const unsigned b0 = hmul2(qf0, prmt(s01.x, s01.y, sel));
+                const unsigned b1 = hmul2(qf1, prmt(s23.x, s23.y, sel));
+                uint4 kc;
+                kc.x = lds32(k_lane + (16 * kk + 0) * C::KRB + 4 * G * BITS);
+                kc.y = lds32(k_lane + (16 * kk + 1) * C::KRB + 4 * G * BITS);
+                kc.z = lds32(k_lane + (16 * kk + 8) * C::KRB + 4 * G * BITS);
+                kc.w = lds32(k_lane + (16 * kk + 9) * C::KRB + 4 * G * BITS);
                 unsigned ra[4], rb[4];
                 extract4<BITS>(kc.x, kc.y, ls, ra);
                 extract4<BITS>(kc.z, kc.w, ls, rb);
@@ -154,6 +185,9 @@ __device__ __forceinline__ void compute_tile(unsigned sa, const unsigned (&qf)[8
 
     // ---------------- out^T += V^T P: M = 16 dims, N = 8 heads, K = the 16 tokens of one score tile
     const unsigned vsel = (g & 1) ? sel_hi : sel_lo;
+    const unsigned vc_lane = sa + 4 * (C::OFF_VC + 9 * t * C::VWPT + ls.word);  // row 9t: pad row per 8 tokens
+    const unsigned vs_lane = sa + 4 * C::OFF_VS + 64 * t;
+    const unsigned vm_lane = sa + 4 * C::OFF_VM + 64 * t + 4 * ((g >> 1) & 1);     // word holding zero[.][g], g < 4
 #pragma unroll
     for (int G = 0; G < C::NG; ++G) {
 #pragma unroll
@@ -161,27 +195,22 @@ __device__ __forceinline__ void compute_tile(unsigned sa, const unsigned (&qf)[8
             const float* p = sacc[2 * G + j];
             const unsigned pb0 = movmatrix_trans(pack_half2(p[0], p[1]));  // tokens of rows 2t, 2t+1; head g
             const unsigned pb1 = movmatrix_trans(pack_half2(p[2], p[3]));  // tokens of rows 2t+8, 2t+9
-            int tok[4];
-            tok[0] = 32 * G + 8 * t + 2 * j;
-            tok[1] = tok[0] + 4;
-            tok[2] = tok[0] + 1;
-            tok[3] = tok[1] + 1;
-            uint2 vs[4], vm[4];
+            // tokens of rows 2t, 2t+1, 2t+8, 2t+9 of this score tile: 32G + 8t + {2j, 2j+4, 2j+1, 2j+5}
+            constexpr int kRow = C::VWPT * 4;
+            const int r[4] = {2 * j, 2 * j + 4, 2 * j + 1, 2 * j + 5};
+            uint2 vs[4];
+            unsigned vmw[4];
             unsigned vw[4][4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                vs[i] = lds64(sa + 4 * (C::OFF_VS + tok[i] * 2));
-                vm[i] = lds64(sa + 4 * (C::OFF_VM + tok[i] * 2));
-                const int ptok = tok[i] ^ ((tok[i] >> 3) & (C::VROWS_PER_128B - 1));
-                const uint4 w4 = lds128(sa + 4 * (C::OFF_VC + ptok * C::VWPT + 4 * ls.word));
-                vw[i][0] = w4.x;
-                vw[i][1] = w4.y;
-                vw[i][2] = w4.z;
-                vw[i][3] = w4.w;
+                vs[i] = lds64(vs_lane + 8 * (32 * G + r[i]));
+                vmw[i] = lds32(vm_lane + 8 * (32 * G + r[i]));
+#pragma unroll
+                for (int d = 0; d < 4; ++d) vw[i][d] = lds32(vc_lane + kRow * (36 * G + r[i]) + 4 * BITS * d);
             }
             {   // sum_n p[h,n] * zero[n,D]: rows = dim groups (lanes g < 4 carry data)
-                unsigned a0 = prmt((g & 2) ? vm[0].y : vm[0].x, (g & 2) ? vm[1].y : vm[1].x, vsel);
-                unsigned a2 = prmt((g & 2) ? vm[2].y : vm[2].x, (g & 2) ? vm[3].y : vm[3].x, vsel);
+                unsigned a0 = prmt(vmw[0], vmw[1], vsel);
+                unsigned a2 = prmt(vmw[2], vmw[3], vsel);
                 if (g >= 4) a0 = a2 = 0u;
                 mma16816(st.pm, a0, 0u, a2, 0u, pb0, pb1);
             }
@@ -252,11 +281,11 @@ __device__ __forceinline__ void finish_cta(const MmaArgs& a, WarpState& st, int 
 
     // ---------------- merge the warps' states into one partial per CTA
     const size_t widx = (size_t)a.work_offset + blockIdx.x;
-    const int dim = tid & (HD - 1), hh = tid >> 7;  // 256 threads: two head halves
+    const int dim = tid & (HD - 1), hh = tid >> 7;  // threads 0..255: two head halves
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const int h = hh * 4 + k;
-        if (h >= a.G) continue;
+        if (h >= a.G || tid >= 256) continue;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, smem_f[w * (8 * HD + 16) + 8 * HD + h]);
@@ -413,8 +442,9 @@ __device__ __forceinline__ void run_cta_fp16(const MmaArgs& a, const SegDev& sg,
         }
     }
     const float c_qk = a.sm_scale * kLog2e;
+    constexpr int kHotWarps = kSmemBytes / HOT_RING_BYTES < NWARPS ? kSmemBytes / HOT_RING_BYTES : NWARPS;
     const unsigned ring = smem_base + wid * HOT_RING_BYTES;
-    for (long long tile = tile0 + wid; tile < tile1; tile += NWARPS) {
+    for (long long tile = tile0 + wid; wid < kHotWarps && tile < tile1; tile += kHotWarps) {
         issue_hot_tile(sg, kvh, tile, ring, lane);
         cp_async_wait<0>();
         __syncwarp();
@@ -438,31 +468,35 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
     WarpState st;
     init_state(st);
 
-    if (wid < C::ACTIVE_WARPS) {
-        // q as the B operand: lane (g, t) holds head g, channels 16k + 4t .. +3
-        unsigned qf[8][2];
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-            uint2 v = make_uint2(0u, 0u);
-            if (g < a.G) v = *reinterpret_cast<const uint2*>(a.q + (size_t)(h0 + g) * HD + 16 * kk + 4 * t);
-            qf[kk][0] = v.x;
-            qf[kk][1] = v.y;
-        }
+    // smem: [q fragments kQBytes][ring of warp 0][ring of warp 1]...
+    const unsigned q_s = smem_base;
+    const unsigned rings = smem_base + kQBytes;
+    const bool active = wid < C::ACTIVE_WARPS;
+    const TileSrc<BITS> src(sg, kvh, lane);
+    const unsigned ring = rings + wid * C::RING_BYTES;
+    const long long first = tile0 + wid;
+    const int n_my = (active && first < tile1) ? (int)((tile1 - first + C::ACTIVE_WARPS - 1) / C::ACTIVE_WARPS) : 0;
+    if (n_my > 0) src.issue(first, ring);
+    if (n_my > 1) src.issue(first + C::ACTIVE_WARPS, ring + C::STAGE_WORDS * 4);
+    // q of the GQA group, staged once per CTA behind the first tile copies (rows padded against bank
+    // conflicts; zero rows for heads >= G)
+    if (tid < 128) {
+        const int head = tid >> 4, ch = tid & 15;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (head < a.G) v = *reinterpret_cast<const uint4*>(a.q + (size_t)(h0 + head) * HD + 8 * ch);
+        *reinterpret_cast<uint4*>(reinterpret_cast<char*>(smem_f) + head * kQRowBytes + 16 * ch) = v;
+    }
+    __syncthreads();
+    if (n_my > 0) {
         const LaneSel<BITS> ls(g);
         const float c_qk = a.sm_scale * kLog2e;
-        const unsigned ring = smem_base + wid * (NSTAGE * C::STAGE_WORDS * 4);
-        const long long first = tile0 + wid;
-        const int n_my = first < tile1 ? (int)((tile1 - first + C::ACTIVE_WARPS - 1) / C::ACTIVE_WARPS) : 0;
-        if (n_my > 0) issue_tile<BITS>(sg, kvh, first, ring, lane);
-        if (n_my > 1) issue_tile<BITS>(sg, kvh, first + C::ACTIVE_WARPS, ring + C::STAGE_WORDS * 4, lane);
         for (int i = 0; i < n_my; ++i) {
             if (i + 1 < n_my) cp_async_wait<1>(); else cp_async_wait<0>();
             __syncwarp();
-            compute_tile<BITS>(ring + (i & 1) * C::STAGE_WORDS * 4, qf, c_qk, st, ls, lane);
+            compute_tile<BITS>(ring + (i & 1) * C::STAGE_WORDS * 4, q_s + g * kQRowBytes + 4 * t, c_qk, st, ls, lane);
             __syncwarp();
             if (i + 2 < n_my)
-                issue_tile<BITS>(sg, kvh, first + (long long)(i + 2) * C::ACTIVE_WARPS,
-                                 ring + (i & 1) * C::STAGE_WORDS * 4, lane);
+                src.issue(first + (long long)(i + 2) * C::ACTIVE_WARPS, ring + (i & 1) * C::STAGE_WORDS * 4);
         }
     }
 

@@ -24,23 +24,28 @@ namespace pkv {
 namespace mma {
 
 constexpr int HD = 128;
-constexpr int NWARPS = 8;
+#ifndef PKV_MMA_WARPS
+#define PKV_MMA_WARPS 12
+#endif
+constexpr int NWARPS = PKV_MMA_WARPS;
 constexpr int NSTAGE = 2;
 constexpr int NTHREADS = NWARPS * 32;
+constexpr int kSmemBytes = 225 * 1024;  // dynamic shared memory of the kernel (of 227 KB usable)
+constexpr int kQRowBytes = 272;          // 128 f16 + 16 pad bytes
+constexpr int kQBytes = 2304;           // q of the GQA group as float16 [8 heads][128], shared by all warps
 
 template <int BITS>
 struct Cfg {
-    static constexpr int T = BITS == 2 ? 128 : 64;  // tokens per tile
+    static constexpr int T = 64;                    // tokens per tile
     static constexpr int NG = T / 32;               // key groups per tile
-    static constexpr int KWPR = T * BITS / 32;      // key code words per channel row of a tile
-    static constexpr int KC_STRIDE = HD + 4;        // words between word-rows of the transposed key tile
-    static constexpr int KC_WORDS = KWPR * KC_STRIDE;
-    static constexpr int KS_PAIRS = NG / 2;         // 32-bit words (two groups of f16) per channel
-    static constexpr int KS_STRIDE = HD + 16;
-    static constexpr int KS_WORDS = KS_PAIRS * KS_STRIDE;
-    static constexpr int VWPT = HD * BITS / 32;     // value code words per token
-    static constexpr int VC_WORDS = T * VWPT;
-    static constexpr int VS_WORDS = T * 2;          // four f16 per token
+    static constexpr int KRB = T * BITS / 8;        // key code bytes per channel row of a tile (16/32/64)
+    static constexpr int KC_WORDS = HD * KRB / 4;   // [channel][row bytes], as in memory
+    static constexpr int KS_WORDS = HD;             // [channel] one word = the tile's two groups (f16 x2)
+    static constexpr int VWPT = HD * BITS / 32;     // value code words per token (8/16/32)
+    static constexpr int VROWS = T + T / 8;         // one pad row per 8 tokens spreads the four token
+                                                    // blocks a load touches over different banks
+    static constexpr int VC_WORDS = VROWS * VWPT;   // [token row][words], as in memory
+    static constexpr int VS_WORDS = T * 2;          // [token][4 f16]
     static constexpr int OFF_KC = 0;
     static constexpr int OFF_KS = OFF_KC + KC_WORDS;
     static constexpr int OFF_KM = OFF_KS + KS_WORDS;
@@ -48,19 +53,17 @@ struct Cfg {
     static constexpr int OFF_VS = OFF_VC + VC_WORDS;
     static constexpr int OFF_VM = OFF_VS + VS_WORDS;
     static constexpr int STAGE_WORDS = OFF_VM + VS_WORDS;
-    // warps that stream tiles (the 8-bit stage is too large for eight rings in 227 KB)
-    static constexpr int ACTIVE_WARPS = BITS == 8 ? 6 : 8;
-    static constexpr int SMEM_BYTES = STAGE_WORDS * 4 * NSTAGE * ACTIVE_WARPS;
-    static constexpr int VROWS_PER_128B = 128 / (VWPT * 4) > 0 ? 128 / (VWPT * 4) : 1;  // 4, 2, 1
+    static constexpr int RING_BYTES = STAGE_WORDS * 4 * NSTAGE;
+    // warps that stream tiles: as many rings as fit
+    static constexpr int ACTIVE_WARPS =
+        (kSmemBytes - kQBytes) / RING_BYTES < NWARPS ? (kSmemBytes - kQBytes) / RING_BYTES : NWARPS;
 };
 
 constexpr int kMergeBytes = NWARPS * (8 * HD + 16) * 4;  // per-warp O[8][128] + m[8] + l[8]
-constexpr int kSmemBytes = 225792;  // max over bit widths (8-bit: 18816 * 2 * 6)
-static_assert(Cfg<2>::SMEM_BYTES <= kSmemBytes && Cfg<4>::SMEM_BYTES <= kSmemBytes &&
-              Cfg<8>::SMEM_BYTES <= kSmemBytes && kMergeBytes <= kSmemBytes, "shared memory budget");
+static_assert(kMergeBytes + kQBytes <= kSmemBytes && Cfg<8>::ACTIVE_WARPS >= 4, "shared memory budget");
+static_assert(Cfg<2>::NG == 2 && Cfg<2>::STAGE_WORDS % 4 == 0 && Cfg<4>::STAGE_WORDS % 4 == 0, "tile geometry");
 
-inline int tile_tokens(int bits) { return bits == 2 ? 128 : 64; }
-inline int active_warps(int bits) { return bits == 8 ? 6 : 8; }
+inline int tile_tokens(int) { return 64; }
 
 struct MmaArgs {
     const __half* q;
@@ -113,6 +116,9 @@ __device__ __forceinline__ void cp_async4(unsigned smem_addr, const void* g) {
 __device__ __forceinline__ void cp_async16(unsigned smem_addr, const void* g) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(g));
 }
+__device__ __forceinline__ void cp_async16_ca(unsigned smem_addr, const void* g) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(g));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
@@ -121,6 +127,11 @@ __device__ __forceinline__ void cp_async_wait() {
 __device__ __forceinline__ uint4 lds128(unsigned addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ unsigned lds32(unsigned addr) {
+    unsigned v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
 __device__ __forceinline__ uint2 lds64(unsigned addr) {
