@@ -16,59 +16,79 @@ struct WarpState {
     float pm[4];       // sum_n p * v_zero, rows = dim groups (lanes g < 4)
 };
 
-// ---- cp.async of one tile into a stage.  Shared-memory layouts are the memory layouts, so every code
-// byte moves in 16-byte copies (4-byte copies throttled the load/store unit):
-//   key codes   [channel][T*BITS/8 bytes]
-//   key scale   [channel] words of two f16 (the tile's two groups); same for zeros   (4-byte copies)
-//   value codes [token row, one pad row per 8 tokens][hd*BITS/8 bytes]
-//   value scale [token][4 f16]          (same for zeros)
-// All address arithmetic that does not depend on the tile is done once per CTA (TileSrc).
+// ---- loads.  Shared-memory layouts are the memory layouts (16-byte cp.async; 4-byte copies throttled
+// the load/store unit, and a copy costs one shared-memory write per 32-byte sector it gathers, so the
+// scattered key rows are fetched in chunks as long as the super-tile allows):
+//   K buffer : codes [channel][KROW bytes], scale [channel][MROW bytes], zero likewise   (CTA-wide)
+//   V stage  : codes [token row, one pad row per 8 tokens][hd*BITS/8 bytes], scale [token][4 f16], zero likewise
 template <int BITS>
-struct TileSrc {
+struct KSrc {
     using C = Cfg<BITS>;
-    static constexpr int CPR = C::KRB / 16;      // 16-byte chunks per key row of a tile
-    static constexpr int CPT = C::VWPT / 4;      // 16-byte chunks per value token row
-    static constexpr int TPI = 32 / CPT;         // tokens covered by one warp instruction
-    const uint8_t* kc;
-    const __half* ks;
-    const __half* km;
+    const uint8_t* kp;
+    const char* ks;
+    const char* km;
+    long long nbK, ngK2;  // bytes per key code row / per key scale row
+    bool meta16;          // scale rows can move in 16-byte copies
+
+    __device__ KSrc(const SegDev& sg, int kvh, long long tile0) {
+        nbK = sg.S * BITS / 8;
+        ngK2 = sg.S / 32 * 2;
+        kp = sg.kp + (size_t)kvh * HD * nbK;
+        ks = reinterpret_cast<const char*>(sg.ks) + (size_t)kvh * HD * ngK2;
+        km = reinterpret_cast<const char*>(sg.km) + (size_t)kvh * HD * ngK2;
+        meta16 = (ngK2 & 15) == 0 && (tile0 & 3) == 0;
+    }
+
+    // keys of tiles [tile, tile + n_sub) into the K buffer at `kb`; every thread of the CTA takes part
+    __device__ __forceinline__ void issue(long long tile, int n_sub, unsigned kb, int tid) const {
+        const int cpr = n_sub * (C::KRB / 16);
+        const uint8_t* src = kp + tile * C::KRB;
+        for (int idx = tid; idx < HD * cpr; idx += NTHREADS) {
+            const int row = idx / cpr, ch = idx - row * cpr;
+            cp_async16_ca(kb + row * C::KROW + 16 * ch, src + (size_t)row * nbK + 16 * ch);
+        }
+        const long long moff = tile * (C::NG * 2);
+        if (meta16) {
+            const int row_bytes = n_sub * C::NG * 2, cpm = (row_bytes + 15) / 16;
+            for (int idx = tid; idx < HD * cpm; idx += NTHREADS) {
+                const int row = idx / cpm, ch = idx - row * cpm;
+                const unsigned nbytes = min(16, row_bytes - 16 * ch);
+                const size_t off = (size_t)row * ngK2 + moff + 16 * ch;
+                cp_async16_zfill(kb + C::OFF_KS + row * C::MROW + 16 * ch, ks + off, nbytes);
+                cp_async16_zfill(kb + C::OFF_KM + row * C::MROW + 16 * ch, km + off, nbytes);
+            }
+        } else {
+            for (int idx = tid; idx < HD * n_sub; idx += NTHREADS) {
+                const int row = idx / n_sub, w = idx - row * n_sub;
+                const size_t off = (size_t)row * ngK2 + moff + 4 * w;
+                cp_async4(kb + C::OFF_KS + row * C::MROW + 4 * w, ks + off);
+                cp_async4(kb + C::OFF_KM + row * C::MROW + 4 * w, km + off);
+            }
+        }
+    }
+};
+
+template <int BITS>
+struct VSrc {
+    using C = Cfg<BITS>;
+    static constexpr int CPT = C::VWPT / 4;  // 16-byte chunks per token row
+    static constexpr int TPI = 32 / CPT;     // tokens covered by one warp instruction
     const uint8_t* vc;
     const char* vs;
     const char* vm;
-    long long kc_step, ks_step;
-    unsigned d_vc;  // lane offset of its value chunk inside the stage (bytes)
+    unsigned d_vc;
     int lane;
 
-    __device__ TileSrc(const SegDev& sg, int kvh, int lane_) : lane(lane_) {
-        const long long S = sg.S, nbK = S * BITS / 8, ngK = S / 32;
-        kc = sg.kp + ((size_t)kvh * HD + lane / CPR) * nbK + 16 * (lane % CPR);
-        kc_step = (32 / CPR) * nbK;
-        ks = sg.ks + ((size_t)kvh * HD + lane) * ngK;
-        km = sg.km + ((size_t)kvh * HD + lane) * ngK;
-        ks_step = 32 * ngK;
-        vc = sg.vp + (size_t)kvh * S * (C::VWPT * 4) + 16 * lane;
+    __device__ VSrc(const SegDev& sg, int kvh, int lane_) : lane(lane_) {
+        vc = sg.vp + (size_t)kvh * sg.S * (C::VWPT * 4) + 16 * lane;
         const int lt = lane / CPT;
-        d_vc = 4 * C::OFF_VC + (lt + lt / 8) * (C::VWPT * 4) + 16 * (lane % CPT);
-        vs = reinterpret_cast<const char*>(sg.vs + (size_t)kvh * S * 4) + 16 * lane;
-        vm = reinterpret_cast<const char*>(sg.vm + (size_t)kvh * S * 4) + 16 * lane;
+        d_vc = (lt + lt / 8) * (C::VWPT * 4) + 16 * (lane % CPT);
+        vs = reinterpret_cast<const char*>(sg.vs + (size_t)kvh * sg.S * 4) + 16 * lane;
+        vm = reinterpret_cast<const char*>(sg.vm + (size_t)kvh * sg.S * 4) + 16 * lane;
     }
 
+    // values of one tile into the stage at `sa`; one warp
     __device__ __forceinline__ void issue(long long tile, unsigned sa) const {
-        const uint8_t* p = kc + tile * C::KRB;
-#pragma unroll
-        for (int it = 0; it < HD * CPR / 32; ++it) {
-            cp_async16_ca(sa + 4 * C::OFF_KC + 16 * (it * 32 + lane), p);
-            p += kc_step;
-        }
-        const __half* s = ks + tile * C::NG;
-        const __half* m = km + tile * C::NG;
-#pragma unroll
-        for (int it = 0; it < HD / 32; ++it) {
-            cp_async4(sa + 4 * C::OFF_KS + 4 * lane + 128 * it, s);
-            cp_async4(sa + 4 * C::OFF_KM + 4 * lane + 128 * it, m);
-            s += ks_step;
-            m += ks_step;
-        }
         const uint8_t* v = vc + tile * (C::T * C::VWPT * 4);
 #pragma unroll
         for (int it = 0; it < C::T / TPI; ++it) {
@@ -76,14 +96,13 @@ struct TileSrc {
             cp_async16(sa + d_vc + (tok0 + tok0 / 8) * (C::VWPT * 4), v + 512 * it);
         }
         const long long off = tile * (C::T * 8);
-        cp_async16(sa + 4 * C::OFF_VS + 16 * lane, vs + off);
-        cp_async16(sa + 4 * C::OFF_VM + 16 * lane, vm + off);
-        cp_async_commit();
+        cp_async16(sa + C::OFF_VS + 16 * lane, vs + off);
+        cp_async16(sa + C::OFF_VM + 16 * lane, vm + off);
     }
 };
 
 template <int BITS>
-__device__ __forceinline__ void compute_tile(unsigned sa, unsigned q_lane, float c_qk,
+__device__ __forceinline__ void compute_tile(unsigned kb, int sub, unsigned sa, unsigned q_lane, float c_qk,
                                              WarpState& st, const LaneSel<BITS>& ls, int lane) {
     using C = Cfg<BITS>;
     const int g = lane >> 2, t = lane & 3;
@@ -96,21 +115,26 @@ __device__ __forceinline__ void compute_tile(unsigned sa, unsigned q_lane, float
     float bacc[4] = {0.f, 0.f, 0.f, 0.f};
     const unsigned msel = (g & 1) ? sel_hi : sel_lo;
     // k-step kk contracts channels 16kk + {2t, 2t+1, 2t+8, 2t+9} in this lane (the natural MMA order)
-    const unsigned k_lane = sa + 4 * C::OFF_KC + 2 * t * C::KRB + 4 * ls.word;
-    const unsigned s_lane = sa + 4 * (C::OFF_KS + 2 * t);
-    const unsigned m_lane = sa + 4 * (C::OFF_KM + 2 * t);
+    const unsigned k_lane = kb + 2 * t * C::KROW + sub * C::KRB + 4 * ls.word;
+    const unsigned s_lane = kb + C::OFF_KS + 2 * t * C::MROW + 4 * sub;
+    const unsigned m_lane = kb + C::OFF_KM + 2 * t * C::MROW + 4 * sub;
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
         const unsigned qf0 = lds32(q_lane + 32 * kk);       // head g, channels 16kk + 2t, +1
         const unsigned qf1 = lds32(q_lane + 32 * kk + 16);  // channels 16kk + 2t + 8, +9
         {   // sum_d q[h,d] * zero[d,G]: rows = groups of the tile (lanes g < NG carry data)
-            const uint2 m01 = lds64(m_lane + 64 * kk), m23 = lds64(m_lane + 64 * kk + 32);
-            unsigned a0 = prmt(m01.x, m01.y, msel), a2 = prmt(m23.x, m23.y, msel);
+            const unsigned m0w = lds32(m_lane + (16 * kk + 0) * C::MROW), m1w = lds32(m_lane + (16 * kk + 1) * C::MROW);
+            const unsigned m2w = lds32(m_lane + (16 * kk + 8) * C::MROW), m3w = lds32(m_lane + (16 * kk + 9) * C::MROW);
+            unsigned a0 = prmt(m0w, m1w, msel), a2 = prmt(m2w, m3w, msel);
             if (g >= C::NG) a0 = a2 = 0u;
             mma16816(bacc, a0, 0u, a2, 0u, qf0, qf1);
         }
         {
-            const uint2 s01 = lds64(s_lane + 64 * kk), s23 = lds64(s_lane + 64 * kk + 32);
+            uint2 s01, s23;
+            s01.x = lds32(s_lane + (16 * kk + 0) * C::MROW);
+            s01.y = lds32(s_lane + (16 * kk + 1) * C::MROW);
+            s23.x = lds32(s_lane + (16 * kk + 8) * C::MROW);
+            s23.y = lds32(s_lane + (16 * kk + 9) * C::MROW);
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int G = e;
@@ -118,10 +142,10 @@ __device__ __forceinline__ void compute_tile(unsigned sa, unsigned q_lane, float
                 const unsigned b0 = hmul2(qf0, prmt(s01.x, s01.y, sel));
                 const unsigned b1 = hmul2(qf1, prmt(s23.x, s23.y, sel));
                 uint4 kc;
-                kc.x = lds32(k_lane + (16 * kk + 0) * C::KRB + 4 * G * BITS);
-                kc.y = lds32(k_lane + (16 * kk + 1) * C::KRB + 4 * G * BITS);
-                kc.z = lds32(k_lane + (16 * kk + 8) * C::KRB + 4 * G * BITS);
-                kc.w = lds32(k_lane + (16 * kk + 9) * C::KRB + 4 * G * BITS);
+                kc.x = lds32(k_lane + (16 * kk + 0) * C::KROW + 4 * G * BITS);
+                kc.y = lds32(k_lane + (16 * kk + 1) * C::KROW + 4 * G * BITS);
+                kc.z = lds32(k_lane + (16 * kk + 8) * C::KROW + 4 * G * BITS);
+                kc.w = lds32(k_lane + (16 * kk + 9) * C::KROW + 4 * G * BITS);
                 unsigned ra[4], rb[4];
                 extract4<BITS>(kc.x, kc.y, ls, ra);
                 extract4<BITS>(kc.z, kc.w, ls, rb);
@@ -185,9 +209,9 @@ __device__ __forceinline__ void compute_tile(unsigned sa, unsigned q_lane, float
 
     // ---------------- out^T += V^T P: M = 16 dims, N = 8 heads, K = the 16 tokens of one score tile
     const unsigned vsel = (g & 1) ? sel_hi : sel_lo;
-    const unsigned vc_lane = sa + 4 * (C::OFF_VC + 9 * t * C::VWPT + ls.word);  // row 9t: pad row per 8 tokens
-    const unsigned vs_lane = sa + 4 * C::OFF_VS + 64 * t;
-    const unsigned vm_lane = sa + 4 * C::OFF_VM + 64 * t + 4 * ((g >> 1) & 1);     // word holding zero[.][g], g < 4
+    const unsigned vc_lane = sa + 4 * (9 * t * C::VWPT + ls.word);  // row 9t: pad row per 8 tokens
+    const unsigned vs_lane = sa + C::OFF_VS + 64 * t;
+    const unsigned vm_lane = sa + C::OFF_VM + 64 * t + 4 * ((g >> 1) & 1);  // word holding zero[.][g], g < 4
 #pragma unroll
     for (int G = 0; G < C::NG; ++G) {
 #pragma unroll
@@ -323,9 +347,6 @@ constexpr int HROW = HD + 8;                      // halves per padded row
 constexpr int HOT_TILE_BYTES = TH * HROW * 2;     // one of K or V
 constexpr int HOT_RING_BYTES = 2 * HOT_TILE_BYTES;
 
-__device__ __forceinline__ void cp_async16_zfill(unsigned smem_addr, const void* g, unsigned src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr), "l"(g), "r"(src_bytes));
-}
 __device__ __forceinline__ void ldmatrix_x4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
@@ -468,17 +489,23 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
     WarpState st;
     init_state(st);
 
-    // smem: [q fragments kQBytes][ring of warp 0][ring of warp 1]...
+    // smem: [q][K buffer 0][K buffer 1][value stages of warp 0][of warp 1]...
     const unsigned q_s = smem_base;
-    const unsigned rings = smem_base + kQBytes;
-    const bool active = wid < C::ACTIVE_WARPS;
-    const TileSrc<BITS> src(sg, kvh, lane);
-    const unsigned ring = rings + wid * C::RING_BYTES;
-    const long long first = tile0 + wid;
-    const int n_my = (active && first < tile1) ? (int)((tile1 - first + C::ACTIVE_WARPS - 1) / C::ACTIVE_WARPS) : 0;
-    if (n_my > 0) src.issue(first, ring);
-    if (n_my > 1) src.issue(first + C::ACTIVE_WARPS, ring + C::STAGE_WORDS * 4);
-    // q of the GQA group, staged once per CTA behind the first tile copies (rows padded against bank
+    const unsigned kbuf = smem_base + kQBytes;
+    const unsigned vring = kbuf + 2 * C::KBUF_BYTES + wid * (NSTAGE * C::VSTAGE_BYTES);
+    const KSrc<BITS> ksrc(sg, kvh, tile0);
+    const VSrc<BITS> vsrc(sg, kvh, lane);
+    const int n_tiles_cta = (int)(tile1 - tile0);
+    const int n_super = (n_tiles_cta + C::NSUB - 1) / C::NSUB;
+
+    // super-tile 0
+    {
+        const int n_sub = min(C::NSUB, n_tiles_cta);
+        ksrc.issue(tile0, n_sub, kbuf, tid);
+        if (wid < n_sub) vsrc.issue(tile0 + wid, vring);
+        cp_async_commit();
+    }
+    // q of the GQA group, staged once per CTA behind the first copies (rows padded against bank
     // conflicts; zero rows for heads >= G)
     if (tid < 128) {
         const int head = tid >> 4, ch = tid & 15;
@@ -486,18 +513,22 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
         if (head < a.G) v = *reinterpret_cast<const uint4*>(a.q + (size_t)(h0 + head) * HD + 8 * ch);
         *reinterpret_cast<uint4*>(reinterpret_cast<char*>(smem_f) + head * kQRowBytes + 16 * ch) = v;
     }
-    __syncthreads();
-    if (n_my > 0) {
-        const LaneSel<BITS> ls(g);
-        const float c_qk = a.sm_scale * kLog2e;
-        for (int i = 0; i < n_my; ++i) {
-            if (i + 1 < n_my) cp_async_wait<1>(); else cp_async_wait<0>();
-            __syncwarp();
-            compute_tile<BITS>(ring + (i & 1) * C::STAGE_WORDS * 4, q_s + g * kQRowBytes + 4 * t, c_qk, st, ls, lane);
-            __syncwarp();
-            if (i + 2 < n_my)
-                src.issue(first + (long long)(i + 2) * C::ACTIVE_WARPS, ring + (i & 1) * C::STAGE_WORDS * 4);
+    const LaneSel<BITS> ls(g);
+    const float c_qk = a.sm_scale * kLog2e;
+    for (int sp = 0; sp < n_super; ++sp) {
+        cp_async_wait<0>();
+        __syncthreads();  // super-tile sp has landed for everyone; everyone is done with sp - 1
+        const int n_sub = min(C::NSUB, n_tiles_cta - sp * C::NSUB);
+        if (sp + 1 < n_super) {
+            const long long next = tile0 + (long long)(sp + 1) * C::NSUB;
+            const int n_next = min(C::NSUB, n_tiles_cta - (sp + 1) * C::NSUB);
+            ksrc.issue(next, n_next, kbuf + ((sp + 1) & 1) * C::KBUF_BYTES, tid);
+            if (wid < n_next) vsrc.issue(next + wid, vring + ((sp + 1) & 1) * C::VSTAGE_BYTES);
+            cp_async_commit();
         }
+        if (wid < n_sub)
+            compute_tile<BITS>(kbuf + (sp & 1) * C::KBUF_BYTES, wid, vring + (sp & 1) * C::VSTAGE_BYTES,
+                               q_s + g * kQRowBytes + 4 * t, c_qk, st, ls, lane);
     }
 
     finish_cta<BITS>(a, st, kvh, smem_f);

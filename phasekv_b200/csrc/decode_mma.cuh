@@ -34,34 +34,34 @@ constexpr int kSmemBytes = 225 * 1024;  // dynamic shared memory of the kernel (
 constexpr int kQRowBytes = 272;          // 128 f16 + 16 pad bytes
 constexpr int kQBytes = 2304;           // q of the GQA group as float16 [8 heads][128], shared by all warps
 
+// Shared memory of a CTA:  [q][K buffer 0][K buffer 1][value ring of warp 0][value ring of warp 1]...
+// A K buffer holds the keys of one SUPER-TILE (NSUB consecutive 64-token tiles of the CTA's range) for
+// all warps: long row chunks make the scattered key rows cheap to fetch.  Warp w computes tile w of
+// the super-tile and streams that tile's values through its own 2-stage ring.
 template <int BITS>
 struct Cfg {
     static constexpr int T = 64;                    // tokens per tile
     static constexpr int NG = T / 32;               // key groups per tile
+    static constexpr int NSUB = BITS == 2 ? NWARPS : BITS == 4 ? (NWARPS < 8 ? NWARPS : 8) : 4;  // tiles per super-tile
     static constexpr int KRB = T * BITS / 8;        // key code bytes per channel row of a tile (16/32/64)
-    static constexpr int KC_WORDS = HD * KRB / 4;   // [channel][row bytes], as in memory
-    static constexpr int KS_WORDS = HD;             // [channel] one word = the tile's two groups (f16 x2)
+    static constexpr int KROW = NSUB * KRB + 16;    // key code row of a super-tile; the 16 pad bytes stagger banks
+    static constexpr int MROW = NSUB * NG * 2;      // key scale (or zero) row of a super-tile: f16 per group
+    static constexpr int KBUF_BYTES = HD * (KROW + 2 * MROW);
+    static constexpr int OFF_KS = HD * KROW;        // byte offsets inside a K buffer
+    static constexpr int OFF_KM = OFF_KS + HD * MROW;
     static constexpr int VWPT = HD * BITS / 32;     // value code words per token (8/16/32)
     static constexpr int VROWS = T + T / 8;         // one pad row per 8 tokens spreads the four token
                                                     // blocks a load touches over different banks
-    static constexpr int VC_WORDS = VROWS * VWPT;   // [token row][words], as in memory
-    static constexpr int VS_WORDS = T * 2;          // [token][4 f16]
-    static constexpr int OFF_KC = 0;
-    static constexpr int OFF_KS = OFF_KC + KC_WORDS;
-    static constexpr int OFF_KM = OFF_KS + KS_WORDS;
-    static constexpr int OFF_VC = OFF_KM + KS_WORDS;
-    static constexpr int OFF_VS = OFF_VC + VC_WORDS;
-    static constexpr int OFF_VM = OFF_VS + VS_WORDS;
-    static constexpr int STAGE_WORDS = OFF_VM + VS_WORDS;
-    static constexpr int RING_BYTES = STAGE_WORDS * 4 * NSTAGE;
-    // warps that stream tiles: as many rings as fit
-    static constexpr int ACTIVE_WARPS =
-        (kSmemBytes - kQBytes) / RING_BYTES < NWARPS ? (kSmemBytes - kQBytes) / RING_BYTES : NWARPS;
+    static constexpr int OFF_VS = VROWS * VWPT * 4; // byte offsets inside a value stage: codes, scale, zero
+    static constexpr int OFF_VM = OFF_VS + T * 8;
+    static constexpr int VSTAGE_BYTES = OFF_VM + T * 8;
+    static constexpr int SMEM_BYTES = kQBytes + 2 * KBUF_BYTES + NSUB * NSTAGE * VSTAGE_BYTES;
 };
 
 constexpr int kMergeBytes = NWARPS * (8 * HD + 16) * 4;  // per-warp O[8][128] + m[8] + l[8]
-static_assert(kMergeBytes + kQBytes <= kSmemBytes && Cfg<8>::ACTIVE_WARPS >= 4, "shared memory budget");
-static_assert(Cfg<2>::NG == 2 && Cfg<2>::STAGE_WORDS % 4 == 0 && Cfg<4>::STAGE_WORDS % 4 == 0, "tile geometry");
+static_assert(kMergeBytes + kQBytes <= kSmemBytes && Cfg<2>::SMEM_BYTES <= kSmemBytes &&
+              Cfg<4>::SMEM_BYTES <= kSmemBytes && Cfg<8>::SMEM_BYTES <= kSmemBytes, "shared memory budget");
+static_assert(Cfg<2>::NG == 2 && Cfg<2>::KBUF_BYTES % 16 == 0 && Cfg<2>::VSTAGE_BYTES % 16 == 0, "tile geometry");
 
 inline int tile_tokens(int) { return 64; }
 
@@ -118,6 +118,9 @@ __device__ __forceinline__ void cp_async16(unsigned smem_addr, const void* g) {
 }
 __device__ __forceinline__ void cp_async16_ca(unsigned smem_addr, const void* g) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(g));
+}
+__device__ __forceinline__ void cp_async16_zfill(unsigned smem_addr, const void* g, unsigned src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr), "l"(g), "r"(src_bytes));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
