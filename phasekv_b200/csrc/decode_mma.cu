@@ -39,8 +39,11 @@ struct KSrc {
         meta16 = (ngK2 & 15) == 0 && (tile0 & 3) == 0;
     }
 
-    // keys of tiles [tile, tile + n_sub) into the K buffer at `kb`; every thread of the CTA takes part
-    __device__ __forceinline__ void issue(long long tile, int n_sub, unsigned kb, int tid) const {
+    // keys of tiles [tile, tile + n_sub) into the K buffer at `kb`; every thread of the CTA takes part.
+    // FULL (n_sub == NSUB) makes every divisor a compile-time constant.
+    template <bool FULL>
+    __device__ __forceinline__ void issue_impl(long long tile, int n_sub_rt, unsigned kb, int tid) const {
+        const int n_sub = FULL ? C::NSUB : n_sub_rt;
         const int cpr = n_sub * (C::KRB / 16);
         const uint8_t* src = kp + tile * C::KRB;
         for (int idx = tid; idx < HD * cpr; idx += NTHREADS) {
@@ -65,6 +68,10 @@ struct KSrc {
                 cp_async4(kb + C::OFF_KM + row * C::MROW + 4 * w, km + off);
             }
         }
+    }
+    __device__ __forceinline__ void issue(long long tile, int n_sub, unsigned kb, int tid) const {
+        if (n_sub == C::NSUB) issue_impl<true>(tile, n_sub, kb, tid);
+        else issue_impl<false>(tile, n_sub, kb, tid);
     }
 };
 
