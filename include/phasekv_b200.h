@@ -114,6 +114,19 @@ int pkv_decode_attention(const void* q, const pkv_segment_t* segs /* host */, in
                          int sm_count, void* workspace, size_t workspace_bytes, void* out, float* m,
                          float* l, float* acc, pkv_stream_t stream);
 
+/* No counterpart in the reference.  Same computation and outputs as pkv_decode_attention, for callers that
+ * cannot hand over scratch memory because they may not allocate on the device (a plugin with a fixed memory
+ * budget, code running under stream capture).  The split-K partials go to an array of
+ * PKV_STATIC_SCRATCH_BYTES that is part of the library image on every GPU that loads it.  Requests that need
+ * more scratch than that fail with PKV_E_LIMIT.  The first call on each device looks the array's device address
+ * up (make that call before starting a stream capture).  All calls on a device share the array: calls whose
+ * kernels may overlap on the GPU must not use this entry point concurrently.  No device memory is allocated
+ * or freed. */
+#define PKV_STATIC_SCRATCH_BYTES (8u << 20)
+int pkv_decode_attention_static(const void* q, const pkv_segment_t* segs /* host */, int n_segs,
+                                int num_q_heads, int num_kv_heads, int head_dim, float sm_scale, int sm_count,
+                                void* out, float* m, float* l, float* acc, pkv_stream_t stream);
+
 /* attention_triton.py:257-266 _reduce_splits and :300-307 _merge_partials:
  * m, l float32 [n_parts, Hq] and acc float32 [n_parts, Hq, hd] (contiguous) are combined with
  * M = max m, w = exp(m - M), L = sum w*l, A = sum w*acc.  out float16 [Hq, hd] = A / L;

@@ -56,6 +56,8 @@ _SIGNATURES = {
                                     ctypes.POINTER(ctypes.c_size_t)], _I32),
     "pkv_decode_attention": ([_VP, ctypes.POINTER(Segment), _I32, _I32, _I32, _I32, _F32, _I32, _VP,
                               ctypes.c_size_t, _VP, _VP, _VP, _VP, _VP], _I32),
+    "pkv_decode_attention_static": ([_VP, ctypes.POINTER(Segment), _I32, _I32, _I32, _I32, _F32, _I32,
+                                     _VP, _VP, _VP, _VP, _VP], _I32),
     "pkv_merge_partials": ([_VP, _VP, _VP, _I32, _I32, _I32, _VP, _VP, _VP, _VP, _VP], _I32),
     "pkv_cold_select_pack": ([_VP, _VP, _I64, _I64, _I32, _I64, _I64, _I64, _I32, _I64,
                               _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP], _I32),

@@ -495,3 +495,43 @@ int pkv_merge_partials(const float* m, const float* l, const float* acc, int n_p
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot provide scratch: a serving plugin that is handed a fixed memory
+// budget at load time and is forbidden to touch the allocator on the request path, or code that runs
+// while a stream is being captured, where cudaMalloc is illegal.  For them the split-K partials live
+// in a fixed array inside the library image.  Every GPU that loads the library carries the array
+// until the process exits, so it is kept modest.
+//
+// The array's name is only a host-side handle: the device address is looked up once per device with
+// cudaGetSymbolAddress (with that device current) on the first call made on that device, which
+// should therefore happen before any stream capture begins.  All calls on a device share the array
+// and it keeps the previous call's partials; nothing in it has to start at zero, because each call
+// overwrites every entry it later reads.  Two calls whose kernels overlap on the GPU race on it.
+namespace {
+__device__ __align__(256) unsigned char g_static_scratch[PKV_STATIC_SCRATCH_BYTES];
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};
+}  // namespace
+
+extern "C" int pkv_decode_attention_static(const void* q, const pkv_segment_t* segs, int n_segs,
+                                           int num_q_heads, int num_kv_heads, int head_dim, float sm_scale,
+                                           int sm_count, void* out, float* m, float* l, float* acc,
+                                           pkv_stream_t stream) {
+    size_t need = 0;
+    const int rc = pkv_decode_workspace_bytes(segs, n_segs, num_q_heads, num_kv_heads, head_dim, sm_count, &need);
+    if (rc != PKV_OK) return rc;
+    if (need > (size_t)PKV_STATIC_SCRATCH_BYTES) return PKV_E_LIMIT;
+    int dev = 0;
+    PKV_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return PKV_E_LIMIT;
+    void* ptr = g_static_scratch_addr[dev];
+    if (ptr == nullptr) {
+        PKV_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        g_static_scratch_addr[dev] = ptr;  // racing first calls store the same value
+    }
+    return pkv_decode_attention(q, segs, n_segs, num_q_heads, num_kv_heads, head_dim, sm_scale, sm_count, ptr,
+                                (size_t)PKV_STATIC_SCRATCH_BYTES, out, m, l, acc, stream);
+}
