@@ -220,6 +220,9 @@ merge_partials_kernel(const float* __restrict__ pm, const float* __restrict__ pl
     __shared__ float red_l[8];
     __shared__ __align__(16) float red_acc[8][256];
     const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    // When launched as a programmatic dependent of the split-K kernel this grid may already be resident while
+    // that kernel finishes; wait here for its results (a no-op for an ordinary launch).
+    cudaGridDependencySynchronize();
     const int nvec = hd >> 2;  // float4 per row (hd % 4 == 0 is checked on the host)
     const bool v0 = lane < nvec, v1 = lane + 32 < nvec;
 
@@ -475,9 +478,25 @@ int pkv_decode_attention(const void* q, const pkv_segment_t* segs, int n_segs, i
     }
     static const int dbg = getenv("PKV_DEBUG_SKIP") ? atoi(getenv("PKV_DEBUG_SKIP")) : 0;
     if (dbg & 1) return PKV_OK;
-    merge_partials_kernel<<<num_q_heads, kMergeThreads, 0, s>>>(pm, pl, pacc, (int)W, num_q_heads, head_dim,
-                                                      static_cast<__half*>(out), m, l, acc);
-    PKV_LAUNCH_CHECK();
+    {
+        // programmatic dependent launch: the merge grid is scheduled while the split-K kernel drains, which hides
+        // its launch latency; cudaGridDependencySynchronize() inside orders the data
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)num_q_heads);
+        cfg.blockDim = dim3(kMergeThreads);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const float* cpm = pm;
+        const float* cpl = pl;
+        const float* cpacc = pacc;
+        PKV_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partials_kernel, cpm, cpl, cpacc, (int)W, num_q_heads, head_dim,
+                                        static_cast<__half*>(out), m, l, acc));
+    }
     return PKV_OK;
 }
 

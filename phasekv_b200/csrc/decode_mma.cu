@@ -109,7 +109,7 @@ struct VSrc {
 };
 
 template <int BITS>
-__device__ __forceinline__ void compute_tile(unsigned kb, int sub, unsigned sa, unsigned q_lane, float c_qk,
+__device__ __forceinline__ void compute_tile(const char* kb, int sub, const char* sa, const char* q_lane, float c_qk,
                                              WarpState& st, const LaneSel<BITS>& ls, int lane) {
     using C = Cfg<BITS>;
     const int g = lane >> 2, t = lane & 3;
@@ -122,26 +122,26 @@ __device__ __forceinline__ void compute_tile(unsigned kb, int sub, unsigned sa, 
     float bacc[4] = {0.f, 0.f, 0.f, 0.f};
     const unsigned msel = (g & 1) ? sel_hi : sel_lo;
     // k-step kk contracts channels 16kk + {2t, 2t+1, 2t+8, 2t+9} in this lane (the natural MMA order)
-    const unsigned k_lane = kb + 2 * t * C::KROW + sub * C::KRB + 4 * ls.word;
-    const unsigned s_lane = kb + C::OFF_KS + 2 * t * C::MROW + 4 * sub;
-    const unsigned m_lane = kb + C::OFF_KM + 2 * t * C::MROW + 4 * sub;
+    const char* k_lane = kb + 2 * t * C::KROW + sub * C::KRB + 4 * ls.word;
+    const char* s_lane = kb + C::OFF_KS + 2 * t * C::MROW + 4 * sub;
+    const char* m_lane = kb + C::OFF_KM + 2 * t * C::MROW + 4 * sub;
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
-        const unsigned qf0 = lds32(q_lane + 32 * kk);       // head g, channels 16kk + 2t, +1
-        const unsigned qf1 = lds32(q_lane + 32 * kk + 16);  // channels 16kk + 2t + 8, +9
-        {   // sum_d q[h,d] * zero[d,G]: rows = groups of the tile (lanes g < NG carry data)
-            const unsigned m0w = lds32(m_lane + (16 * kk + 0) * C::MROW), m1w = lds32(m_lane + (16 * kk + 1) * C::MROW);
-            const unsigned m2w = lds32(m_lane + (16 * kk + 8) * C::MROW), m3w = lds32(m_lane + (16 * kk + 9) * C::MROW);
+        const unsigned qf0 = ldp32(q_lane + 32 * kk);       // head g, channels 16kk + 2t, +1
+        const unsigned qf1 = ldp32(q_lane + 32 * kk + 16);  // channels 16kk + 2t + 8, +9
+        {   // sum_d q[h,d] * zero[d,G]: rows = groups of the tile; only rows g < NG are read back, so the
+            // other lanes may feed whatever they loaded
+            const unsigned m0w = ldp32(m_lane + (16 * kk + 0) * C::MROW), m1w = ldp32(m_lane + (16 * kk + 1) * C::MROW);
+            const unsigned m2w = ldp32(m_lane + (16 * kk + 8) * C::MROW), m3w = ldp32(m_lane + (16 * kk + 9) * C::MROW);
             unsigned a0 = prmt(m0w, m1w, msel), a2 = prmt(m2w, m3w, msel);
-            if (g >= C::NG) a0 = a2 = 0u;
             mma16816(bacc, a0, 0u, a2, 0u, qf0, qf1);
         }
         {
             uint2 s01, s23;
-            s01.x = lds32(s_lane + (16 * kk + 0) * C::MROW);
-            s01.y = lds32(s_lane + (16 * kk + 1) * C::MROW);
-            s23.x = lds32(s_lane + (16 * kk + 8) * C::MROW);
-            s23.y = lds32(s_lane + (16 * kk + 9) * C::MROW);
+            s01.x = ldp32(s_lane + (16 * kk + 0) * C::MROW);
+            s01.y = ldp32(s_lane + (16 * kk + 1) * C::MROW);
+            s23.x = ldp32(s_lane + (16 * kk + 8) * C::MROW);
+            s23.y = ldp32(s_lane + (16 * kk + 9) * C::MROW);
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int G = e;
@@ -149,10 +149,10 @@ __device__ __forceinline__ void compute_tile(unsigned kb, int sub, unsigned sa, 
                 const unsigned b0 = hmul2(qf0, prmt(s01.x, s01.y, sel));
                 const unsigned b1 = hmul2(qf1, prmt(s23.x, s23.y, sel));
                 uint4 kc;
-                kc.x = lds32(k_lane + (16 * kk + 0) * C::KROW + 4 * G * BITS);
-                kc.y = lds32(k_lane + (16 * kk + 1) * C::KROW + 4 * G * BITS);
-                kc.z = lds32(k_lane + (16 * kk + 8) * C::KROW + 4 * G * BITS);
-                kc.w = lds32(k_lane + (16 * kk + 9) * C::KROW + 4 * G * BITS);
+                kc.x = ldp32(k_lane + (16 * kk + 0) * C::KROW + 4 * G * BITS);
+                kc.y = ldp32(k_lane + (16 * kk + 1) * C::KROW + 4 * G * BITS);
+                kc.z = ldp32(k_lane + (16 * kk + 8) * C::KROW + 4 * G * BITS);
+                kc.w = ldp32(k_lane + (16 * kk + 9) * C::KROW + 4 * G * BITS);
                 unsigned ra[4], rb[4];
                 extract4<BITS>(kc.x, kc.y, ls, ra);
                 extract4<BITS>(kc.z, kc.w, ls, rb);
@@ -216,9 +216,9 @@ __device__ __forceinline__ void compute_tile(unsigned kb, int sub, unsigned sa, 
 
     // ---------------- out^T += V^T P: M = 16 dims, N = 8 heads, K = the 16 tokens of one score tile
     const unsigned vsel = (g & 1) ? sel_hi : sel_lo;
-    const unsigned vc_lane = sa + 4 * (9 * t * C::VWPT + ls.word);  // row 9t: pad row per 8 tokens
-    const unsigned vs_lane = sa + C::OFF_VS + 64 * t;
-    const unsigned vm_lane = sa + C::OFF_VM + 64 * t + 4 * ((g >> 1) & 1);  // word holding zero[.][g], g < 4
+    const char* vc_lane = sa + 4 * (9 * t * C::VWPT + ls.word);  // row 9t: pad row per 8 tokens
+    const char* vs_lane = sa + C::OFF_VS + 64 * t;
+    const char* vm_lane = sa + C::OFF_VM + 64 * t + 4 * ((g >> 1) & 1);  // word holding zero[.][g], g < 4
 #pragma unroll
     for (int G = 0; G < C::NG; ++G) {
 #pragma unroll
@@ -234,15 +234,14 @@ __device__ __forceinline__ void compute_tile(unsigned kb, int sub, unsigned sa, 
             unsigned vw[4][4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                vs[i] = lds64(vs_lane + 8 * (32 * G + r[i]));
-                vmw[i] = lds32(vm_lane + 8 * (32 * G + r[i]));
+                vs[i] = ldp64(vs_lane + 8 * (32 * G + r[i]));
+                vmw[i] = ldp32(vm_lane + 8 * (32 * G + r[i]));
 #pragma unroll
-                for (int d = 0; d < 4; ++d) vw[i][d] = lds32(vc_lane + kRow * (36 * G + r[i]) + 4 * BITS * d);
+                for (int d = 0; d < 4; ++d) vw[i][d] = ldp32(vc_lane + kRow * (36 * G + r[i]) + 4 * BITS * d);
             }
-            {   // sum_n p[h,n] * zero[n,D]: rows = dim groups (lanes g < 4 carry data)
+            {   // sum_n p[h,n] * zero[n,D]: rows = dim groups; only rows g < 4 are read back
                 unsigned a0 = prmt(vmw[0], vmw[1], vsel);
                 unsigned a2 = prmt(vmw[2], vmw[3], vsel);
-                if (g >= 4) a0 = a2 = 0u;
                 mma16816(st.pm, a0, 0u, a2, 0u, pb0, pb1);
             }
 #pragma unroll
@@ -497,7 +496,7 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
     init_state(st);
 
     // smem: [q][K buffer 0][K buffer 1][value stages of warp 0][of warp 1]...
-    const unsigned q_s = smem_base;
+    const char* smem_c = reinterpret_cast<const char*>(smem_f);
     const unsigned kbuf = smem_base + kQBytes;
     const unsigned vring = kbuf + 2 * C::KBUF_BYTES + wid * (NSTAGE * C::VSTAGE_BYTES);
     const KSrc<BITS> ksrc(sg, kvh, tile0);
@@ -520,6 +519,9 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
         if (head < a.G) v = *reinterpret_cast<const uint4*>(a.q + (size_t)(h0 + head) * HD + 8 * ch);
         *reinterpret_cast<uint4*>(reinterpret_cast<char*>(smem_f) + head * kQRowBytes + 16 * ch) = v;
     }
+    // let a programmatic dependent (the merge) be scheduled as soon as SMs free up; it still waits for this
+    // grid to complete before it reads anything
+    cudaTriggerProgrammaticLaunchCompletion();
     const LaneSel<BITS> ls(g);
     const float c_qk = a.sm_scale * kLog2e;
     for (int sp = 0; sp < n_super; ++sp) {
@@ -534,8 +536,9 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
             cp_async_commit();
         }
         if (wid < n_sub)
-            compute_tile<BITS>(kbuf + (sp & 1) * C::KBUF_BYTES, wid, vring + (sp & 1) * C::VSTAGE_BYTES,
-                               q_s + g * kQRowBytes + 4 * t, c_qk, st, ls, lane);
+            compute_tile<BITS>(smem_c + kQBytes + (sp & 1) * C::KBUF_BYTES, wid,
+                               smem_c + kQBytes + 2 * C::KBUF_BYTES + (wid * NSTAGE + (sp & 1)) * C::VSTAGE_BYTES,
+                               smem_c + g * kQRowBytes + 4 * t, c_qk, st, ls, lane);
     }
 
     finish_cta<BITS>(a, st, kvh, smem_f);

@@ -132,6 +132,11 @@ __device__ __forceinline__ uint4 lds128(unsigned addr) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
+// plain loads through pointers derived from the shared array: the compiler folds constant offsets into the
+// instruction, which hand-written ld.shared with a computed address register cannot
+__device__ __forceinline__ unsigned ldp32(const char* p) { return *reinterpret_cast<const unsigned*>(p); }
+__device__ __forceinline__ uint2 ldp64(const char* p) { return *reinterpret_cast<const uint2*>(p); }
+__device__ __forceinline__ uint4 ldp128(const char* p) { return *reinterpret_cast<const uint4*>(p); }
 __device__ __forceinline__ unsigned lds32(unsigned addr) {
     unsigned v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
