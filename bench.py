@@ -35,8 +35,8 @@ METRIC = "decode_attn_hbm_GBps"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode launch at 32768 prompt tokens,
-# from the ncu capture summarised under profiles/ (None until a capture exists).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# from the ncu capture summarised in profiles/decode_mma_kernel_qwen7b_32k.md.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 13_630_000  # 13.12 MB split-K kernel + 0.51 MB merge, reads; writes 0
 
 
 def parse_args():
