@@ -244,6 +244,28 @@ def _remove_batch(pt: PackedTensor) -> PackedTensor:
                    orig_shape=tuple(pt.orig_shape[1:]), axis=pt.axis - 1)
 
 
+def _cached_packed_segment(segment, num_splits: Optional[int]):
+    """Descriptor of a frozen packed segment of a ``LayerTiers``.  Segments are immutable once built
+    (the prompt is read-only, cold segments are never re-quantised), so the descriptor is built once
+    and kept on the segment object; it is rebuilt if the tensors behind it were replaced."""
+    key, value = segment.key, segment.value
+    tag = (key.packed.data_ptr(), value.packed.data_ptr(), key.scale.data_ptr(), value.scale.data_ptr(),
+           int(num_splits or 0))
+    cached = getattr(segment, "_pkv_descriptor", None)
+    if cached is not None and cached[0] == tag:
+        return cached[1], cached[2], cached[3]
+    k, v = _remove_batch(key), _remove_batch(value)
+    if k.axis != 1 or v.axis != 2:
+        raise ValueError("K must be packed along the token axis and V along head_dim")
+    seg, keep = _packed_segment(k, v, num_splits)
+    shape = (k.orig_shape[0], k.orig_shape[2])
+    try:
+        segment._pkv_descriptor = (tag, seg, keep, shape)
+    except AttributeError:  # objects without a __dict__ are simply not cached
+        pass
+    return seg, keep, shape
+
+
 def layer_segments(tiers, num_splits: Optional[int] = None):
     """Segment descriptors for every tier of a ``LayerTiers`` (batch 1), in prompt, extensions,
     cold, hot order, plus the tensors that must stay alive while they are in use."""
@@ -251,18 +273,15 @@ def layer_segments(tiers, num_splits: Optional[int] = None):
     keep: list = []
     hkv = hd = None
     for segment in [tiers.prompt, *tiers.prompt_extensions, *tiers.cold]:
-        key, value = _remove_batch(segment.key), _remove_batch(segment.value)
-        if key.axis != 1 or value.axis != 2:
-            raise ValueError("K must be packed along the token axis and V along head_dim")
-        s, kp = _packed_segment(key, value, num_splits)
-        segs.append(s), keep.extend(kp)
-        hkv, _, hd = key.orig_shape
+        s, kp, (hkv, hd) = _cached_packed_segment(segment, num_splits)
+        segs.append(s), keep.append(kp)
     if tiers.hot_len:
         hot_k, hot_v = tiers.hot_views()
         if hot_k.shape[0] != 1:
             raise ValueError("the PhaseKV decode path supports batch=1 only")
         s, kp = _fp16_segment(hot_k[0], hot_v[0])
         segs.append(s), keep.extend(kp)
+        hkv, hd = hot_k.shape[1], hot_k.shape[3]
     return segs, keep, hkv, hd
 
 
