@@ -53,7 +53,8 @@ def find_nvcc() -> str:
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not is_stale():
         return LIB_PATH
-    cmd = [find_nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", LIB_PATH, *sources()]
+    extra = os.environ.get("PKV_NVCC_FLAGS", "").split()  # e.g. -DPKV_MMA_WARPS=16 for tuning experiments
+    cmd = [find_nvcc(), *NVCC_FLAGS, *extra, *(["-Xptxas", "-v"] if verbose else []), "-o", LIB_PATH, *sources()]
     # nvcc hands host code to the compiler named by CC/CXX only if told to; use the system g++.
     env = dict(os.environ)
     env.pop("CC", None)

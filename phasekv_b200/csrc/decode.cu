@@ -223,6 +223,7 @@ merge_partials_kernel(const float* __restrict__ pm, const float* __restrict__ pl
     // When launched as a programmatic dependent of the split-K kernel this grid may already be resident while
     // that kernel finishes; wait here for its results (a no-op for an ordinary launch).
     cudaGridDependencySynchronize();
+    cudaTriggerProgrammaticLaunchCompletion();  // the next kernel of the stream may start its own prologue
     const int nvec = hd >> 2;  // float4 per row (hd % 4 == 0 is checked on the host)
     const bool v0 = lane < nvec, v1 = lane + 32 < nvec;
 

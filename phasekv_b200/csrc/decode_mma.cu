@@ -455,6 +455,8 @@ __device__ __forceinline__ void run_cta_fp16(const MmaArgs& a, const SegDev& sg,
     const long long tile0 = (long long)split * sg.split_len;
     const long long tile1 = min(n_tiles, tile0 + sg.split_len);
     const int h0 = kvh * a.G;
+    cudaGridDependencySynchronize();  // the hot tier and q may have been written by the previous kernel
+    cudaTriggerProgrammaticLaunchCompletion();
     WarpState st;
     init_state(st);
     // q as the B operand in natural channel order: k = 2t, 2t+1 | 2t+8, 2t+9 of each 16-channel step
@@ -511,6 +513,7 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
         if (wid < n_sub) vsrc.issue(tile0 + wid, vring);
         cp_async_commit();
     }
+    cudaGridDependencySynchronize();  // everything below may depend on the previous kernel of the stream
     // q of the GQA group, staged once per CTA behind the first copies (rows padded against bank
     // conflicts; zero rows for heads >= G)
     if (tid < 128) {
@@ -588,8 +591,20 @@ int launch(const MmaArgs& a, int work, int Hkv, cudaStream_t stream) {
         PKV_CUDA_TRY(cudaFuncSetAttribute(decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         configured[dev] = true;
     }
-    decode_mma_kernel<<<dim3((unsigned)work, (unsigned)Hkv), NTHREADS, kSmemBytes, stream>>>(a);
-    PKV_LAUNCH_CHECK();
+    // Programmatic dependent launch: the grid may become resident while the previous kernel of the stream
+    // drains.  Until cudaGridDependencySynchronize() it only touches the frozen packed segments, which no
+    // earlier kernel of a decode step writes; q, the hot tier and the scratch are touched after it.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)work, (unsigned)Hkv);
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    PKV_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_mma_kernel, a));
     return PKV_OK;
 }
 
