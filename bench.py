@@ -47,6 +47,8 @@ def parse_args():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--prompt", type=int, default=32768, help="prompt-tier tokens per layer")
     ap.add_argument("--layers", type=int, default=28)
+    ap.add_argument("--workload", choices=("decode", "pack"), default="decode",
+                    help="decode: the headline decode-attention step; pack: prefill quantise+pack and cold cooling")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the context sweep, the SDPA baselines and the CPU baseline")
     return ap.parse_args()
@@ -328,11 +330,64 @@ def workload_config(args):
             "parallelism": "batch-sharded, no collective"}
 
 
+# ----------------------------------------------------------------------------- pack workload
+def run_pack_workload(args):
+    """Prefill quantise+pack of 32768 tokens x 4 KV heads x 128 dims (K along tokens, V along dims) at
+    2/4/8 bits over rotating input buffers larger than L2, and the lazy cold-tier cooling step
+    (64 aged tokens -> top 32 by value norm, 4-bit).  One JSON line; value = 2-bit K+V pack GB/s."""
+    import torch
+    from phasekv_b200 import workloads
+    from phasekv_b200.cold_tier import select_and_pack_cold
+    from phasekv_b200.kernels import packing
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    s = workloads.QWEN2_5_7B
+    S, copies = 32768, 6  # 6 x (K + V) x 33.5 MB = 403 MB of input
+    gen = torch.Generator(device=dev).manual_seed(5)
+    ks = [torch.randn(1, s.num_kv_heads, S, s.head_dim, generator=gen, device=dev).half() for _ in range(copies)]
+    vs = [torch.randn(1, s.num_kv_heads, S, s.head_dim, generator=gen, device=dev).half() for _ in range(copies)]
+    peak, peak_kind = measured_peak()
+    res = {}
+    for bits in (2, 4, 8):
+        def step():
+            for k, v in zip(ks, vs):
+                packing.quantize_pack(k, bits, -2, GROUP)
+                packing.quantize_pack(v, bits, -1, GROUP)
+        reps = args.steps // 10 + 1
+        ms = time_graph(torch, step, reps, 3)  # graph replay: no Python between the launches
+        us = ms * 1e3 / copies
+        nbytes = 2 * (S * s.num_kv_heads * s.head_dim) * 2 + 2 * S * s.num_kv_heads * (s.head_dim * bits // 8 + 4 * s.head_dim // GROUP)
+        res[str(bits)] = {"us_per_kv_pack": us, "GBps": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak,
+                          "algorithmic_bytes": nbytes}
+    hot_k = torch.randn(1, s.num_kv_heads, 192, s.head_dim, generator=gen, device=dev).half()
+    hot_v = torch.randn(1, s.num_kv_heads, 192, s.head_dim, generator=gen, device=dev).half()
+    for _ in range(3):
+        select_and_pack_cold(hot_k.clone(), hot_v.clone(), 192, 64, 32, 4, GROUP)
+    bufs = [(hot_k.clone(), hot_v.clone()) for _ in range(50)]
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for bk, bv in bufs:
+        select_and_pack_cold(bk, bv, 192, 64, 32, 4, GROUP)
+    e1.record()
+    e1.synchronize()
+    print(json.dumps({"metric": "quantize_pack_GBps", "value": res["2"]["GBps"], "unit": UNIT, "n_gpus": 1,
+                      "steps": args.steps, "warmup": 3, "higher_is_better": True, "data": "synthetic",
+                      "config": {"workload": "prefill quantise+pack, 32768 tok x 4 KV heads x 128 dims, K along tokens + V along dims, gs 32",
+                                 "l2_policy": "rotating inputs larger than L2"},
+                      "by_bits": res, "peak": peak, "peak_source": f"of {peak_kind}",
+                      "cold_cooling_us": e0.elapsed_time(e1) * 1e3 / len(bufs),
+                      "cold_config": "64 aged of 192 hot tokens -> keep 32, 4-bit, 4 KV heads, one launch (python call included)"}))
+
+
 # ----------------------------------------------------------------------------- main arm
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.workload == "pack":
+        run_pack_workload(args)
         return
     import torch
     import torch.distributed as dist

@@ -31,8 +31,9 @@ __device__ void quantize_run(Load load, int a_begin, int a_end, int A, int gs, u
             hi = fmaxf(hi, v);
         }
         const float sc = __fdiv_rn(fmaxf(__fsub_rn(hi, lo), 1e-8f), QMAX);
+        const float inv = __frcp_rn(sc);
         for (int a = g0; a < g1; ++a) {
-            float qv = rintf(__fdiv_rn(__fsub_rn(load(a), lo), sc));
+            float qv = quantise_round(__fsub_rn(load(a), lo), sc, inv);
             qv = fminf(fmaxf(qv, 0.f), QMAX);
             const int pos = a % VPB;
             cur |= (unsigned)qv << (pos * BITS);

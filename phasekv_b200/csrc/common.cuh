@@ -40,4 +40,16 @@ __device__ __forceinline__ unsigned extract_code_rt(unsigned byte, unsigned idx_
     return (byte >> (idx_in_byte * bits)) & ((1u << bits) - 1u);
 }
 
+
+// rint((d / sc)) with the quotient rounded to float32 first, exactly as IEEE division gives it, at
+// the cost of a multiply in the common case: d * (1/sc) is within two ulp of the true quotient, so
+// the two can only round to different integers when the product lies within a hair of a half-integer;
+// only then is the real division done.  (Quotients here are at most 255, two ulp < 3.1e-5.)
+__device__ __forceinline__ float quantise_round(float d, float sc, float inv_sc) {
+    const float r = d * inv_sc;
+    const float t = rintf(r);
+    if (fabsf(r - t) > 0.4999f) return rintf(__fdiv_rn(d, sc));
+    return t;
+}
+
 }  // namespace pkv

@@ -77,9 +77,10 @@ __global__ void quantize_pack_kernel(const __half* __restrict__ x, int64_t outer
             hi = fmaxf(hi, v);
         }
         const float sc = __fdiv_rn(fmaxf(__fsub_rn(hi, lo), 1e-8f), QMAX);
+        const float inv = __frcp_rn(sc);
         for (int64_t a = g0; a < g1; ++a) {
             const float v = __half2float(xp[a * inner]);
-            float qv = rintf(__fdiv_rn(__fsub_rn(v, lo), sc));
+            float qv = quantise_round(__fsub_rn(v, lo), sc, inv);
             qv = fminf(fmaxf(qv, 0.f), QMAX);
             const int pos = (int)(a % VPB);
             cur |= (unsigned)qv << (pos * BITS);
@@ -132,12 +133,13 @@ __global__ void quantize_pack_lastdim32_kernel(const __half* __restrict__ x, int
         hi = fmaxf(hi, v[i]);
     }
     const float sc = __fdiv_rn(fmaxf(__fsub_rn(hi, lo), 1e-8f), QMAX);
+    const float inv = __frcp_rn(sc);
     unsigned w[BITS];  // 32 codes * BITS bits = BITS 32-bit words
 #pragma unroll
     for (int i = 0; i < BITS; ++i) w[i] = 0;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-        float qv = rintf(__fdiv_rn(__fsub_rn(v[i], lo), sc));
+        float qv = quantise_round(__fsub_rn(v[i], lo), sc, inv);
         qv = fminf(fmaxf(qv, 0.f), QMAX);
         w[(i * BITS) / 32] |= (unsigned)qv << ((i * BITS) % 32);
     }
@@ -151,6 +153,84 @@ __global__ void quantize_pack_lastdim32_kernel(const __half* __restrict__ x, int
     }
     scale[g] = __float2half_rn(sc);
     mins[g] = __float2half_rn(lo);
+}
+
+// Fast path for the key layout: the axis is strided (inner = head_dim contiguous), the group is 32
+// positions and the axis length a multiple of 32.  One thread owns 8 neighbouring channels of one
+// group: it reads the group's 32 rows twice with 16-byte loads (the second pass hits L1), keeps
+// min/max and the packed words of its 8 channels in registers and writes 4*BITS bytes per channel.
+// This is the transpose from token-major input to channel-major packed output.
+template <int BITS>
+__global__ void __launch_bounds__(128)
+quantize_pack_axis32_kernel(const __half* __restrict__ x, int64_t outer, int64_t A, int64_t inner,
+                            uint8_t* __restrict__ packed, __half* __restrict__ scale,
+                            __half* __restrict__ mins) {
+    constexpr float QMAX = (float)((1 << BITS) - 1);
+    const int64_t chunks = inner / 8, groups = A / 32;
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid >= outer * groups * chunks) return;
+    const int64_t j8 = tid % chunks;
+    const int64_t g = (tid / chunks) % groups;
+    const int64_t o = tid / (chunks * groups);
+    const uint4* src = reinterpret_cast<const uint4*>(x + (o * A + g * 32) * inner + j8 * 8);
+    const int64_t row_stride = inner / 8;  // in uint4
+
+    float lo[8], hi[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        lo[c] = INFINITY;
+        hi[c] = -INFINITY;
+    }
+#pragma unroll 8
+    for (int a = 0; a < 32; ++a) {
+        const uint4 raw = __ldg(src + a * row_stride);
+        const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const float2 f = __half22float2(h2[c]);
+            lo[2 * c] = fminf(lo[2 * c], f.x);
+            hi[2 * c] = fmaxf(hi[2 * c], f.x);
+            lo[2 * c + 1] = fminf(lo[2 * c + 1], f.y);
+            hi[2 * c + 1] = fmaxf(hi[2 * c + 1], f.y);
+        }
+    }
+    float sc[8], inv[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        sc[c] = __fdiv_rn(fmaxf(__fsub_rn(hi[c], lo[c]), 1e-8f), QMAX);
+        inv[c] = __frcp_rn(sc[c]);
+    }
+
+    unsigned w[8][BITS];  // per channel: 32 codes of BITS bits
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+#pragma unroll
+        for (int k = 0; k < BITS; ++k) w[c][k] = 0u;
+#pragma unroll
+    for (int a = 0; a < 32; ++a) {
+        const uint4 raw = __ldg(src + a * row_stride);
+        const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const float2 f = __half22float2(h2[c]);
+            float q0 = quantise_round(__fsub_rn(f.x, lo[2 * c]), sc[2 * c], inv[2 * c]);
+            float q1 = quantise_round(__fsub_rn(f.y, lo[2 * c + 1]), sc[2 * c + 1], inv[2 * c + 1]);
+            q0 = fminf(fmaxf(q0, 0.f), QMAX);
+            q1 = fminf(fmaxf(q1, 0.f), QMAX);
+            w[2 * c][(a * BITS) / 32] |= (unsigned)q0 << ((a * BITS) % 32);
+            w[2 * c + 1][(a * BITS) / 32] |= (unsigned)q1 << ((a * BITS) % 32);
+        }
+    }
+    const int64_t nb = A * BITS / 8, ng = groups;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const int64_t row = o * inner + j8 * 8 + c;
+        uint2* dst = reinterpret_cast<uint2*>(packed + row * nb + g * (4 * BITS));
+#pragma unroll
+        for (int k = 0; k < BITS; k += 2) dst[k / 2] = make_uint2(w[c][k], w[c][k + 1]);
+        scale[row * ng + g] = __float2half_rn(sc[c]);
+        mins[row * ng + g] = __float2half_rn(lo[c]);
+    }
 }
 
 template <int BITS>
@@ -268,6 +348,16 @@ int pkv_quantize_pack(const void* x, int64_t outer, int64_t axis_len, int64_t in
         if (bits == 2) quantize_pack_lastdim32_kernel<2><<<grid, 128, 0, s>>>(xh, n_groups, packed, sc, mn);
         else if (bits == 4) quantize_pack_lastdim32_kernel<4><<<grid, 128, 0, s>>>(xh, n_groups, packed, sc, mn);
         else quantize_pack_lastdim32_kernel<8><<<grid, 128, 0, s>>>(xh, n_groups, packed, sc, mn);
+        PKV_LAUNCH_CHECK();
+        return PKV_OK;
+    }
+
+    if (inner % 8 == 0 && inner > 1 && group == 32 && axis_len % 32 == 0 && aligned) {
+        const int64_t n = outer * (axis_len / 32) * (inner / 8);
+        const unsigned grid = (unsigned)ceil_div(n, 128);
+        if (bits == 2) quantize_pack_axis32_kernel<2><<<grid, 128, 0, s>>>(xh, outer, axis_len, inner, packed, sc, mn);
+        else if (bits == 4) quantize_pack_axis32_kernel<4><<<grid, 128, 0, s>>>(xh, outer, axis_len, inner, packed, sc, mn);
+        else quantize_pack_axis32_kernel<8><<<grid, 128, 0, s>>>(xh, outer, axis_len, inner, packed, sc, mn);
         PKV_LAUNCH_CHECK();
         return PKV_OK;
     }
