@@ -29,14 +29,64 @@ struct KSrc {
     const char* km;
     long long nbK, ngK2;  // bytes per key code row / per key scale row
     bool meta16;          // scale rows can move in 16-byte copies
+    bool aligned;         // code rows start on 16 bytes: cp.async path; otherwise load_sync
 
     __device__ KSrc(const SegDev& sg, int kvh, long long tile0) {
-        nbK = sg.S * BITS / 8;
-        ngK2 = sg.S / 32 * 2;
+        nbK = (sg.S * BITS + 7) / 8;
+        ngK2 = (sg.S + 31) / 32 * 2;
         kp = sg.kp + (size_t)kvh * HD * nbK;
         ks = reinterpret_cast<const char*>(sg.ks) + (size_t)kvh * HD * ngK2;
         km = reinterpret_cast<const char*>(sg.km) + (size_t)kvh * HD * ngK2;
-        meta16 = (ngK2 & 15) == 0 && (tile0 & 3) == 0;
+        aligned = (nbK & 15) == 0 && (ngK2 & 3) == 0 && sg.S % C::T == 0;
+        meta16 = aligned && (ngK2 & 15) == 0 && (tile0 & 3) == 0;
+    }
+
+    // Ragged segments (any length, so any row alignment): the same K buffer image built with ordinary
+    // loads.  A 16-byte chunk is read as aligned 32-bit words and realigned with funnel shifts; bytes past
+    // the end of a row come out as the neighbouring row's bytes or zero and belong to masked tokens only.
+    // Reads stay inside [tensor start, tensor end rounded up to 4 bytes).
+    __device__ __forceinline__ void load_sync(long long tile, int n_sub, char* kb, int tid) const {
+        const int cpr = n_sub * (C::KRB / 16);
+        for (int idx = tid; idx < HD * cpr; idx += NTHREADS) {
+            const int row = idx / cpr, ch = idx - row * cpr;
+            const long long off = tile * C::KRB + 16 * ch;
+            const long long valid = nbK - off;  // bytes of this row at and after the chunk start
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (valid > 0) {
+                const uintptr_t ga = reinterpret_cast<uintptr_t>(kp + (size_t)row * nbK + off);
+                const unsigned mis = (unsigned)(ga & 3u);
+                const unsigned* wp = reinterpret_cast<const unsigned*>(ga - mis);
+                const int last = (int)((mis + (valid < 16 ? valid : 16) - 1) >> 2);
+                unsigned w[5];
+#pragma unroll
+                for (int i = 0; i < 5; ++i) w[i] = i <= last ? __ldg(wp + i) : 0u;
+                const unsigned sh = 8u * mis;
+                v.x = __funnelshift_r(w[0], w[1], sh);
+                v.y = __funnelshift_r(w[1], w[2], sh);
+                v.z = __funnelshift_r(w[2], w[3], sh);
+                v.w = __funnelshift_r(w[3], w[4], sh);
+            }
+            *reinterpret_cast<uint4*>(kb + row * C::KROW + 16 * ch) = v;
+        }
+        const long long moff = tile * (C::NG * 2);
+        for (int idx = tid; idx < HD * n_sub; idx += NTHREADS) {
+            const int row = idx / n_sub, w = idx - row * n_sub;
+            const long long off = moff + 4 * w;
+            const long long valid = ngK2 - off;
+            unsigned sv = 0u, mv = 0u;
+            if (valid > 0) {
+                const unsigned short* sp = reinterpret_cast<const unsigned short*>(ks + (size_t)row * ngK2 + off);
+                const unsigned short* mp = reinterpret_cast<const unsigned short*>(km + (size_t)row * ngK2 + off);
+                sv = __ldg(sp);
+                mv = __ldg(mp);
+                if (valid > 2) {
+                    sv |= (unsigned)__ldg(sp + 1) << 16;
+                    mv |= (unsigned)__ldg(mp + 1) << 16;
+                }
+            }
+            *reinterpret_cast<unsigned*>(kb + C::OFF_KS + row * C::MROW + 4 * w) = sv;
+            *reinterpret_cast<unsigned*>(kb + C::OFF_KM + row * C::MROW + 4 * w) = mv;
+        }
     }
 
     // keys of tiles [tile, tile + n_sub) into the K buffer at `kb`; every thread of the CTA takes part.
@@ -85,8 +135,10 @@ struct VSrc {
     const char* vm;
     unsigned d_vc;
     int lane;
+    bool meta16;  // this head's scale rows start on 16 bytes
 
     __device__ VSrc(const SegDev& sg, int kvh, int lane_) : lane(lane_) {
+        meta16 = (((long long)kvh * sg.S) & 1) == 0;
         vc = sg.vp + (size_t)kvh * sg.S * (C::VWPT * 4) + 16 * lane;
         const int lt = lane / CPT;
         d_vc = (lt + lt / 8) * (C::VWPT * 4) + 16 * (lane % CPT);
@@ -94,23 +146,44 @@ struct VSrc {
         vm = reinterpret_cast<const char*>(sg.vm + (size_t)kvh * sg.S * 4) + 16 * lane;
     }
 
-    // values of one tile into the stage at `sa`; one warp
-    __device__ __forceinline__ void issue(long long tile, unsigned sa) const {
+    // values of one tile into the stage at `sa`; one warp.  Rows of tokens >= n_valid are zero-filled
+    // (their probabilities are zero, but garbage scales could be NaN).
+    __device__ __forceinline__ void issue(long long tile, unsigned sa, int n_valid) const {
         const uint8_t* v = vc + tile * (C::T * C::VWPT * 4);
-#pragma unroll
-        for (int it = 0; it < C::T / TPI; ++it) {
-            const int tok0 = it * TPI;
-            cp_async16(sa + d_vc + (tok0 + tok0 / 8) * (C::VWPT * 4), v + 512 * it);
-        }
         const long long off = tile * (C::T * 8);
-        cp_async16(sa + C::OFF_VS + 16 * lane, vs + off);
-        cp_async16(sa + C::OFF_VM + 16 * lane, vm + off);
+        if (n_valid >= C::T && meta16) {
+#pragma unroll
+            for (int it = 0; it < C::T / TPI; ++it) {
+                const int tok0 = it * TPI;
+                cp_async16(sa + d_vc + (tok0 + tok0 / 8) * (C::VWPT * 4), v + 512 * it);
+            }
+            cp_async16(sa + C::OFF_VS + 16 * lane, vs + off);
+            cp_async16(sa + C::OFF_VM + 16 * lane, vm + off);
+        } else {
+            const int lt = lane / CPT;
+#pragma unroll
+            for (int it = 0; it < C::T / TPI; ++it) {
+                const int tok0 = it * TPI;
+                const bool ok = tok0 + lt < n_valid;
+                cp_async16_zfill(sa + d_vc + (tok0 + tok0 / 8) * (C::VWPT * 4), ok ? v + 512 * it : vc, ok ? 16u : 0u);
+            }
+            // scale / zero rows are 8 bytes per token and, for an odd number of tokens per head, only 8-byte
+            // aligned: two 8-byte copies per lane (tokens lane and lane + 32)
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int tok = lane + 32 * k;
+                const unsigned nb = tok < n_valid ? 8u : 0u;
+                const long long so = nb ? off + 8 * tok - 16 * lane : -16 * (long long)lane;
+                cp_async8_zfill(sa + C::OFF_VS + 8 * tok, vs + so, nb);
+                cp_async8_zfill(sa + C::OFF_VM + 8 * tok, vm + so, nb);
+            }
+        }
     }
 };
 
 template <int BITS>
 __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char* sa, const char* q_lane, float c_qk,
-                                             WarpState& st, const LaneSel<BITS>& ls, int lane) {
+                                             WarpState& st, const LaneSel<BITS>& ls, int lane, int n_valid) {
     using C = Cfg<BITS>;
     const int g = lane >> 2, t = lane & 3;
     const unsigned sel_lo = 0x5410u, sel_hi = 0x7632u;
@@ -175,6 +248,11 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
             s[1] = (s[1] * unscale<BITS>(2 * j) + bias1) * c_qk;
             s[2] = (s[2] * unscale<BITS>(2 * j + 1) + bias0) * c_qk;
             s[3] = (s[3] * unscale<BITS>(2 * j + 1) + bias1) * c_qk;
+            if (n_valid < C::T) {  // last tile of a ragged segment: rows are tokens 32G + 4g + 2j (+1)
+                const int tok = 32 * G + 4 * g + 2 * j;
+                if (tok >= n_valid) s[0] = s[1] = -INFINITY;
+                if (tok + 1 >= n_valid) s[2] = s[3] = -INFINITY;
+            }
             mx[0] = fmaxf(mx[0], fmaxf(s[0], s[2]));
             mx[1] = fmaxf(mx[1], fmaxf(s[1], s[3]));
         }
@@ -489,10 +567,12 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const unsigned smem_base = (unsigned)__cvta_generic_to_shared(smem_f);
-    const long long n_tiles = sg.S / C::T;
+    const long long n_tiles = (sg.S + C::T - 1) / C::T;
     const long long tile0 = (long long)split * sg.split_len;
     const long long tile1 = min(n_tiles, tile0 + sg.split_len);
     const int h0 = kvh * a.G;
+    // tokens of tile `tl` that exist (the last tile of a ragged segment is partial)
+    auto valid_of = [&](long long tl) { return (int)min((long long)C::T, sg.S - tl * C::T); };
 
     WarpState st;
     init_state(st);
@@ -506,11 +586,11 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
     const int n_tiles_cta = (int)(tile1 - tile0);
     const int n_super = (n_tiles_cta + C::NSUB - 1) / C::NSUB;
 
-    // super-tile 0
-    {
+    // super-tile 0 (frozen packed data: may be fetched before the dependency wait)
+    if (ksrc.aligned) {
         const int n_sub = min(C::NSUB, n_tiles_cta);
         ksrc.issue(tile0, n_sub, kbuf, tid);
-        if (wid < n_sub) vsrc.issue(tile0 + wid, vring);
+        if (wid < n_sub) vsrc.issue(tile0 + wid, vring, valid_of(tile0 + wid));
         cp_async_commit();
     }
     cudaGridDependencySynchronize();  // everything below may depend on the previous kernel of the stream
@@ -528,20 +608,34 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
     const LaneSel<BITS> ls(g);
     const float c_qk = a.sm_scale * kLog2e;
     for (int sp = 0; sp < n_super; ++sp) {
-        cp_async_wait<0>();
-        __syncthreads();  // super-tile sp has landed for everyone; everyone is done with sp - 1
         const int n_sub = min(C::NSUB, n_tiles_cta - sp * C::NSUB);
-        if (sp + 1 < n_super) {
-            const long long next = tile0 + (long long)(sp + 1) * C::NSUB;
-            const int n_next = min(C::NSUB, n_tiles_cta - (sp + 1) * C::NSUB);
-            ksrc.issue(next, n_next, kbuf + ((sp + 1) & 1) * C::KBUF_BYTES, tid);
-            if (wid < n_next) vsrc.issue(next + wid, vring + ((sp + 1) & 1) * C::VSTAGE_BYTES);
+        const long long first = tile0 + (long long)sp * C::NSUB;
+        int buf = sp & 1;
+        if (ksrc.aligned) {
+            cp_async_wait<0>();
+            __syncthreads();  // super-tile sp has landed for everyone; everyone is done with sp - 1
+            if (sp + 1 < n_super) {
+                const long long next = first + C::NSUB;
+                const int n_next = min(C::NSUB, n_tiles_cta - (sp + 1) * C::NSUB);
+                ksrc.issue(next, n_next, kbuf + ((sp + 1) & 1) * C::KBUF_BYTES, tid);
+                if (wid < n_next)
+                    vsrc.issue(next + wid, vring + ((sp + 1) & 1) * C::VSTAGE_BYTES, valid_of(next + wid));
+                cp_async_commit();
+            }
+        } else {
+            // ragged segment: keys through ordinary loads into buffer 0, no overlap with the compute
+            buf = 0;
+            __syncthreads();  // everyone is done with the previous super-tile
+            if (wid < n_sub) vsrc.issue(first + wid, vring, valid_of(first + wid));
             cp_async_commit();
+            ksrc.load_sync(first, n_sub, reinterpret_cast<char*>(smem_f) + kQBytes, tid);
+            cp_async_wait<0>();
+            __syncthreads();
         }
         if (wid < n_sub)
-            compute_tile<BITS>(smem_c + kQBytes + (sp & 1) * C::KBUF_BYTES, wid,
-                               smem_c + kQBytes + 2 * C::KBUF_BYTES + (wid * NSTAGE + (sp & 1)) * C::VSTAGE_BYTES,
-                               smem_c + g * kQRowBytes + 4 * t, c_qk, st, ls, lane);
+            compute_tile<BITS>(smem_c + kQBytes + buf * C::KBUF_BYTES, wid,
+                               smem_c + kQBytes + 2 * C::KBUF_BYTES + (wid * NSTAGE + buf) * C::VSTAGE_BYTES,
+                               smem_c + g * kQRowBytes + 4 * t, c_qk, st, ls, lane, valid_of(first + wid));
     }
 
     finish_cta<BITS>(a, st, kvh, smem_f);
@@ -570,7 +664,6 @@ bool eligible(const pkv_segment_t& s, int Hq, int Hkv, int hd) {
     }
     if (s.kind != PKV_SEG_KIVI) return false;
     if (s.k_bits != s.v_bits || s.k_group != 32 || s.v_group != 32) return false;
-    if (s.seq_len % tile_tokens(s.k_bits) != 0) return false;
     const uintptr_t bits = reinterpret_cast<uintptr_t>(s.k_packed) | reinterpret_cast<uintptr_t>(s.k_scale) |
                            reinterpret_cast<uintptr_t>(s.k_mins) | reinterpret_cast<uintptr_t>(s.v_packed) |
                            reinterpret_cast<uintptr_t>(s.v_scale) | reinterpret_cast<uintptr_t>(s.v_mins);
@@ -580,7 +673,7 @@ bool eligible(const pkv_segment_t& s, int Hq, int Hkv, int hd) {
 // Tiles of a segment as the tensor-core kernel counts them.
 long long tiles_of(const pkv_segment_t& s) {
     if (s.kind == PKV_SEG_FP16) return (s.seq_len + TH - 1) / TH;
-    return s.seq_len / tile_tokens(s.k_bits);
+    return (s.seq_len + tile_tokens(s.k_bits) - 1) / tile_tokens(s.k_bits);
 }
 
 int launch(const MmaArgs& a, int work, int Hkv, cudaStream_t stream) {

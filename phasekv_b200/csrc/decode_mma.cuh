@@ -122,6 +122,9 @@ __device__ __forceinline__ void cp_async16_ca(unsigned smem_addr, const void* g)
 __device__ __forceinline__ void cp_async16_zfill(unsigned smem_addr, const void* g, unsigned src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr), "l"(g), "r"(src_bytes));
 }
+__device__ __forceinline__ void cp_async8_zfill(unsigned smem_addr, const void* g, unsigned src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(smem_addr), "l"(g), "r"(src_bytes));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
