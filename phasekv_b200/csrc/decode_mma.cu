@@ -219,8 +219,8 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
             for (int e = 0; e < 2; ++e) {
                 const int G = e;
                 const unsigned sel = e ? sel_hi : sel_lo;
-                const unsigned b0 = hmul2(qf0, prmt(s01.x, s01.y, sel));
-                const unsigned b1 = hmul2(qf1, prmt(s23.x, s23.y, sel));
+                const unsigned s0p = prmt(s01.x, s01.y, sel), s1p = prmt(s23.x, s23.y, sel);
+                const unsigned b0 = hmul2(qf0, s0p), b1 = hmul2(qf1, s1p);
                 uint4 kc;
                 kc.x = ldp32(k_lane + (16 * kk + 0) * C::KROW + 4 * G * BITS);
                 kc.y = ldp32(k_lane + (16 * kk + 1) * C::KROW + 4 * G * BITS);
@@ -231,6 +231,12 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
                 extract4<BITS>(kc.z, kc.w, ls, rb);
                 mma16816(sacc[2 * G + 0], ra[0], ra[1], rb[0], rb[1], b0, b1);
                 mma16816(sacc[2 * G + 1], ra[2], ra[3], rb[2], rb[3], b0, b1);
+                // q*scale does not fit float16 exactly; its rounding error (2^-11 of products that reach
+                // tens on outlier channels) would dominate the score error, so the residual goes through
+                // the tensor core as well (the A operands are already built)
+                const unsigned b0l = hfma2_residual(qf0, s0p, b0), b1l = hfma2_residual(qf1, s1p, b1);
+                mma16816(sacc[2 * G + 0], ra[0], ra[1], rb[0], rb[1], b0l, b1l);
+                mma16816(sacc[2 * G + 1], ra[2], ra[3], rb[2], rb[3], b0l, b1l);
             }
         }
     }
@@ -333,6 +339,10 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
                 extract4<BITS>(vw[2][d], vw[3][d], ls, rb);
                 mma16816(st.o[d][0], ra[0], ra[1], rb[0], rb[1], b0, b1);
                 mma16816(st.o[d][1], ra[2], ra[3], rb[2], rb[3], b0, b1);
+                // same for p*scale: feed what float16 rounding dropped (matters when few tokens dominate)
+                const unsigned b0l = hfma2_residual(pb0, s01, b0), b1l = hfma2_residual(pb1, s23, b1);
+                mma16816(st.o[d][0], ra[0], ra[1], rb[0], rb[1], b0l, b1l);
+                mma16816(st.o[d][1], ra[2], ra[3], rb[2], rb[3], b0l, b1l);
             }
         }
     }

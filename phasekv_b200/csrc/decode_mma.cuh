@@ -100,6 +100,12 @@ __device__ __forceinline__ unsigned hmul2(unsigned a, unsigned b) {
     asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
     return r;
 }
+// a * b - hi in one fused float16x2 operation: the part of the product that `hi` = rn(a * b) lost
+__device__ __forceinline__ unsigned hfma2_residual(unsigned a, unsigned b, unsigned hi) {
+    unsigned r;
+    asm("{.reg .b32 n; neg.f16x2 n, %3; fma.rn.f16x2 %0, %1, %2, n;}" : "=r"(r) : "r"(a), "r"(b), "r"(hi));
+    return r;
+}
 __device__ __forceinline__ unsigned pack_half2(float lo, float hi) {
     unsigned r;
     asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

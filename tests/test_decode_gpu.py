@@ -69,8 +69,8 @@ def test_kivi_layer_partial_shapes_of_the_reference_test(oracle, attn, length, h
     """The seven shapes and three launch options of the reference's
     tests/test_phasekv_launch_config.py:64-79 against a float32 dense-quantised softmax built in the
     test.  Shapes served by the SIMT kernel (head_dim != 128) meet the reference's own tolerance
-    (atol 3e-4, rtol 1e-3); the tensor-core kernel forms q*scale and p*scale in float16 (relative 2^-11
-    per product), so its bound is atol 1e-3, rtol 5e-3 here, still inside the 2e-3 / 1e-2 parity bar."""
+    (atol 3e-4, rtol 1e-3); the tensor-core kernel rounds the probabilities to float16 (relative 2^-12
+    on average), so its bound is atol 6e-4, rtol 2e-3 here, well inside the 2e-3 / 1e-2 parity bar."""
     gen = torch.Generator().manual_seed(42)
     q = torch.randn(heads, dim, generator=gen).half()
     kd = torch.randn(2, length, dim, generator=gen).half()
@@ -90,7 +90,7 @@ def test_kivi_layer_partial_shapes_of_the_reference_test(oracle, attn, length, h
     for options in ({}, {"num_splits": 8, "block_n": 64, "num_warps": 4}, {"num_splits": 3}):
         m, total, acc = attn._kivi_layer_partial(q.cuda(), kg, vg, heads, **options)
         assert m.shape == (heads,) and acc.shape == (heads, dim)
-        tol = dict(atol=1e-3, rtol=5e-3) if dim == 128 else dict(atol=3e-4, rtol=1e-3)
+        tol = dict(atol=6e-4, rtol=2e-3) if dim == 128 else dict(atol=3e-4, rtol=1e-3)
         torch.testing.assert_close((acc / total[:, None]).cpu(), expected, **tol)
 
 
@@ -106,17 +106,41 @@ def test_qwen7b_single_layer_contexts(oracle, attn, prompt):
     attention_close(out, ref)
 
 
+def _exact_attention(oracle, q, key, value, heads):
+    """float64 softmax attention over the exactly dequantised codes (no float16 rounding of K or V)."""
+    def dense(pt):
+        codes = oracle.unpack_low_bits(pt.packed, pt.bits, pt.axis_len).double()
+        groups = torch.arange(pt.axis_len) // pt.group_size
+        return (codes * pt.scale.double()[..., groups] + pt.mins.double()[..., groups]).movedim(-1, pt.axis)
+    rep = heads // key.orig_shape[1]
+    dk, dv = dense(key)[0].repeat_interleave(rep, 0), dense(value)[0].repeat_interleave(rep, 0)
+    probs = torch.softmax(torch.einsum("hd,hsd->hs", q.double(), dk) / q.shape[-1] ** 0.5, dim=-1)
+    return torch.einsum("hs,hsd->hd", probs, dv).float()
+
+
 @pytest.mark.parametrize("bits", [2, 4, 8])
 def test_ragged_lengths_on_the_tensor_core_path(oracle, attn, bits):
-    """Any segment length: rows that start on odd bytes, partial last groups, partial last bytes."""
+    """Any segment length: rows that start on odd bytes, partial last groups, partial last bytes.
+
+    With a handful of tokens the output is of order |v| ~ 2..3, where one float16 step is 2e-3, and the
+    dequantise-then-attend semantics itself (K and V rounded to float16 before the softmax, with outlier
+    channels near 30) sits up to 3e-3 away from the exact attention over the codes.  So these tiny cases
+    are held to the exact result (1.2e-3: float16 output rounding plus 2e-4), and to the oracle with the
+    parity bar widened by the oracle's own distance from exact."""
     from phasekv_b200 import workloads
     shape = workloads.QWEN2_5_7B
     for S in (1, 3, 31, 63, 64, 65, 127, 129, 1000, 4097, 8193):
         segs, hk, hv, q = _pack_tiers(oracle, shape, S, bits, [], 4, 0, seed=1000 * bits + S)
-        ref = oracle.segments_decode_reference(q[0, :, 0, :], segs, None, None, shape.num_q_heads)
-        out = attn.fused_phasekv_decode(q[0, :, 0, :].cuda(), make_tiers(segs), shape.num_q_heads)
+        q2 = q[0, :, 0, :]
+        ref = oracle.segments_decode_reference(q2, segs, None, None, shape.num_q_heads).float()
+        exact = _exact_attention(oracle, q2, segs[0][0], segs[0][1], shape.num_q_heads)
+        out = attn.fused_phasekv_decode(q2.cuda(), make_tiers(segs), shape.num_q_heads).float().cpu()
         assert torch.isfinite(out).all(), S
-        attention_close(out, ref)
+        e_exact = (out - exact).abs().max().item()
+        e_oracle = (out - ref).abs().max().item()
+        slack = (ref - exact).abs().max().item()
+        assert e_exact <= 1.2e-3, f"S={S} bits={bits}: {e_exact:.2e} from the exact attention"
+        assert e_oracle <= 2e-3 + slack, f"S={S} bits={bits}: {e_oracle:.2e} from the oracle (oracle-exact {slack:.2e})"
 
 
 def test_many_cold_segments_and_hot_capacity(oracle, attn):
