@@ -8,6 +8,10 @@ namespace mma {
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
+#ifndef PKV_K_UNROLL
+#define PKV_K_UNROLL 4
+#endif
+constexpr int kKUnroll = PKV_K_UNROLL;  // k-steps of the score loop unrolled together
 
 struct WarpState {
     float m[2];        // running max (log2 domain) of heads 2t, 2t+1
@@ -198,7 +202,8 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
     const char* k_lane = kb + 2 * t * C::KROW + sub * C::KRB + 4 * ls.word;
     const char* s_lane = kb + C::OFF_KS + 2 * t * C::MROW + 4 * sub;
     const char* m_lane = kb + C::OFF_KM + 2 * t * C::MROW + 4 * sub;
-#pragma unroll
+    // partially unrolled: the fully unrolled loop made the kernel instruction-fetch bound on short contexts
+#pragma unroll kKUnroll
     for (int kk = 0; kk < 8; ++kk) {
         const unsigned qf0 = ldp32(q_lane + 32 * kk);       // head g, channels 16kk + 2t, +1
         const unsigned qf1 = ldp32(q_lane + 32 * kk + 16);  // channels 16kk + 2t + 8, +9
