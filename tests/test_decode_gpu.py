@@ -143,6 +143,34 @@ def test_ragged_lengths_on_the_tensor_core_path(oracle, attn, bits):
         assert e_oracle <= 2e-3 + slack, f"S={S} bits={bits}: {e_oracle:.2e} from the oracle (oracle-exact {slack:.2e})"
 
 
+def test_batched_serving_shapes_with_jittered_lengths(oracle, attn):
+    """The batched-serving configuration (8192 prompt @2-bit + 512 cold @4-bit + 128 hot, lengths jittered
+    by +-25 % per sequence): sequences are independent, so the batch is a loop over sequences; a sample of
+    them (shortest, longest, six more) is checked against the oracle."""
+    from phasekv_b200 import workloads
+    shape = workloads.QWEN2_5_7B
+    lengths = workloads.jittered_lengths(0, 64, 8192, 512, 128, hot_capacity=192)
+    order = sorted(range(64), key=lambda i: lengths[i][0])
+    sample = [order[0], order[-1]] + order[5:60:10]
+    assert len({lengths[i] for i in sample}) >= 6 and any(lengths[i][0] % 64 for i in sample)
+    for i in sample:
+        p, c, h = lengths[i]
+        segs, hk, hv, q = _pack_tiers(oracle, shape, p, 2, [c], 4, h, seed=workloads.layer_seed(0, 3, i))
+        ref = oracle.segments_decode_reference(q[0, :, 0, :], segs, hk, hv, shape.num_q_heads)
+        out = attn.fused_phasekv_decode(q[0, :, 0, :].cuda(), make_tiers(segs, hk, hv, hot_len=h), shape.num_q_heads)
+        attention_close(out, ref)
+
+
+def test_long_context_262144_tokens(oracle, attn):
+    """The long-context configuration on one GPU: 262144 prompt tokens @2-bit + 1024 cold @4-bit + 128 hot."""
+    from phasekv_b200 import workloads
+    shape = workloads.QWEN2_5_7B
+    segs, hk, hv, q = _pack_tiers(oracle, shape, 262144, 2, [1024], 4, 128, seed=262144)
+    ref = oracle.segments_decode_reference(q[0, :, 0, :], segs, hk, hv, shape.num_q_heads)
+    out = attn.fused_phasekv_decode(q[0, :, 0, :].cuda(), make_tiers(segs, hk, hv, hot_len=128), shape.num_q_heads)
+    attention_close(out, ref)
+
+
 def test_many_cold_segments_and_hot_capacity(oracle, attn):
     """cold = 8 frozen segments of 64 tokens, hot buffer with spare capacity (only hot_len valid)."""
     from phasekv_b200 import workloads
