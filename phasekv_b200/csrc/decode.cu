@@ -227,24 +227,19 @@ merge_partials_kernel(const float* __restrict__ pm, const float* __restrict__ pl
     const int nvec = hd >> 2;  // float4 per row (hd % 4 == 0 is checked on the host)
     const bool v0 = lane < nvec, v1 = lane + 32 < nvec;
 
-    // global max over all parts (each thread looks at a strided subset; loads independent)
-    float mx = -INFINITY;
-    for (int p = tid; p < n_parts; p += kMergeThreads) mx = fmaxf(mx, __ldg(pm + (size_t)p * Hq + h));
-    mx = warp_max(mx);
-    if (lane == 0) red_m[wid] = mx;
-    __syncthreads();
-    mx = red_m[0];
-#pragma unroll
-    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red_m[w]);
-
+    // Every load of a batch (acc rows, m, l of up to 8 * kMergeMaxInflight parts) is issued before anything
+    // is reduced, so a typical merge (a few dozen parts) is one memory round trip.  Batches are combined
+    // with a running maximum, like the online softmax itself.
+    float run_m = -INFINITY;  // block-wide running max (identical in every thread)
     float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
     float ls = 0.f;
-    for (int base = wid; base < n_parts; base += 8 * kMergeMaxInflight) {
+    for (int base = 0; base < n_parts; base += 8 * kMergeMaxInflight) {
         float4 r0[kMergeMaxInflight], r1[kMergeMaxInflight];
         float wm[kMergeMaxInflight], wl[kMergeMaxInflight];
+        float mx = -INFINITY;
 #pragma unroll
         for (int u = 0; u < kMergeMaxInflight; ++u) {
-            const int p = base + 8 * u;
+            const int p = base + wid + 8 * u;
             r0[u] = r1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
             wm[u] = -INFINITY;
             wl[u] = 0.f;
@@ -257,6 +252,19 @@ merge_partials_kernel(const float* __restrict__ pm, const float* __restrict__ pl
             }
         }
 #pragma unroll
+        for (int u = 0; u < kMergeMaxInflight; ++u) mx = fmaxf(mx, wm[u]);
+        __syncthreads();  // red_m is free again
+        if (lane == 0) red_m[wid] = mx;
+        __syncthreads();
+        mx = run_m;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) mx = fmaxf(mx, red_m[w]);
+        const float rescale = expf(run_m - mx);  // first batch: exp(-inf) = 0 on zero accumulators
+        run_m = mx;
+        ls *= rescale;
+        a0.x *= rescale; a0.y *= rescale; a0.z *= rescale; a0.w *= rescale;
+        a1.x *= rescale; a1.y *= rescale; a1.z *= rescale; a1.w *= rescale;
+#pragma unroll
         for (int u = 0; u < kMergeMaxInflight; ++u) {
             const float wgt = expf(wm[u] - mx);  // -inf -> 0
             ls = fmaf(wgt, wl[u], ls);
@@ -266,6 +274,7 @@ merge_partials_kernel(const float* __restrict__ pm, const float* __restrict__ pl
             a1.z = fmaf(wgt, r1[u].z, a1.z); a1.w = fmaf(wgt, r1[u].w, a1.w);
         }
     }
+    const float mx = run_m;
     if (v0) *reinterpret_cast<float4*>(&red_acc[wid][4 * lane]) = a0;
     if (v1) *reinterpret_cast<float4*>(&red_acc[wid][4 * (lane + 32)]) = a1;
     if (lane == 0) red_l[wid] = ls;  // every lane of a warp holds the same sum
@@ -331,7 +340,7 @@ DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, i
     // generic kernel: about four CTAs per SM over its share of the layer
     const long long target = std::max<long long>(1, (4LL * sm_count) / ((long long)Hkv * head_chunks));
     // tensor-core kernel: one CTA per SM (it owns the SM's shared memory), one wave
-    const double fast_ctas_per_head = std::max(1.0, (double)sm_count / Hkv);
+    const double fast_ctas_per_head = std::max(1.0, (double)sm_count * mma::CTAS_PER_SM / Hkv);
     for (int i = 0; i < n_segs; ++i) {
         const pkv_segment_t& s = segs[i];
         SegDev d;

@@ -11,7 +11,11 @@ constexpr float kLog2e = 1.4426950408889634f;
 #ifndef PKV_K_UNROLL
 #define PKV_K_UNROLL 4
 #endif
-constexpr int kKUnroll = PKV_K_UNROLL;  // k-steps of the score loop unrolled together
+constexpr int kKUnroll = PKV_K_UNROLL;
+#ifndef PKV_ABLATE
+#define PKV_ABLATE 0
+#endif
+constexpr int kAblate = PKV_ABLATE;  // timing experiments only: 1 no score loop, 2 no value loop, 4 no key copies, 8 no value copies  // k-steps of the score loop unrolled together
 
 struct WarpState {
     float m[2];        // running max (log2 domain) of heads 2t, 2t+1
@@ -124,6 +128,7 @@ struct KSrc {
         }
     }
     __device__ __forceinline__ void issue(long long tile, int n_sub, unsigned kb, int tid) const {
+        if (kAblate & 4) return;
         if (n_sub == C::NSUB) issue_impl<true>(tile, n_sub, kb, tid);
         else issue_impl<false>(tile, n_sub, kb, tid);
     }
@@ -153,6 +158,7 @@ struct VSrc {
     // values of one tile into the stage at `sa`; one warp.  Rows of tokens >= n_valid are zero-filled
     // (their probabilities are zero, but garbage scales could be NaN).
     __device__ __forceinline__ void issue(long long tile, unsigned sa, int n_valid) const {
+        if (kAblate & 8) return;
         const uint8_t* v = vc + tile * (C::T * C::VWPT * 4);
         const long long off = tile * (C::T * 8);
         if (n_valid >= C::T && meta16) {
@@ -204,7 +210,7 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
     const char* m_lane = kb + C::OFF_KM + 2 * t * C::MROW + 4 * sub;
     // partially unrolled: the fully unrolled loop made the kernel instruction-fetch bound on short contexts
 #pragma unroll kKUnroll
-    for (int kk = 0; kk < 8; ++kk) {
+    for (int kk = 0; kk < ((kAblate & 1) ? 0 : 8); ++kk) {
         const unsigned qf0 = ldp32(q_lane + 32 * kk);       // head g, channels 16kk + 2t, +1
         const unsigned qf1 = ldp32(q_lane + 32 * kk + 16);  // channels 16kk + 2t + 8, +9
         {   // sum_d q[h,d] * zero[d,G]: rows = groups of the tile; only rows g < NG are read back, so the
@@ -309,7 +315,7 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
     const char* vs_lane = sa + C::OFF_VS + 64 * t;
     const char* vm_lane = sa + C::OFF_VM + 64 * t + 4 * ((g >> 1) & 1);  // word holding zero[.][g], g < 4
 #pragma unroll
-    for (int G = 0; G < C::NG; ++G) {
+    for (int G = 0; G < ((kAblate & 2) ? 0 : C::NG); ++G) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             const float* p = sacc[2 * G + j];
@@ -404,11 +410,9 @@ __device__ __forceinline__ void finish_cta(const MmaArgs& a, WarpState& st, int 
 
     // ---------------- merge the warps' states into one partial per CTA
     const size_t widx = (size_t)a.work_offset + blockIdx.x;
-    const int dim = tid & (HD - 1), hh = tid >> 7;  // threads 0..255: two head halves
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const int h = hh * 4 + k;
-        if (h >= a.G || tid >= 256) continue;
+    for (int idx = tid; idx < 8 * HD; idx += NTHREADS) {
+        const int h = idx >> 7, dim = idx & (HD - 1);
+        if (h >= a.G) break;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, smem_f[w * (8 * HD + 16) + 8 * HD + h]);
@@ -656,7 +660,7 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
     finish_cta<BITS>(a, st, kvh, smem_f);
 }
 
-__global__ void __launch_bounds__(NTHREADS, 1) decode_mma_kernel(const __grid_constant__ MmaArgs a) {
+__global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_mma_kernel(const __grid_constant__ MmaArgs a) {
     extern __shared__ __align__(16) float smem_f[];
     const int w = blockIdx.x, kvh = blockIdx.y;
     int si = 0;

@@ -28,9 +28,13 @@ constexpr int HD = 128;
 #define PKV_MMA_WARPS 12
 #endif
 constexpr int NWARPS = PKV_MMA_WARPS;
+#ifndef PKV_MMA_CTAS_PER_SM
+#define PKV_MMA_CTAS_PER_SM 1
+#endif
+constexpr int CTAS_PER_SM = PKV_MMA_CTAS_PER_SM;  // co-resident CTAs drift apart and mix their phases
 constexpr int NSTAGE = 2;
 constexpr int NTHREADS = NWARPS * 32;
-constexpr int kSmemBytes = 225 * 1024;  // dynamic shared memory of the kernel (of 227 KB usable)
+constexpr int kSmemBytes = (CTAS_PER_SM == 1 ? 225 : 112) * 1024;  // dynamic shared memory per CTA (227 KB per SM)
 constexpr int kQRowBytes = 272;          // 128 f16 + 16 pad bytes
 constexpr int kQBytes = 2304;           // q of the GQA group as float16 [8 heads][128], shared by all warps
 
@@ -42,10 +46,13 @@ template <int BITS>
 struct Cfg {
     static constexpr int T = 64;                    // tokens per tile
     static constexpr int NG = T / 32;               // key groups per tile
-    static constexpr int NSUB = BITS == 2 ? NWARPS : BITS == 4 ? (NWARPS < 8 ? NWARPS : 8) : 4;  // tiles per super-tile
+    // tiles per super-tile: one per warp if the buffers fit
+    static constexpr int NSUB_WANT = CTAS_PER_SM == 1 ? (BITS == 2 ? NWARPS : BITS == 4 ? 8 : 4)
+                                                      : (BITS == 2 ? NWARPS : BITS == 4 ? 4 : 2);
+    static constexpr int NSUB = NSUB_WANT < NWARPS ? NSUB_WANT : NWARPS;
     static constexpr int KRB = T * BITS / 8;        // key code bytes per channel row of a tile (16/32/64)
     static constexpr int KROW = NSUB * KRB + 16;    // key code row of a super-tile; the 16 pad bytes stagger banks
-    static constexpr int MROW = NSUB * NG * 2;      // key scale (or zero) row of a super-tile: f16 per group
+    static constexpr int MROW = (NSUB * NG * 2 + 15) / 16 * 16;  // key scale (or zero) row of a super-tile: f16 per group, 16-byte rows
     static constexpr int KBUF_BYTES = HD * (KROW + 2 * MROW);
     static constexpr int OFF_KS = HD * KROW;        // byte offsets inside a K buffer
     static constexpr int OFF_KM = OFF_KS + HD * MROW;
