@@ -106,7 +106,7 @@ struct KSrc {
         const uint8_t* src = kp + tile * C::KRB;
         for (int idx = tid; idx < HD * cpr; idx += NTHREADS) {
             const int row = idx / cpr, ch = idx - row * cpr;
-            cp_async16_ca(kb + row * C::KROW + 16 * ch, src + (size_t)row * nbK + 16 * ch);
+            cp_async16(kb + row * C::KROW + 16 * ch, src + (size_t)row * nbK + 16 * ch);
         }
         const long long moff = tile * (C::NG * 2);
         if (meta16) {
