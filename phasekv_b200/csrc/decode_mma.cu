@@ -15,6 +15,18 @@ constexpr int kKUnroll = PKV_K_UNROLL;
 #ifndef PKV_ABLATE
 #define PKV_ABLATE 0
 #endif
+#ifndef PKV_KEY_BULK
+#define PKV_KEY_BULK 0
+#endif
+#ifndef PKV_VALUE_BULK
+#define PKV_VALUE_BULK 0
+#endif
+// Bulk (TMA, mbarrier-tracked) copies are implemented for both operands and were measured against cp.async on
+// B200 at 32768 / 131072 prompt tokens: keys as one bulk copy per row (384 small requests per super-tile)
+// 14.1 / 35.0 us, values only (ten requests per tile) 12.3 / 29.2 us, cp.async for both 11.8 / 28.4 us.
+// The descriptor-less requests are too small to pay off, so both default to cp.async.
+constexpr bool kKeyBulk = PKV_KEY_BULK != 0;
+constexpr bool kValueBulk = PKV_VALUE_BULK != 0;
 constexpr int kAblate = PKV_ABLATE;  // timing experiments only: 1 no score loop, 2 no value loop, 4 no key copies, 8 no value copies  // k-steps of the score loop unrolled together
 
 struct WarpState {
@@ -127,6 +139,27 @@ struct KSrc {
             }
         }
     }
+    // The same image through bulk copies, one row per thread: 128 code rows, 128 scale rows, 128 zero rows.
+    // Every thread of the CTA arrives on `bar` exactly once (with the bytes it asked for), so the phase
+    // completes when all copies have landed.  Needs 16-byte aligned rows and n_sub % 4 == 0.
+    __device__ __forceinline__ void issue_bulk(long long tile, int n_sub, unsigned kb, int tid, unsigned bar) const {
+        unsigned bytes = 0;
+        for (int idx = tid; idx < 3 * HD; idx += NTHREADS) bytes += idx < HD ? n_sub * C::KRB : n_sub * C::NG * 2;
+        mbar_arrive_expect_tx(bar, bytes);
+        const long long moff = tile * (C::NG * 2);
+        for (int idx = tid; idx < 3 * HD; idx += NTHREADS) {
+            if (idx < HD) {
+                bulk_g2s(kb + idx * C::KROW, kp + (size_t)idx * nbK + tile * C::KRB, n_sub * C::KRB, bar);
+            } else if (idx < 2 * HD) {
+                const int row = idx - HD;
+                bulk_g2s(kb + C::OFF_KS + row * C::MROW, ks + (size_t)row * ngK2 + moff, n_sub * C::NG * 2, bar);
+            } else {
+                const int row = idx - 2 * HD;
+                bulk_g2s(kb + C::OFF_KM + row * C::MROW, km + (size_t)row * ngK2 + moff, n_sub * C::NG * 2, bar);
+            }
+        }
+    }
+
     __device__ __forceinline__ void issue(long long tile, int n_sub, unsigned kb, int tid) const {
         if (kAblate & 4) return;
         if (n_sub == C::NSUB) issue_impl<true>(tile, n_sub, kb, tid);
@@ -153,6 +186,21 @@ struct VSrc {
         d_vc = (lt + lt / 8) * (C::VWPT * 4) + 16 * (lane % CPT);
         vs = reinterpret_cast<const char*>(sg.vs + (size_t)kvh * sg.S * 4) + 16 * lane;
         vm = reinterpret_cast<const char*>(sg.vm + (size_t)kvh * sg.S * 4) + 16 * lane;
+    }
+
+    // A full tile through bulk copies: lanes 0..7 one block of 8 token rows each (the pad row follows each
+    // block), lane 8 the scales, lane 9 the zeros; every lane arrives on `bar` once.
+    __device__ __forceinline__ void issue_bulk(long long tile, unsigned sa, unsigned bar) const {
+        constexpr unsigned kBlock = 8 * C::VWPT * 4;
+        const unsigned bytes = lane < 8 ? kBlock : lane < 10 ? (unsigned)(C::T * 8) : 0u;
+        mbar_arrive_expect_tx(bar, bytes);
+        if (lane < 8) {
+            bulk_g2s(sa + 9 * lane * (C::VWPT * 4), vc - 16 * lane + tile * (C::T * C::VWPT * 4) + kBlock * lane, kBlock, bar);
+        } else if (lane == 8) {
+            bulk_g2s(sa + C::OFF_VS, vs - 16 * lane + tile * (C::T * 8), C::T * 8, bar);
+        } else if (lane == 9) {
+            bulk_g2s(sa + C::OFF_VM, vm - 16 * lane + tile * (C::T * 8), C::T * 8, bar);
+        }
     }
 
     // values of one tile into the stage at `sa`; one warp.  Rows of tokens >= n_valid are zero-filled
@@ -596,21 +644,48 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
     WarpState st;
     init_state(st);
 
-    // smem: [q][K buffer 0][K buffer 1][value stages of warp 0][of warp 1]...
+    // smem: [mbarriers][q][K buffer 0][K buffer 1][value stages of warp 0][of warp 1]...
     const char* smem_c = reinterpret_cast<const char*>(smem_f);
-    const unsigned kbuf = smem_base + kQBytes;
+    const unsigned kbuf = smem_base + kHeadBytes;
     const unsigned vring = kbuf + 2 * C::KBUF_BYTES + wid * (NSTAGE * C::VSTAGE_BYTES);
     const KSrc<BITS> ksrc(sg, kvh, tile0);
     const VSrc<BITS> vsrc(sg, kvh, lane);
     const int n_tiles_cta = (int)(tile1 - tile0);
     const int n_super = (n_tiles_cta + C::NSUB - 1) / C::NSUB;
+    // Bulk (TMA) copies when every row chunk is 16-byte aligned and sized; cp.async otherwise.
+    const bool bulk = (kKeyBulk || kValueBulk) && ksrc.meta16 && (n_tiles_cta & 3) == 0 && !(kAblate & 12);
+    const unsigned kbar = smem_base;                        // [2] key buffers
+    const unsigned vbar = smem_base + 16 + wid * 16;        // [2] value stages of this warp
+    bool timed_out = false;
+    if (bulk) {
+        if (tid == 0) {
+            mbar_init(kbar, NTHREADS);
+            mbar_init(kbar + 8, NTHREADS);
+        }
+        if (lane == 0) {
+            mbar_init(vbar, 32);
+            mbar_init(vbar + 8, 32);
+        }
+        fence_mbar_init();
+        __syncthreads();
+    }
 
     // super-tile 0 (frozen packed data: may be fetched before the dependency wait)
     if (ksrc.aligned) {
         const int n_sub = min(C::NSUB, n_tiles_cta);
-        ksrc.issue(tile0, n_sub, kbuf, tid);
-        if (wid < n_sub) vsrc.issue(tile0 + wid, vring, valid_of(tile0 + wid));
-        cp_async_commit();
+        if (bulk) {
+            if (kKeyBulk) ksrc.issue_bulk(tile0, n_sub, kbuf, tid, kbar);
+            else ksrc.issue(tile0, n_sub, kbuf, tid);
+            if (wid < n_sub) {
+                if (kValueBulk) vsrc.issue_bulk(tile0 + wid, vring, vbar);
+                else vsrc.issue(tile0 + wid, vring, valid_of(tile0 + wid));
+            }
+            cp_async_commit();
+        } else {
+            ksrc.issue(tile0, n_sub, kbuf, tid);
+            if (wid < n_sub) vsrc.issue(tile0 + wid, vring, valid_of(tile0 + wid));
+            cp_async_commit();
+        }
     }
     cudaGridDependencySynchronize();  // everything below may depend on the previous kernel of the stream
     // q of the GQA group, staged once per CTA behind the first copies (rows padded against bank
@@ -619,7 +694,7 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
         const int head = tid >> 4, ch = tid & 15;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (head < a.G) v = *reinterpret_cast<const uint4*>(a.q + (size_t)(h0 + head) * HD + 8 * ch);
-        *reinterpret_cast<uint4*>(reinterpret_cast<char*>(smem_f) + head * kQRowBytes + 16 * ch) = v;
+        *reinterpret_cast<uint4*>(reinterpret_cast<char*>(smem_f) + kBarBytes + head * kQRowBytes + 16 * ch) = v;
     }
     // let a programmatic dependent (the merge) be scheduled as soon as SMs free up; it still waits for this
     // grid to complete before it reads anything
@@ -631,15 +706,36 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
         const long long first = tile0 + (long long)sp * C::NSUB;
         int buf = sp & 1;
         if (ksrc.aligned) {
-            cp_async_wait<0>();
+            if (bulk) {
+                const unsigned parity = (sp >> 1) & 1;
+                if (kKeyBulk) {
+                    if (!mbar_wait(kbar + 8 * buf, parity)) timed_out = true;
+                } else {
+                    cp_async_wait<0>();
+                }
+                if (kValueBulk && wid < n_sub && !mbar_wait(vbar + 8 * buf, parity)) timed_out = true;
+            } else {
+                cp_async_wait<0>();
+            }
             __syncthreads();  // super-tile sp has landed for everyone; everyone is done with sp - 1
             if (sp + 1 < n_super) {
                 const long long next = first + C::NSUB;
                 const int n_next = min(C::NSUB, n_tiles_cta - (sp + 1) * C::NSUB);
-                ksrc.issue(next, n_next, kbuf + ((sp + 1) & 1) * C::KBUF_BYTES, tid);
-                if (wid < n_next)
-                    vsrc.issue(next + wid, vring + ((sp + 1) & 1) * C::VSTAGE_BYTES, valid_of(next + wid));
-                cp_async_commit();
+                const int nb = (sp + 1) & 1;
+                if (bulk) {
+                    fence_proxy_async();  // the buffers were last read through the generic proxy
+                    if (kKeyBulk) ksrc.issue_bulk(next, n_next, kbuf + nb * C::KBUF_BYTES, tid, kbar + 8 * nb);
+                    else ksrc.issue(next, n_next, kbuf + nb * C::KBUF_BYTES, tid);
+                    if (wid < n_next) {
+                        if (kValueBulk) vsrc.issue_bulk(next + wid, vring + nb * C::VSTAGE_BYTES, vbar + 8 * nb);
+                        else vsrc.issue(next + wid, vring + nb * C::VSTAGE_BYTES, valid_of(next + wid));
+                    }
+                    cp_async_commit();
+                } else {
+                    ksrc.issue(next, n_next, kbuf + nb * C::KBUF_BYTES, tid);
+                    if (wid < n_next) vsrc.issue(next + wid, vring + nb * C::VSTAGE_BYTES, valid_of(next + wid));
+                    cp_async_commit();
+                }
             }
         } else {
             // ragged segment: keys through ordinary loads into buffer 0, no overlap with the compute
@@ -647,14 +743,27 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
             __syncthreads();  // everyone is done with the previous super-tile
             if (wid < n_sub) vsrc.issue(first + wid, vring, valid_of(first + wid));
             cp_async_commit();
-            ksrc.load_sync(first, n_sub, reinterpret_cast<char*>(smem_f) + kQBytes, tid);
+            ksrc.load_sync(first, n_sub, reinterpret_cast<char*>(smem_f) + kHeadBytes, tid);
             cp_async_wait<0>();
             __syncthreads();
         }
         if (wid < n_sub)
-            compute_tile<BITS>(smem_c + kQBytes + buf * C::KBUF_BYTES, wid,
-                               smem_c + kQBytes + 2 * C::KBUF_BYTES + (wid * NSTAGE + buf) * C::VSTAGE_BYTES,
-                               smem_c + g * kQRowBytes + 4 * t, c_qk, st, ls, lane, valid_of(first + wid));
+            compute_tile<BITS>(smem_c + kHeadBytes + buf * C::KBUF_BYTES, wid,
+                               smem_c + kHeadBytes + 2 * C::KBUF_BYTES + (wid * NSTAGE + buf) * C::VSTAGE_BYTES,
+                               smem_c + kBarBytes + g * kQRowBytes + 4 * t, c_qk, st, ls, lane, valid_of(first + wid));
+    }
+    if (bulk) {
+        __syncthreads();  // nobody waits on the barriers any more: release their memory
+        if (tid == 0) {
+            mbar_inval(kbar);
+            mbar_inval(kbar + 8);
+        }
+        if (lane == 0) {
+            mbar_inval(vbar);
+            mbar_inval(vbar + 8);
+        }
+        // a wait that gave up means the result of this CTA cannot be trusted: poison it rather than hang
+        if (timed_out) st.m[0] = st.m[1] = __int_as_float(0x7fc00000);
     }
 
     finish_cta<BITS>(a, st, kvh, smem_f);

@@ -35,8 +35,10 @@ constexpr int CTAS_PER_SM = PKV_MMA_CTAS_PER_SM;  // co-resident CTAs drift apar
 constexpr int NSTAGE = 2;
 constexpr int NTHREADS = NWARPS * 32;
 constexpr int kSmemBytes = (CTAS_PER_SM == 1 ? 225 : 112) * 1024;  // dynamic shared memory per CTA (227 KB per SM)
+constexpr int kBarBytes = 256;           // mbarriers: two key buffers + two value stages per warp
 constexpr int kQRowBytes = 272;          // 128 f16 + 16 pad bytes
 constexpr int kQBytes = 2304;           // q of the GQA group as float16 [8 heads][128], shared by all warps
+constexpr int kHeadBytes = kBarBytes + kQBytes;  // shared memory in front of the key buffers
 
 // Shared memory of a CTA:  [q][K buffer 0][K buffer 1][value ring of warp 0][value ring of warp 1]...
 // A K buffer holds the keys of one SUPER-TILE (NSUB consecutive 64-token tiles of the CTA's range) for
@@ -62,11 +64,11 @@ struct Cfg {
     static constexpr int OFF_VS = VROWS * VWPT * 4; // byte offsets inside a value stage: codes, scale, zero
     static constexpr int OFF_VM = OFF_VS + T * 8;
     static constexpr int VSTAGE_BYTES = OFF_VM + T * 8;
-    static constexpr int SMEM_BYTES = kQBytes + 2 * KBUF_BYTES + NSUB * NSTAGE * VSTAGE_BYTES;
+    static constexpr int SMEM_BYTES = kHeadBytes + 2 * KBUF_BYTES + NSUB * NSTAGE * VSTAGE_BYTES;
 };
 
 constexpr int kMergeBytes = NWARPS * (8 * HD + 16) * 4;  // per-warp O[8][128] + m[8] + l[8]
-static_assert(kMergeBytes + kQBytes <= kSmemBytes && Cfg<2>::SMEM_BYTES <= kSmemBytes &&
+static_assert(kMergeBytes + kHeadBytes <= kSmemBytes && Cfg<2>::SMEM_BYTES <= kSmemBytes &&
               Cfg<4>::SMEM_BYTES <= kSmemBytes && Cfg<8>::SMEM_BYTES <= kSmemBytes, "shared memory budget");
 static_assert(Cfg<2>::NG == 2 && Cfg<2>::KBUF_BYTES % 16 == 0 && Cfg<2>::VSTAGE_BYTES % 16 == 0, "tile geometry");
 
@@ -137,6 +139,38 @@ __device__ __forceinline__ void cp_async16_zfill(unsigned smem_addr, const void*
 }
 __device__ __forceinline__ void cp_async8_zfill(unsigned smem_addr, const void* g, unsigned src_bytes) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(smem_addr), "l"(g), "r"(src_bytes));
+}
+// ---- bulk (TMA) copies global -> shared, completion counted in bytes on an mbarrier.  They are issued by
+// one thread per copy and bypass the load/store unit, which ordinary cp.async copies at HBM rate saturate.
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_inval(unsigned bar) {
+    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar));
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait: returns false if the phase did not complete within the iteration budget (the caller poisons
+// its result instead of hanging the GPU).
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+    for (int it = 0; it < (1 << 22); ++it) {
+        unsigned ok;
+        asm volatile(
+            "{.reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p;}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
