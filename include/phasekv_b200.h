@@ -60,6 +60,17 @@ int pkv_unpack_low_bits(const uint8_t* packed, int64_t rows, int64_t row_bytes, 
 int pkv_quantize_pack(const void* x, int64_t outer, int64_t axis_len, int64_t inner, int bits,
                       int64_t group, uint8_t* packed, void* scale, void* mins, pkv_stream_t stream);
 
+/* The same with padded output rows: consecutive rows of `packed` are packed_pitch bytes apart and rows of
+ * scale / mins meta_pitch elements apart (0 = dense, as above; otherwise >= the dense row length).  The
+ * padding is not written.  A key tensor whose rows are padded to whole 64-token tiles
+ * (packed_pitch = ceil(S/64) * 64 * bits / 8, meta_pitch a multiple of 8 and >= 2 * ceil(S/64)) lets the
+ * decode kernel stream a segment of ANY length with 16-byte copies; with dense rows that holds only for
+ * S % 64 == 0 and other lengths take a slower loader.  The reference's PackedTensor stays valid: its
+ * `packed`, `scale`, `mins` tensors become views with a row stride. */
+int pkv_quantize_pack_pitched(const void* x, int64_t outer, int64_t axis_len, int64_t inner, int bits,
+                              int64_t group, uint8_t* packed, void* scale, void* mins, int64_t packed_pitch,
+                              int64_t meta_pitch, pkv_stream_t stream);
+
 /* packing.py:158-175 unpack_dequantize: inverse of the above, out float16 [outer, axis_len, inner],
  * computed as float32 code*scale then +mins (two roundings) then rounded to float16. */
 int pkv_unpack_dequantize(const uint8_t* packed, const void* scale, const void* mins, int64_t outer,
@@ -91,6 +102,10 @@ typedef struct pkv_segment {
     int32_t k_bits, v_bits;   /* 2, 4 or 8 (ignored for PKV_SEG_FP16) */
     int32_t k_group, v_group; /* quantisation group sizes (after clamping to the axis length) */
     int32_t num_splits;       /* 0 = let the library choose; else as plan_kivi_decode(num_splits=...) */
+    /* PKV_SEG_KIVI only; 0 = dense.  Bytes between consecutive channel rows of k_packed, and elements between
+     * consecutive rows of k_scale / k_mins (see pkv_quantize_pack_pitched).  Heads are hd rows apart. */
+    int64_t k_row_pitch;
+    int64_t k_meta_pitch;
 } pkv_segment_t;
 
 #define PKV_MAX_SEGMENTS 4096
@@ -126,6 +141,33 @@ int pkv_decode_attention(const void* q, const pkv_segment_t* segs /* host */, in
 int pkv_decode_attention_static(const void* q, const pkv_segment_t* segs /* host */, int n_segs,
                                 int num_q_heads, int num_kv_heads, int head_dim, float sm_scale, int sm_count,
                                 void* out, float* m, float* l, float* acc, pkv_stream_t stream);
+
+/* Batched decode for serving: `batch` independent sequences, each with its own list of segments, attended in
+ * ONE split-K launch and ONE merge launch.  The reference's entry point is batch 1 only
+ * (attention_triton.py:655-657: fused_phasekv_decode raises unless orig_shape[0] == 1) and a batch is served by
+ * looping it; this pair of calls is what such a loop is replaced by.
+ *
+ * pkv_decode_batch_plan (host only, no CUDA call): sequence i owns segs[seg_offsets[i] .. seg_offsets[i+1]).
+ * It cuts every segment into work items of balanced cost, orders them longest first, and writes a
+ * position-independent table (segment descriptors, work list, per-sequence ranges of partials) into `table`
+ * (host memory, 16-byte aligned).  `table_bytes` receives the bytes used, `workspace_bytes` the device scratch
+ * the launch needs.  With table == NULL only the two sizes are computed.  Every segment must be one the
+ * tensor-core kernel takes (KIVI layout with head_dim 128, group 32, equal K/V bits, or float16; GQA group
+ * <= 8; 16-byte aligned buffers), otherwise PKV_E_LAYOUT: serve such sequences one by one.
+ * PKV_E_WORKSPACE when table_capacity is too small.  The plan depends on lengths and pointers only, so it
+ * stays valid until one of them changes.
+ *
+ * pkv_decode_attention_batched: q float16 [batch, Hq, hd], out float16 [batch, Hq, hd].  `table_device` is a
+ * copy of the table in device memory made by the caller (any stream-ordered copy before this call);
+ * `table_host` is the host original, read for the launch geometry only.  Same workspace rules as
+ * pkv_decode_attention. */
+int pkv_decode_batch_plan(const pkv_segment_t* segs /* host */, const int32_t* seg_offsets /* host [batch+1] */,
+                          int batch, int num_q_heads, int num_kv_heads, int head_dim, int sm_count,
+                          void* table /* host, may be NULL */, size_t table_capacity, size_t* table_bytes,
+                          size_t* workspace_bytes);
+int pkv_decode_attention_batched(const void* q, const void* table_host, const void* table_device,
+                                 float sm_scale, void* workspace, size_t workspace_bytes, void* out,
+                                 pkv_stream_t stream);
 
 /* attention_triton.py:257-266 _reduce_splits and :300-307 _merge_partials:
  * m, l float32 [n_parts, Hq] and acc float32 [n_parts, Hq, hd] (contiguous) are combined with

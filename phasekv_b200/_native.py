@@ -28,6 +28,7 @@ class Segment(ctypes.Structure):
         ("seq_len", ctypes.c_int64), ("head_stride", ctypes.c_int64),
         ("kind", ctypes.c_int32), ("k_bits", ctypes.c_int32), ("v_bits", ctypes.c_int32),
         ("k_group", ctypes.c_int32), ("v_group", ctypes.c_int32), ("num_splits", ctypes.c_int32),
+        ("k_row_pitch", ctypes.c_int64), ("k_meta_pitch", ctypes.c_int64),
     ]
 
 
@@ -51,6 +52,7 @@ _SIGNATURES = {
     "pkv_pack_low_bits": ([_VP, _I64, _I64, _I32, _VP, _VP], _I32),
     "pkv_unpack_low_bits": ([_VP, _I64, _I64, _I64, _I32, _VP, _VP], _I32),
     "pkv_quantize_pack": ([_VP, _I64, _I64, _I64, _I32, _I64, _VP, _VP, _VP, _VP], _I32),
+    "pkv_quantize_pack_pitched": ([_VP, _I64, _I64, _I64, _I32, _I64, _VP, _VP, _VP, _I64, _I64, _VP], _I32),
     "pkv_unpack_dequantize": ([_VP, _VP, _VP, _I64, _I64, _I64, _I32, _I64, _VP, _VP], _I32),
     "pkv_decode_workspace_bytes": ([ctypes.POINTER(Segment), _I32, _I32, _I32, _I32, _I32,
                                     ctypes.POINTER(ctypes.c_size_t)], _I32),
@@ -58,6 +60,10 @@ _SIGNATURES = {
                               ctypes.c_size_t, _VP, _VP, _VP, _VP, _VP], _I32),
     "pkv_decode_attention_static": ([_VP, ctypes.POINTER(Segment), _I32, _I32, _I32, _I32, _F32, _I32,
                                      _VP, _VP, _VP, _VP, _VP], _I32),
+    "pkv_decode_batch_plan": ([ctypes.POINTER(Segment), ctypes.POINTER(ctypes.c_int32), _I32, _I32, _I32, _I32, _I32,
+                               _VP, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t),
+                               ctypes.POINTER(ctypes.c_size_t)], _I32),
+    "pkv_decode_attention_batched": ([_VP, _VP, _VP, _F32, _VP, ctypes.c_size_t, _VP, _VP], _I32),
     "pkv_merge_partials": ([_VP, _VP, _VP, _I32, _I32, _I32, _VP, _VP, _VP, _VP, _VP], _I32),
     "pkv_cold_select_pack": ([_VP, _VP, _I64, _I64, _I32, _I64, _I64, _I64, _I32, _I64,
                               _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP], _I32),

@@ -8,10 +8,12 @@
 // (attention_triton.py:257-266 and :300-307 of the reference define the same algebra).
 #include <math.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include "common.cuh"
 #include "decode_plan.h"
 #include "decode_mma.cuh"
+#include "merge.cuh"
 
 namespace pkv {
 namespace {
@@ -91,7 +93,7 @@ decode_generic_kernel(const __grid_constant__ DecodeArgs a) {
         for (int h = 0; h < GMAX; ++h) dot[h] = 0.f;
         if (n < t1) {
             if (sg.kind == PKV_SEG_KIVI) {
-                const long long nbK = ceil_div(S, kvpb), ngK = ceil_div(S, sg.kgs);
+                const long long nbK = sg.k_pitch, ngK = sg.km_pitch;
                 const uint8_t* kp = sg.kp + (size_t)kvh * hd * nbK + n / kvpb;
                 const __half* ks = sg.ks + (size_t)kvh * hd * ngK + n / sg.kgs;
                 const __half* km = sg.km + (size_t)kvh * hd * ngK + n / sg.kgs;
@@ -204,95 +206,16 @@ decode_generic_kernel(const __grid_constant__ DecodeArgs a) {
     }
 }
 
-// Log-sum-exp merge of n_parts partials, one query head per CTA of 256 threads.
-// Warp w owns parts p = w (mod 8) and lane owns four consecutive dims (float4; head_dim <= 256 means
-// up to two float4 per lane), so every load of a thread is independent of the others and of the
-// weights: they are all issued before the first use, one memory round trip for the whole merge.
-constexpr int kMergeThreads = 256;
-constexpr int kMergeMaxInflight = 6;  // parts per thread held in registers at once
-
 __global__ void __launch_bounds__(kMergeThreads)
 merge_partials_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
                       const float* __restrict__ pacc, int n_parts, int Hq, int hd,
                       __half* __restrict__ out, float* __restrict__ m_out,
                       float* __restrict__ l_out, float* __restrict__ acc_out) {
-    __shared__ float red_m[8];
-    __shared__ float red_l[8];
-    __shared__ __align__(16) float red_acc[8][256];
-    const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     // When launched as a programmatic dependent of the split-K kernel this grid may already be resident while
     // that kernel finishes; wait here for its results (a no-op for an ordinary launch).
     cudaGridDependencySynchronize();
     cudaTriggerProgrammaticLaunchCompletion();  // the next kernel of the stream may start its own prologue
-    const int nvec = hd >> 2;  // float4 per row (hd % 4 == 0 is checked on the host)
-    const bool v0 = lane < nvec, v1 = lane + 32 < nvec;
-
-    // Every load of a batch (acc rows, m, l of up to 8 * kMergeMaxInflight parts) is issued before anything
-    // is reduced, so a typical merge (a few dozen parts) is one memory round trip.  Batches are combined
-    // with a running maximum, like the online softmax itself.
-    float run_m = -INFINITY;  // block-wide running max (identical in every thread)
-    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
-    float ls = 0.f;
-    for (int base = 0; base < n_parts; base += 8 * kMergeMaxInflight) {
-        float4 r0[kMergeMaxInflight], r1[kMergeMaxInflight];
-        float wm[kMergeMaxInflight], wl[kMergeMaxInflight];
-        float mx = -INFINITY;
-#pragma unroll
-        for (int u = 0; u < kMergeMaxInflight; ++u) {
-            const int p = base + wid + 8 * u;
-            r0[u] = r1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            wm[u] = -INFINITY;
-            wl[u] = 0.f;
-            if (p < n_parts) {
-                const float4* row = reinterpret_cast<const float4*>(pacc + ((size_t)p * Hq + h) * hd);
-                if (v0) r0[u] = __ldg(row + lane);
-                if (v1) r1[u] = __ldg(row + lane + 32);
-                wm[u] = __ldg(pm + (size_t)p * Hq + h);
-                wl[u] = __ldg(pl + (size_t)p * Hq + h);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kMergeMaxInflight; ++u) mx = fmaxf(mx, wm[u]);
-        __syncthreads();  // red_m is free again
-        if (lane == 0) red_m[wid] = mx;
-        __syncthreads();
-        mx = run_m;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) mx = fmaxf(mx, red_m[w]);
-        const float rescale = expf(run_m - mx);  // first batch: exp(-inf) = 0 on zero accumulators
-        run_m = mx;
-        ls *= rescale;
-        a0.x *= rescale; a0.y *= rescale; a0.z *= rescale; a0.w *= rescale;
-        a1.x *= rescale; a1.y *= rescale; a1.z *= rescale; a1.w *= rescale;
-#pragma unroll
-        for (int u = 0; u < kMergeMaxInflight; ++u) {
-            const float wgt = expf(wm[u] - mx);  // -inf -> 0
-            ls = fmaf(wgt, wl[u], ls);
-            a0.x = fmaf(wgt, r0[u].x, a0.x); a0.y = fmaf(wgt, r0[u].y, a0.y);
-            a0.z = fmaf(wgt, r0[u].z, a0.z); a0.w = fmaf(wgt, r0[u].w, a0.w);
-            a1.x = fmaf(wgt, r1[u].x, a1.x); a1.y = fmaf(wgt, r1[u].y, a1.y);
-            a1.z = fmaf(wgt, r1[u].z, a1.z); a1.w = fmaf(wgt, r1[u].w, a1.w);
-        }
-    }
-    const float mx = run_m;
-    if (v0) *reinterpret_cast<float4*>(&red_acc[wid][4 * lane]) = a0;
-    if (v1) *reinterpret_cast<float4*>(&red_acc[wid][4 * (lane + 32)]) = a1;
-    if (lane == 0) red_l[wid] = ls;  // every lane of a warp holds the same sum
-    __syncthreads();
-    float L = 0.f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) L += red_l[w];
-    if (tid < hd) {
-        float A = 0.f;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) A += red_acc[w][tid];
-        if (out) out[(size_t)h * hd + tid] = __float2half_rn(A / L);
-        if (acc_out) acc_out[(size_t)h * hd + tid] = A;
-    }
-    if (tid == 0) {
-        if (m_out) m_out[h] = mx;
-        if (l_out) l_out[h] = L;
-    }
+    merge_parts(pm, pl, pacc, n_parts, Hq, hd, blockIdx.x, out, m_out, l_out, acc_out);
 }
 
 int check_segments(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int hd) {
@@ -313,6 +236,12 @@ int check_segments(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int h
         if (!valid_bits(s.k_bits) || !valid_bits(s.v_bits)) return PKV_E_BITS;
         if (s.k_group <= 0 || s.v_group <= 0) return PKV_E_LAYOUT;
         if (!s.k_scale || !s.k_mins || !s.v_scale || !s.v_mins) return PKV_E_NULL;
+        if (s.k_row_pitch || s.k_meta_pitch) {
+            if (s.kind != PKV_SEG_KIVI) return PKV_E_LAYOUT;
+            if ((s.k_row_pitch && s.k_row_pitch < ceil_div(s.seq_len * s.k_bits, 8)) ||
+                (s.k_meta_pitch && s.k_meta_pitch < ceil_div(s.seq_len, s.k_group)))
+                return PKV_E_SHAPE;
+        }
     }
     return PKV_OK;
 }
@@ -322,6 +251,29 @@ int check_segments(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int h
 // bytes-proportional cost of streaming a segment
 static double seg_cost(const pkv_segment_t& s) {
     return (double)s.seq_len * (s.kind == PKV_SEG_FP16 ? 16 : s.k_bits);
+}
+
+// Device image of a segment descriptor (work-list fields left at zero).
+static SegDev seg_dev_of(const pkv_segment_t& s) {
+    SegDev d = {};
+    d.kp = static_cast<const uint8_t*>(s.k_packed);
+    d.ks = static_cast<const __half*>(s.k_scale);
+    d.km = static_cast<const __half*>(s.k_mins);
+    d.vp = static_cast<const uint8_t*>(s.v_packed);
+    d.vs = static_cast<const __half*>(s.v_scale);
+    d.vm = static_cast<const __half*>(s.v_mins);
+    d.S = s.seq_len;
+    d.head_stride = s.head_stride;
+    d.kind = s.kind;
+    d.kbits = s.kind == PKV_SEG_FP16 ? 8 : s.k_bits;
+    d.vbits = s.kind == PKV_SEG_FP16 ? 8 : s.v_bits;
+    d.kgs = s.kind == PKV_SEG_FP16 ? 1 : s.k_group;
+    d.vgs = s.kind == PKV_SEG_FP16 ? 1 : s.v_group;
+    if (s.kind == PKV_SEG_KIVI) {
+        d.k_pitch = s.k_row_pitch ? s.k_row_pitch : ceil_div(s.seq_len * s.k_bits, 8);
+        d.km_pitch = s.k_meta_pitch ? s.k_meta_pitch : ceil_div(s.seq_len, s.k_group);
+    }
+    return d;
 }
 
 DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int hd, int sm_count) {
@@ -343,20 +295,7 @@ DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, i
     const double fast_ctas_per_head = std::max(1.0, (double)sm_count * mma::CTAS_PER_SM / Hkv);
     for (int i = 0; i < n_segs; ++i) {
         const pkv_segment_t& s = segs[i];
-        SegDev d;
-        d.kp = static_cast<const uint8_t*>(s.k_packed);
-        d.ks = static_cast<const __half*>(s.k_scale);
-        d.km = static_cast<const __half*>(s.k_mins);
-        d.vp = static_cast<const uint8_t*>(s.v_packed);
-        d.vs = static_cast<const __half*>(s.v_scale);
-        d.vm = static_cast<const __half*>(s.v_mins);
-        d.S = s.seq_len;
-        d.head_stride = s.head_stride;
-        d.kind = s.kind;
-        d.kbits = s.kind == PKV_SEG_FP16 ? 8 : s.k_bits;
-        d.vbits = s.kind == PKV_SEG_FP16 ? 8 : s.v_bits;
-        d.kgs = s.kind == PKV_SEG_FP16 ? 1 : s.k_group;
-        d.vgs = s.kind == PKV_SEG_FP16 ? 1 : s.v_group;
+        SegDev d = seg_dev_of(s);
         if (is_fast[i]) {
             const long long tiles = mma::tiles_of(s);
             long long ctas;
@@ -423,7 +362,6 @@ int pkv_decode_attention(const void* q, const pkv_segment_t* segs, int n_segs, i
     float* pacc = reinterpret_cast<float*>(static_cast<char*>(workspace));
     float* pm = pacc + W * num_q_heads * head_dim;
     float* pl = pm + W * num_q_heads;
-    // one tensor-core launch and nothing else: its last CTAs do the merge themselves
     static const bool carve = getenv("PKV_NO_CARVEOUT") == nullptr;
     static thread_local bool carved = false;
     if (carve && !carved) {
@@ -563,4 +501,187 @@ extern "C" int pkv_decode_attention_static(const void* q, const pkv_segment_t* s
     }
     return pkv_decode_attention(q, segs, n_segs, num_q_heads, num_kv_heads, head_dim, sm_scale, sm_count, ptr,
                                 (size_t)PKV_STATIC_SCRATCH_BYTES, out, m, l, acc, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Batched decode (serving): many sequences, one split-K launch, one merge launch.
+//
+// The table the planner writes is position independent (offsets, no host pointers) so the caller can
+// copy it to the device with any copy it likes and keep it there while lengths and pointers stay the
+// same:  [BatchHeader][SegDev x n_segs][BatchWork x n_work][BatchRange x batch], each array 16-byte aligned.
+namespace pkv {
+namespace {
+
+constexpr uint32_t kBatchMagic = 0x42564b50u;  // "PKVB"
+
+struct BatchHeader {
+    uint32_t magic;
+    int32_t batch, n_segs, n_work, n_parts;
+    int32_t Hq, Hkv, hd;
+    uint32_t off_segs, off_work, off_ranges, bytes;
+    uint32_t pad[4];
+};
+static_assert(sizeof(BatchHeader) == 64, "header is one 64-byte block");
+
+// partials [part_begin, part_begin + n_parts) belong to one sequence
+struct BatchRange {
+    int32_t part_begin, n_parts;
+};
+
+inline size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
+
+__global__ void __launch_bounds__(kMergeThreads)
+merge_batched_kernel(const float* __restrict__ pm, const float* __restrict__ pl, const float* __restrict__ pacc,
+                     const BatchRange* __restrict__ ranges, int Hq, int hd, __half* __restrict__ out) {
+    cudaGridDependencySynchronize();
+    cudaTriggerProgrammaticLaunchCompletion();
+    const int seq = blockIdx.y;
+    const BatchRange r = ranges[seq];
+    merge_parts(pm + (size_t)r.part_begin * Hq, pl + (size_t)r.part_begin * Hq,
+                pacc + (size_t)r.part_begin * Hq * hd, r.n_parts, Hq, hd, blockIdx.x,
+                out + (size_t)seq * Hq * hd, nullptr, nullptr, nullptr);
+}
+
+// Tiles per work item.  `per_sm` is the layer's work per SM in 64-token tiles.  Few tiles per SM: one wave,
+// the tiles spread evenly.  Many: about three waves of long items; the short cold and hot segments, sorted to
+// the end of the work list, fill the tail.  (Measured on B200 with 64 sequences of ~8832 tokens: 2-3 waves
+// 135 us per layer, 4 waves 144, 6-8 waves 148: every item pays its first-load latency, warp merge and
+// partial write once.)  Items are whole super-tiles (what the CTA's warps compute side by side).
+int item_tiles(double per_sm) {
+    const int waves = (int)std::max(1.0, std::min(3.0, per_sm / 12.0));
+    int t = (int)std::ceil(per_sm / waves);
+    t = std::max(1, std::min(t, 4096));
+    if (t >= 12) t = (t + 6) / 12 * 12;
+    else if (t > 4) t = (t + 3) / 4 * 4;
+    return t;
+}
+
+}  // namespace
+}  // namespace pkv
+
+extern "C" int pkv_decode_batch_plan(const pkv_segment_t* segs, const int32_t* seg_offsets, int batch,
+                                     int num_q_heads, int num_kv_heads, int head_dim, int sm_count, void* table,
+                                     size_t table_capacity, size_t* table_bytes, size_t* workspace_bytes) {
+    if (!segs || !seg_offsets || !table_bytes || !workspace_bytes) return PKV_E_NULL;
+    if (batch <= 0 || seg_offsets[0] != 0) return PKV_E_SHAPE;
+    for (int i = 0; i < batch; ++i)
+        if (seg_offsets[i + 1] <= seg_offsets[i]) return PKV_E_SHAPE;  // every sequence attends to something
+    const int n_segs = seg_offsets[batch];
+    if (n_segs > (1 << 20)) return PKV_E_LIMIT;
+    for (int first = 0; first < n_segs; first += PKV_MAX_SEGMENTS) {
+        const int rc = check_segments(segs + first, std::min(PKV_MAX_SEGMENTS, n_segs - first), num_q_heads,
+                                      num_kv_heads, head_dim);
+        if (rc != PKV_OK) return rc;
+    }
+    double units = 0.0;  // 64-token tiles (a float16 tile of 32 tokens moves about as many bytes per token x4)
+    for (int i = 0; i < n_segs; ++i) {
+        if (!mma::eligible(segs[i], num_q_heads, num_kv_heads, head_dim)) return PKV_E_LAYOUT;
+        if (mma::tiles_of(segs[i]) > INT32_MAX) return PKV_E_LIMIT;
+        units += (double)mma::tiles_of(segs[i]);
+    }
+    const int per_item = item_tiles(units * num_kv_heads / std::max(sm_count, 1));
+
+    std::vector<mma::BatchWork> work;
+    std::vector<BatchRange> ranges(batch);
+    int parts = 0;
+    for (int b = 0; b < batch; ++b) {
+        ranges[b].part_begin = parts;
+        for (int si = seg_offsets[b]; si < seg_offsets[b + 1]; ++si) {
+            const long long tiles = mma::tiles_of(segs[si]);
+            long long n = ceil_div(tiles, per_item);
+            long long len = ceil_div(tiles, n);
+            // an item that starts on a multiple of four tiles keeps the key scale rows 16-byte aligned
+            if (segs[si].kind != PKV_SEG_FP16 && len > 4) len = (len + 3) / 4 * 4;
+            n = ceil_div(tiles, len);
+            for (long long k = 0; k < n; ++k) {
+                mma::BatchWork w = {};
+                w.seg = si;
+                w.seq = b;
+                w.tile_begin = (int)(k * len);
+                w.n_tiles = (int)std::min(len, tiles - k * len);
+                w.part = parts++;
+                work.push_back(w);
+            }
+            if (parts > (1 << 24)) return PKV_E_LIMIT;
+        }
+        ranges[b].n_parts = parts - ranges[b].part_begin;
+    }
+    // longest first: the hardware hands CTAs out in index order, so short items fill the tail
+    std::stable_sort(work.begin(), work.end(),
+                     [](const mma::BatchWork& a, const mma::BatchWork& b) { return a.n_tiles > b.n_tiles; });
+
+    BatchHeader h = {};
+    h.magic = kBatchMagic;
+    h.batch = batch;
+    h.n_segs = n_segs;
+    h.n_work = (int32_t)work.size();
+    h.n_parts = parts;
+    h.Hq = num_q_heads;
+    h.Hkv = num_kv_heads;
+    h.hd = head_dim;
+    h.off_segs = (uint32_t)sizeof(BatchHeader);
+    h.off_work = (uint32_t)align16(h.off_segs + (size_t)n_segs * sizeof(SegDev));
+    h.off_ranges = (uint32_t)align16(h.off_work + work.size() * sizeof(mma::BatchWork));
+    h.bytes = (uint32_t)align16(h.off_ranges + (size_t)batch * sizeof(BatchRange));
+    *table_bytes = h.bytes;
+    *workspace_bytes = (size_t)parts * num_q_heads * (head_dim + 2) * sizeof(float);
+    if (!table) return PKV_OK;
+    if (table_capacity < h.bytes) return PKV_E_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(table) & 15u) return PKV_E_LAYOUT;
+    char* base = static_cast<char*>(table);
+    memset(base, 0, h.bytes);
+    memcpy(base, &h, sizeof(h));
+    SegDev* sd = reinterpret_cast<SegDev*>(base + h.off_segs);
+    for (int i = 0; i < n_segs; ++i) sd[i] = seg_dev_of(segs[i]);
+    memcpy(base + h.off_work, work.data(), work.size() * sizeof(mma::BatchWork));
+    memcpy(base + h.off_ranges, ranges.data(), (size_t)batch * sizeof(BatchRange));
+    return PKV_OK;
+}
+
+extern "C" int pkv_decode_attention_batched(const void* q, const void* table_host, const void* table_device,
+                                            float sm_scale, void* workspace, size_t workspace_bytes, void* out,
+                                            pkv_stream_t stream) {
+    if (!q || !table_host || !table_device || !workspace || !out) return PKV_E_NULL;
+    BatchHeader h;
+    memcpy(&h, table_host, sizeof(h));
+    if (h.magic != kBatchMagic || h.batch <= 0 || h.n_work <= 0 || h.n_parts <= 0) return PKV_E_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(table_device) | reinterpret_cast<uintptr_t>(workspace)) & 15u) return PKV_E_LAYOUT;
+    const size_t P = (size_t)h.n_parts;
+    if (workspace_bytes < P * h.Hq * (h.hd + 2) * sizeof(float)) return PKV_E_WORKSPACE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float* pacc = static_cast<float*>(workspace);
+    float* pm = pacc + P * h.Hq * h.hd;
+    float* pl = pm + P * h.Hq;
+    const char* dev = static_cast<const char*>(table_device);
+
+    mma::BatchArgs a;
+    a.q = static_cast<const __half*>(q);
+    a.pm = pm;
+    a.pl = pl;
+    a.pacc = pacc;
+    a.Hq = h.Hq;
+    a.Hkv = h.Hkv;
+    a.G = h.Hq / h.Hkv;
+    a.sm_scale = sm_scale;
+    a.segs = reinterpret_cast<const SegDev*>(dev + h.off_segs);
+    a.work = reinterpret_cast<const mma::BatchWork*>(dev + h.off_work);
+    const int rc = mma::launch_batched(a, h.n_work, h.Hkv, s);
+    if (rc != PKV_OK) return rc;
+
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)h.Hq, (unsigned)h.batch);
+    cfg.blockDim = dim3(kMergeThreads);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const float* cpm = pm;
+    const float* cpl = pl;
+    const float* cpacc = pacc;
+    const BatchRange* ranges = reinterpret_cast<const BatchRange*>(dev + h.off_ranges);
+    PKV_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_batched_kernel, cpm, cpl, cpacc, ranges, (int)h.Hq, (int)h.hd,
+                                    static_cast<__half*>(out)));
+    return PKV_OK;
 }

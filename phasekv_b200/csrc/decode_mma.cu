@@ -52,12 +52,16 @@ struct KSrc {
     bool aligned;         // code rows start on 16 bytes: cp.async path; otherwise load_sync
 
     __device__ KSrc(const SegDev& sg, int kvh, long long tile0) {
-        nbK = (sg.S * BITS + 7) / 8;
-        ngK2 = (sg.S + 31) / 32 * 2;
+        nbK = sg.k_pitch;
+        ngK2 = sg.km_pitch * 2;
         kp = sg.kp + (size_t)kvh * HD * nbK;
         ks = reinterpret_cast<const char*>(sg.ks) + (size_t)kvh * HD * ngK2;
         km = reinterpret_cast<const char*>(sg.km) + (size_t)kvh * HD * ngK2;
-        aligned = (nbK & 15) == 0 && (ngK2 & 3) == 0 && sg.S % C::T == 0;
+        // 16-byte copies need rows that start on 16 bytes and hold whole tiles (dense rows do when S is a
+        // multiple of the tile, padded rows always); the partial last tile of a padded segment reads padding,
+        // which only reaches masked tokens.
+        const long long tiles = (sg.S + C::T - 1) / C::T;
+        aligned = (nbK & 15) == 0 && (ngK2 & 3) == 0 && nbK >= tiles * C::KRB && ngK2 >= tiles * (C::NG * 2);
         meta16 = aligned && (ngK2 & 15) == 0 && (tile0 & 3) == 0;
     }
 
@@ -410,7 +414,7 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
 // Per-warp epilogue and cross-warp merge.  BITS > 0: packed tile accumulators (undo the power-of-two
 // code scaling, add the zero terms).  BITS == 0: float16 tile accumulators (plain).
 template <int BITS>
-__device__ __forceinline__ void finish_cta(const MmaArgs& a, WarpState& st, int kvh, float* smem_f) {
+__device__ __forceinline__ void finish_cta(const CtaCtx& a, WarpState& st, int kvh, float* smem_f) {
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int h0 = kvh * a.G;
@@ -457,7 +461,7 @@ __device__ __forceinline__ void finish_cta(const MmaArgs& a, WarpState& st, int 
     __syncthreads();
 
     // ---------------- merge the warps' states into one partial per CTA
-    const size_t widx = (size_t)a.work_offset + blockIdx.x;
+    const size_t widx = a.widx;
     for (int idx = tid; idx < 8 * HD; idx += NTHREADS) {
         const int h = idx >> 7, dim = idx & (HD - 1);
         if (h >= a.G) break;
@@ -592,13 +596,11 @@ __device__ __forceinline__ void compute_hot_tile(unsigned sa, const unsigned (&q
     }
 }
 
-__device__ __forceinline__ void run_cta_fp16(const MmaArgs& a, const SegDev& sg, int split, int kvh, float* smem_f) {
+__device__ __forceinline__ void run_cta_fp16(const CtaCtx& a, const SegDev& sg, long long tile0, long long tile1,
+                                             int kvh, float* smem_f) {
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const unsigned smem_base = (unsigned)__cvta_generic_to_shared(smem_f);
-    const long long n_tiles = (sg.S + TH - 1) / TH;
-    const long long tile0 = (long long)split * sg.split_len;
-    const long long tile1 = min(n_tiles, tile0 + sg.split_len);
     const int h0 = kvh * a.G;
     cudaGridDependencySynchronize();  // the hot tier and q may have been written by the previous kernel
     cudaTriggerProgrammaticLaunchCompletion();
@@ -629,14 +631,12 @@ __device__ __forceinline__ void run_cta_fp16(const MmaArgs& a, const SegDev& sg,
 }
 
 template <int BITS>
-__device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int split, int kvh, float* smem_f) {
+__device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long long tile0, long long tile1, int kvh,
+                                        float* smem_f) {
     using C = Cfg<BITS>;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const unsigned smem_base = (unsigned)__cvta_generic_to_shared(smem_f);
-    const long long n_tiles = (sg.S + C::T - 1) / C::T;
-    const long long tile0 = (long long)split * sg.split_len;
-    const long long tile1 = min(n_tiles, tile0 + sg.split_len);
     const int h0 = kvh * a.G;
     // tokens of tile `tl` that exist (the last tile of a ragged segment is partial)
     auto valid_of = [&](long long tl) { return (int)min((long long)C::T, sg.S - tl * C::T); };
@@ -769,6 +769,22 @@ __device__ __forceinline__ void run_cta(const MmaArgs& a, const SegDev& sg, int 
     finish_cta<BITS>(a, st, kvh, smem_f);
 }
 
+__device__ __forceinline__ long long tiles_in(const SegDev& sg) {
+    return sg.kind == PKV_SEG_FP16 ? (sg.S + TH - 1) / TH : (sg.S + 63) / 64;
+}
+
+// Tiles [tile0, tile0 + n_tiles) of segment `sg` for KV head `kvh`, one partial written to row a.widx.
+__device__ __forceinline__ void run_item(const CtaCtx& a, const SegDev& sg, long long tile0, long long n_tiles,
+                                         int kvh, float* smem_f) {
+    const long long tile1 = min(tiles_in(sg), tile0 + n_tiles);
+    if (sg.kind == PKV_SEG_FP16) run_cta_fp16(a, sg, tile0, tile1, kvh, smem_f);
+    else if (sg.kbits == 2) run_cta<2>(a, sg, tile0, tile1, kvh, smem_f);
+    else if (sg.kbits == 4) run_cta<4>(a, sg, tile0, tile1, kvh, smem_f);
+    else run_cta<8>(a, sg, tile0, tile1, kvh, smem_f);
+}
+
+// One sequence, segment descriptors inside the parameter block; work item w of a segment covers
+// split_len tiles.
 __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_mma_kernel(const __grid_constant__ MmaArgs a) {
     extern __shared__ __align__(16) float smem_f[];
     const int w = blockIdx.x, kvh = blockIdx.y;
@@ -776,10 +792,17 @@ __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_mma_kernel(const
     while (si + 1 < a.n_segs && w >= a.segs[si + 1].work_begin) ++si;
     const SegDev& sg = a.segs[si];
     const int split = w - sg.work_begin;
-    if (sg.kind == PKV_SEG_FP16) run_cta_fp16(a, sg, split, kvh, smem_f);
-    else if (sg.kbits == 2) run_cta<2>(a, sg, split, kvh, smem_f);
-    else if (sg.kbits == 4) run_cta<4>(a, sg, split, kvh, smem_f);
-    else run_cta<8>(a, sg, split, kvh, smem_f);
+    const CtaCtx ctx = {a.q, a.pm, a.pl, a.pacc, (size_t)a.work_offset + blockIdx.x, a.Hq, a.G, a.sm_scale};
+    run_item(ctx, sg, (long long)split * sg.split_len, sg.split_len, kvh, smem_f);
+}
+
+// Many sequences, descriptors and an explicit work list in device memory (see BatchTable).
+__global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_mma_batched_kernel(const __grid_constant__ BatchArgs a) {
+    extern __shared__ __align__(16) float smem_f[];
+    const BatchWork wk = a.work[blockIdx.x];
+    const SegDev& sg = a.segs[wk.seg];
+    const CtaCtx ctx = {a.q + (size_t)wk.seq * a.Hq * HD, a.pm, a.pl, a.pacc, (size_t)wk.part, a.Hq, a.G, a.sm_scale};
+    run_item(ctx, sg, wk.tile_begin, wk.n_tiles, blockIdx.y, smem_f);
 }
 
 }  // namespace
@@ -791,7 +814,9 @@ bool eligible(const pkv_segment_t& s, int Hq, int Hkv, int hd) {
         return (bits & 15u) == 0 && s.head_stride % 8 == 0;
     }
     if (s.kind != PKV_SEG_KIVI) return false;
-    if (s.k_bits != s.v_bits || s.k_group != 32 || s.v_group != 32) return false;
+    // a segment shorter than one group has its key group clamped to its length: still one group per 32 tokens
+    const bool k_group_ok = s.k_group == 32 || (s.seq_len < 32 && s.k_group == s.seq_len);
+    if (s.k_bits != s.v_bits || !k_group_ok || s.v_group != 32) return false;
     const uintptr_t bits = reinterpret_cast<uintptr_t>(s.k_packed) | reinterpret_cast<uintptr_t>(s.k_scale) |
                            reinterpret_cast<uintptr_t>(s.k_mins) | reinterpret_cast<uintptr_t>(s.v_packed) |
                            reinterpret_cast<uintptr_t>(s.v_scale) | reinterpret_cast<uintptr_t>(s.v_mins);
@@ -804,12 +829,14 @@ long long tiles_of(const pkv_segment_t& s) {
     return (s.seq_len + tile_tokens(s.k_bits) - 1) / tile_tokens(s.k_bits);
 }
 
-int launch(const MmaArgs& a, int work, int Hkv, cudaStream_t stream) {
-    static thread_local bool configured[64] = {};
+namespace {
+template <class Kernel, class Args>
+int launch_pdl(Kernel kernel, const Args& a, int work, int Hkv, cudaStream_t stream, bool* configured) {
     int dev = 0;
     PKV_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 64 && !configured[dev]) {
-        PKV_CUDA_TRY(cudaFuncSetAttribute(decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    if (dev < 0 || dev >= 64) return PKV_E_LIMIT;
+    if (!configured[dev]) {
+        PKV_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         configured[dev] = true;
     }
     // Programmatic dependent launch: the grid may become resident while the previous kernel of the stream
@@ -825,8 +852,19 @@ int launch(const MmaArgs& a, int work, int Hkv, cudaStream_t stream) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    PKV_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_mma_kernel, a));
+    PKV_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, a));
     return PKV_OK;
+}
+}  // namespace
+
+int launch(const MmaArgs& a, int work, int Hkv, cudaStream_t stream) {
+    static thread_local bool configured[64] = {};
+    return launch_pdl(decode_mma_kernel, a, work, Hkv, stream, configured);
+}
+
+int launch_batched(const BatchArgs& a, int work, int Hkv, cudaStream_t stream) {
+    static thread_local bool configured[64] = {};
+    return launch_pdl(decode_mma_batched_kernel, a, work, Hkv, stream, configured);
 }
 
 }  // namespace mma

@@ -86,6 +86,39 @@ struct MmaArgs {
     SegDev segs[kMaxInlineSegs];  // split_len counts TILES here
 };
 
+// What a CTA needs besides its segment: the query rows of its sequence and where its partial goes.
+struct CtaCtx {
+    const __half* q;  // [Hq][128] of this CTA's sequence
+    float* pm;
+    float* pl;
+    float* pacc;
+    size_t widx;      // row of the partial arrays this CTA writes
+    int Hq, G;
+    float sm_scale;
+};
+
+// Batched decode: segment descriptors of all sequences and an explicit work list, both in device memory.
+struct BatchWork {
+    int seg;         // index into the segment table
+    int seq;         // sequence (row block of q and out)
+    int tile_begin;  // first tile of the item inside the segment
+    int n_tiles;
+    int part;        // row of the partial arrays
+    int pad[3];
+};
+static_assert(sizeof(BatchWork) == 32, "work items are read as two 16-byte words");
+
+struct BatchArgs {
+    const __half* q;  // [batch][Hq][128]
+    float* pm;
+    float* pl;
+    float* pacc;
+    int Hq, Hkv, G;
+    float sm_scale;
+    const SegDev* segs;
+    const BatchWork* work;
+};
+
 // ------------------------------------------------------------------ small PTX helpers
 __device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
@@ -262,5 +295,7 @@ bool eligible(const pkv_segment_t& s, int Hq, int Hkv, int hd);
 long long tiles_of(const pkv_segment_t& s);
 // Launch over `work` CTAs per KV head; a.segs[*].work_begin is relative to this launch.
 int launch(const MmaArgs& a, int work, int Hkv, cudaStream_t stream);
+// Launch over a device-resident work list of `work` items per KV head.
+int launch_batched(const BatchArgs& a, int work, int Hkv, cudaStream_t stream);
 }  // namespace mma
 }  // namespace pkv

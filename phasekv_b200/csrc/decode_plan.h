@@ -22,6 +22,8 @@ struct SegDev {
     long long S;
     long long head_stride;
     long long split_len;  // tokens per work item
+    long long k_pitch;    // bytes between channel rows of kp (KIVI layout)
+    long long km_pitch;   // elements between rows of ks / km (KIVI layout)
     int kind, kbits, vbits, kgs, vgs;
     int work_begin;  // index of the segment's first work item
     int n_splits;    // work items of this segment

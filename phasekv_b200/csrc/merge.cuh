@@ -1,0 +1,96 @@
+// Log-sum-exp merge of split-K partials, shared by the single-sequence and the batched decode entry points.
+#pragma once
+
+#include "common.cuh"
+
+namespace pkv {
+
+// Log-sum-exp merge of n_parts partials, one query head per CTA of 256 threads.
+// Warp w owns parts p = w (mod 8) and lane owns four consecutive dims (float4; head_dim <= 256 means
+// up to two float4 per lane), so every load of a thread is independent of the others and of the
+// weights: they are all issued before the first use, one memory round trip for the whole merge.
+constexpr int kMergeThreads = 256;
+constexpr int kMergeMaxInflight = 6;  // parts per thread held in registers at once
+
+// pm, pl, pacc point at the first of the n_parts partial rows ([part][Hq] and [part][Hq][hd]); out, m_out, l_out,
+// acc_out at the result rows of this query head's sequence ([Hq][hd] and [Hq]).
+__device__ __forceinline__ void merge_parts(const float* __restrict__ pm, const float* __restrict__ pl,
+                                            const float* __restrict__ pacc, int n_parts, int Hq, int hd, int h,
+                                            __half* __restrict__ out, float* __restrict__ m_out,
+                                            float* __restrict__ l_out, float* __restrict__ acc_out) {
+    __shared__ float red_m[8];
+    __shared__ float red_l[8];
+    __shared__ __align__(16) float red_acc[8][256];
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int nvec = hd >> 2;  // float4 per row (hd % 4 == 0 is checked on the host)
+    const bool v0 = lane < nvec, v1 = lane + 32 < nvec;
+
+    // Every load of a batch (acc rows, m, l of up to 8 * kMergeMaxInflight parts) is issued before anything
+    // is reduced, so a typical merge (a few dozen parts) is one memory round trip.  Batches are combined
+    // with a running maximum, like the online softmax itself.
+    float run_m = -INFINITY;  // block-wide running max (identical in every thread)
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+    float ls = 0.f;
+    for (int base = 0; base < n_parts; base += 8 * kMergeMaxInflight) {
+        float4 r0[kMergeMaxInflight], r1[kMergeMaxInflight];
+        float wm[kMergeMaxInflight], wl[kMergeMaxInflight];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int u = 0; u < kMergeMaxInflight; ++u) {
+            const int p = base + wid + 8 * u;
+            r0[u] = r1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            wm[u] = -INFINITY;
+            wl[u] = 0.f;
+            if (p < n_parts) {
+                const float4* row = reinterpret_cast<const float4*>(pacc + ((size_t)p * Hq + h) * hd);
+                if (v0) r0[u] = __ldg(row + lane);
+                if (v1) r1[u] = __ldg(row + lane + 32);
+                wm[u] = __ldg(pm + (size_t)p * Hq + h);
+                wl[u] = __ldg(pl + (size_t)p * Hq + h);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kMergeMaxInflight; ++u) mx = fmaxf(mx, wm[u]);
+        __syncthreads();  // red_m is free again
+        if (lane == 0) red_m[wid] = mx;
+        __syncthreads();
+        mx = run_m;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) mx = fmaxf(mx, red_m[w]);
+        const float rescale = expf(run_m - mx);  // first batch: exp(-inf) = 0 on zero accumulators
+        run_m = mx;
+        ls *= rescale;
+        a0.x *= rescale; a0.y *= rescale; a0.z *= rescale; a0.w *= rescale;
+        a1.x *= rescale; a1.y *= rescale; a1.z *= rescale; a1.w *= rescale;
+#pragma unroll
+        for (int u = 0; u < kMergeMaxInflight; ++u) {
+            const float wgt = expf(wm[u] - mx);  // -inf -> 0
+            ls = fmaf(wgt, wl[u], ls);
+            a0.x = fmaf(wgt, r0[u].x, a0.x); a0.y = fmaf(wgt, r0[u].y, a0.y);
+            a0.z = fmaf(wgt, r0[u].z, a0.z); a0.w = fmaf(wgt, r0[u].w, a0.w);
+            a1.x = fmaf(wgt, r1[u].x, a1.x); a1.y = fmaf(wgt, r1[u].y, a1.y);
+            a1.z = fmaf(wgt, r1[u].z, a1.z); a1.w = fmaf(wgt, r1[u].w, a1.w);
+        }
+    }
+    const float mx = run_m;
+    if (v0) *reinterpret_cast<float4*>(&red_acc[wid][4 * lane]) = a0;
+    if (v1) *reinterpret_cast<float4*>(&red_acc[wid][4 * (lane + 32)]) = a1;
+    if (lane == 0) red_l[wid] = ls;  // every lane of a warp holds the same sum
+    __syncthreads();
+    float L = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) L += red_l[w];
+    if (tid < hd) {
+        float A = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) A += red_acc[w][tid];
+        if (out) out[(size_t)h * hd + tid] = __float2half_rn(A / L);
+        if (acc_out) acc_out[(size_t)h * hd + tid] = A;
+    }
+    if (tid == 0) {
+        if (m_out) m_out[h] = mx;
+        if (l_out) l_out[h] = L;
+    }
+}
+
+}  // namespace pkv

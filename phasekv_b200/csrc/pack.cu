@@ -163,7 +163,7 @@ __global__ void quantize_pack_lastdim32_kernel(const __half* __restrict__ x, int
 template <int BITS>
 __global__ void __launch_bounds__(128)
 quantize_pack_axis32_kernel(const __half* __restrict__ x, int64_t outer, int64_t A, int64_t inner,
-                            uint8_t* __restrict__ packed, __half* __restrict__ scale,
+                            int64_t nb, int64_t ng, uint8_t* __restrict__ packed, __half* __restrict__ scale,
                             __half* __restrict__ mins) {
     constexpr float QMAX = (float)((1 << BITS) - 1);
     const int64_t chunks = inner / 8, groups = A / 32;
@@ -221,7 +221,6 @@ quantize_pack_axis32_kernel(const __half* __restrict__ x, int64_t outer, int64_t
             w[2 * c + 1][(a * BITS) / 32] |= (unsigned)q1 << ((a * BITS) % 32);
         }
     }
-    const int64_t nb = A * BITS / 8, ng = groups;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
         const int64_t row = o * inner + j8 * 8 + c;
@@ -270,7 +269,7 @@ using namespace pkv;
 
 extern "C" {
 
-int pkv_abi_version(void) { return 1; }
+int pkv_abi_version(void) { return 2; }
 
 int pkv_last_cuda_error(void) { return g_last_cuda_error; }
 
@@ -329,20 +328,30 @@ int pkv_unpack_low_bits(const uint8_t* packed, int64_t rows, int64_t row_bytes, 
 
 int pkv_quantize_pack(const void* x, int64_t outer, int64_t axis_len, int64_t inner, int bits,
                       int64_t group, uint8_t* packed, void* scale, void* mins, pkv_stream_t stream) {
+    return pkv_quantize_pack_pitched(x, outer, axis_len, inner, bits, group, packed, scale, mins, 0, 0, stream);
+}
+
+int pkv_quantize_pack_pitched(const void* x, int64_t outer, int64_t axis_len, int64_t inner, int bits,
+                              int64_t group, uint8_t* packed, void* scale, void* mins, int64_t packed_pitch,
+                              int64_t meta_pitch, pkv_stream_t stream) {
     if (!valid_bits(bits)) return PKV_E_BITS;
     if (outer < 0 || inner < 0 || axis_len <= 0 || group <= 0 || group > axis_len) return PKV_E_SHAPE;
     if (outer * inner == 0) return PKV_OK;
     if (!x || !packed || !scale || !mins) return PKV_E_NULL;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int vpb = 8 / bits;
-    const int64_t nb = ceil_div(axis_len, vpb), ng = ceil_div(axis_len, group);
+    const int64_t dense_nb = ceil_div(axis_len, vpb), dense_ng = ceil_div(axis_len, group);
+    // row strides of the outputs: bytes of `packed`, elements of `scale` / `mins`
+    const int64_t nb = packed_pitch ? packed_pitch : dense_nb, ng = meta_pitch ? meta_pitch : dense_ng;
+    if (nb < dense_nb || ng < dense_ng) return PKV_E_SHAPE;
+    const bool dense = nb == dense_nb && ng == dense_ng;
     const __half* xh = static_cast<const __half*>(x);
     __half* sc = static_cast<__half*>(scale);
     __half* mn = static_cast<__half*>(mins);
 
     const bool aligned = ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) &&
                          ((reinterpret_cast<uintptr_t>(packed) & 15u) == 0);
-    if (inner == 1 && group == 32 && axis_len % 32 == 0 && aligned) {
+    if (inner == 1 && group == 32 && axis_len % 32 == 0 && aligned && dense) {
         const int64_t n_groups = outer * (axis_len / 32);
         const unsigned grid = (unsigned)ceil_div(n_groups, 128);
         if (bits == 2) quantize_pack_lastdim32_kernel<2><<<grid, 128, 0, s>>>(xh, n_groups, packed, sc, mn);
@@ -352,12 +361,12 @@ int pkv_quantize_pack(const void* x, int64_t outer, int64_t axis_len, int64_t in
         return PKV_OK;
     }
 
-    if (inner % 8 == 0 && inner > 1 && group == 32 && axis_len % 32 == 0 && aligned) {
+    if (inner % 8 == 0 && inner > 1 && group == 32 && axis_len % 32 == 0 && aligned && nb % 8 == 0) {
         const int64_t n = outer * (axis_len / 32) * (inner / 8);
         const unsigned grid = (unsigned)ceil_div(n, 128);
-        if (bits == 2) quantize_pack_axis32_kernel<2><<<grid, 128, 0, s>>>(xh, outer, axis_len, inner, packed, sc, mn);
-        else if (bits == 4) quantize_pack_axis32_kernel<4><<<grid, 128, 0, s>>>(xh, outer, axis_len, inner, packed, sc, mn);
-        else quantize_pack_axis32_kernel<8><<<grid, 128, 0, s>>>(xh, outer, axis_len, inner, packed, sc, mn);
+        if (bits == 2) quantize_pack_axis32_kernel<2><<<grid, 128, 0, s>>>(xh, outer, axis_len, inner, nb, ng, packed, sc, mn);
+        else if (bits == 4) quantize_pack_axis32_kernel<4><<<grid, 128, 0, s>>>(xh, outer, axis_len, inner, nb, ng, packed, sc, mn);
+        else quantize_pack_axis32_kernel<8><<<grid, 128, 0, s>>>(xh, outer, axis_len, inner, nb, ng, packed, sc, mn);
         PKV_LAUNCH_CHECK();
         return PKV_OK;
     }

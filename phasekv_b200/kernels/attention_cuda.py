@@ -44,12 +44,24 @@ def _packed_segment(key: PackedTensor, value: PackedTensor, num_splits: Optional
     else:
         raise ValueError("K must be packed along tokens or head_dim, V along head_dim")
     _vals_per_byte(key.bits), _vals_per_byte(value.bits)
-    keep = [key.packed.contiguous(), key.scale.contiguous(), key.mins.contiguous(),
-            value.packed.contiguous(), value.scale.contiguous(), value.mins.contiguous()]
+    k_rows = [key.packed, key.scale, key.mins]
+    pitches = [0, 0]
+    if kind == nv.PKV_SEG_KIVI and all(_padded_rows(t) for t in k_rows) and key.scale.stride(1) == key.mins.stride(1):
+        pitches = [key.packed.stride(1), key.scale.stride(1)]  # uint8 rows: bytes; float16 rows: elements
+    else:
+        k_rows = [t.contiguous() for t in k_rows]
+    keep = k_rows + [value.packed.contiguous(), value.scale.contiguous(), value.mins.contiguous()]
     seg = nv.Segment(*(t.data_ptr() for t in keep), int(key.orig_shape[1]), 0, kind,
                      int(key.bits), int(value.bits), int(key.group_size), int(value.group_size),
-                     int(num_splits or 0))
+                     int(num_splits or 0), *pitches)
     return seg, keep
+
+
+def _padded_rows(t: torch.Tensor) -> bool:
+    """``t`` is ``[Hkv, hd, n]`` with dense elements, rows a fixed pitch apart and heads ``hd`` rows apart
+    (what ``quantize_pack`` hands out for keys, or a slice of it along the last dimension)."""
+    return (t.dim() == 3 and t.stride(2) == 1 and t.stride(1) >= t.shape[2]
+            and (t.shape[0] == 1 or t.stride(0) == t.shape[1] * t.stride(1)))
 
 
 def _fp16_segment(hot_k: torch.Tensor, hot_v: torch.Tensor) -> Tuple[nv.Segment, list]:
@@ -64,7 +76,7 @@ def _fp16_segment(hot_k: torch.Tensor, hot_v: torch.Tensor) -> Tuple[nv.Segment,
         hot_k, hot_v = hot_k.contiguous(), hot_v.contiguous()
     head_stride = hot_k.stride(0) if hot_k.shape[0] > 1 else hot_k.shape[1] * hd
     seg = nv.Segment(hot_k.data_ptr(), None, None, hot_v.data_ptr(), None, None,
-                     int(hot_k.shape[1]), int(head_stride), nv.PKV_SEG_FP16, 8, 8, 1, 1, 0)
+                     int(hot_k.shape[1]), int(head_stride), nv.PKV_SEG_FP16, 8, 8, 1, 1, 0, 0, 0)
     return seg, [hot_k, hot_v]
 
 
@@ -299,3 +311,71 @@ def fused_phasekv_decode(q: torch.Tensor, tiers, num_attention_heads: int,
                      num_splits, block_n, num_warps)
     out, _ = _run_decode(q, segs, keep, num_attention_heads, hkv, True, False)
     return out
+
+
+# --------------------------------------------------------------------------- batched serving
+class BatchDecodePlan:
+    """Work list for one layer of a batch of sequences, resident on the device.
+
+    The reference serves a batch by looping ``fused_phasekv_decode`` over sequences (it raises for
+    ``orig_shape[0] != 1``, attention_triton.py:655-657).  Here all sequences of a layer go through one
+    split-K launch and one merge launch; the plan (segment descriptors, work items of balanced cost,
+    per-sequence ranges of partials) is built on the host from lengths and pointers and stays valid
+    until one of them changes, e.g. for the frozen tiers between two cooling steps.
+    """
+
+    def __init__(self, tiers_list: Sequence, num_attention_heads: int):
+        if not tiers_list:
+            raise ValueError("empty batch")
+        segs: List[nv.Segment] = []
+        offsets = [0]
+        self._keep: list = []
+        hkv = hd = None
+        for tiers in tiers_list:
+            s, keep, hkv_i, hd_i = layer_segments(tiers)
+            if hkv is not None and (hkv_i, hd_i) != (hkv, hd):
+                raise ValueError("all sequences of a batch must share the KV head count and head_dim")
+            hkv, hd = hkv_i, hd_i
+            segs.extend(s)
+            self._keep.append(keep)
+            offsets.append(len(segs))
+        if num_attention_heads % hkv != 0:
+            raise ValueError(f"Hq {num_attention_heads} is not a multiple of Hkv {hkv}")
+        self.batch, self.num_q_heads, self.num_kv_heads, self.head_dim = len(tiers_list), num_attention_heads, hkv, hd
+        first = tiers_list[0]
+        self.device = (first.hot_k if first.hot_len else first.prompt.key.packed).device
+        L = nv.lib()
+        arr = (nv.Segment * len(segs))(*segs)
+        off = (ctypes.c_int32 * len(offsets))(*offsets)
+        tb, wb = ctypes.c_size_t(0), ctypes.c_size_t(0)
+        sms = _device_sm_count(self.device)
+        nv.check(L.pkv_decode_batch_plan(arr, off, self.batch, num_attention_heads, hkv, hd, sms, None, 0,
+                                         ctypes.byref(tb), ctypes.byref(wb)))
+        self.table_host = torch.empty(tb.value, dtype=torch.uint8).pin_memory()
+        nv.check(L.pkv_decode_batch_plan(arr, off, self.batch, num_attention_heads, hkv, hd, sms,
+                                         self.table_host.data_ptr(), tb.value, ctypes.byref(tb), ctypes.byref(wb)))
+        self.workspace_bytes = int(wb.value)
+        self.table_device = self.table_host.to(self.device, non_blocking=True)
+        self.work_items = int(self.table_host[12:16].view(torch.int32).item())
+
+    def run(self, q: torch.Tensor) -> torch.Tensor:
+        nv.require_cuda(q, "q")
+        if tuple(q.shape) != (self.batch, self.num_q_heads, self.head_dim) or q.dtype != torch.float16:
+            raise ValueError(f"q must be float16 [{self.batch}, {self.num_q_heads}, {self.head_dim}]")
+        q = q.contiguous()
+        out = torch.empty_like(q)
+        with torch.cuda.device(self.device):
+            stream = nv.stream_of(self.device)
+            ws = _workspace(self.device, stream, self.workspace_bytes)
+            nv.check(nv.lib().pkv_decode_attention_batched(
+                q.data_ptr(), self.table_host.data_ptr(), self.table_device.data_ptr(),
+                1.0 / (self.head_dim ** 0.5), ws.data_ptr(), ws.numel(), out.data_ptr(), stream))
+        return out
+
+
+def fused_phasekv_decode_batched(q: torch.Tensor, tiers_list, num_attention_heads: int) -> torch.Tensor:
+    """``q`` float16 ``[B, Hq, hd]`` against ``tiers_list`` (one ``LayerTiers`` per sequence, or a
+    ``BatchDecodePlan`` built from them) -> float16 ``[B, Hq, hd]``, row ``i`` equal to
+    ``fused_phasekv_decode(q[i], tiers_list[i], Hq)``."""
+    plan = tiers_list if isinstance(tiers_list, BatchDecodePlan) else BatchDecodePlan(tiers_list, num_attention_heads)
+    return plan.run(q)

@@ -104,6 +104,10 @@ def _axis_view(shape, axis: int):
     return outer, int(shape[axis]), inner
 
 
+#: tile geometry of the decode kernel that padded key rows are sized for
+KEY_TILE_TOKENS, KEY_TILE_GROUP = 64, 32
+
+
 def quantize_pack(x: torch.Tensor, bits: int, axis: int, group_size: int) -> PackedTensor:
     """Grouped asymmetric min-max quantisation along ``axis`` with the codes really packed.
 
@@ -126,13 +130,22 @@ def quantize_pack(x: torch.Tensor, bits: int, axis: int, group_size: int) -> Pac
     gs = length if group_size is None or group_size <= 0 else min(int(group_size), length)
     moved = tuple(s for i, s in enumerate(orig_shape) if i != axis)
     dev = x.device
-    packed = torch.empty(*moved, (length + vpb - 1) // vpb, dtype=torch.uint8, device=dev)
-    n_groups = (length + gs - 1) // gs
-    scale = torch.empty(*moved, n_groups, dtype=torch.float16, device=dev)
-    mins = torch.empty(*moved, n_groups, dtype=torch.float16, device=dev)
+    nb, n_groups = (length + vpb - 1) // vpb, (length + gs - 1) // gs
+    # Key layout (the axis is not the last dimension, rows are long): pad the rows of the outputs to whole
+    # 64-token tiles so that the decode kernel can stream a segment of any length with 16-byte copies.  The
+    # tensors handed back are views of the logical shape; the padding is never read as data.
+    row_bytes, row_groups = nb, n_groups
+    if inner > 1 and gs == KEY_TILE_GROUP:
+        tiles = (length + KEY_TILE_TOKENS - 1) // KEY_TILE_TOKENS
+        row_bytes = tiles * KEY_TILE_TOKENS // vpb
+        row_groups = (tiles * (KEY_TILE_TOKENS // KEY_TILE_GROUP) + 7) // 8 * 8
+    packed = torch.empty(*moved, row_bytes, dtype=torch.uint8, device=dev)[..., :nb]
+    scale = torch.empty(*moved, row_groups, dtype=torch.float16, device=dev)[..., :n_groups]
+    mins = torch.empty(*moved, row_groups, dtype=torch.float16, device=dev)[..., :n_groups]
     with torch.cuda.device(dev):
-        nv.check(nv.lib().pkv_quantize_pack(nv.ptr(x), outer, length, inner, bits, gs, nv.ptr(packed),
-                                            nv.ptr(scale), nv.ptr(mins), nv.stream_of(dev)))
+        nv.check(nv.lib().pkv_quantize_pack_pitched(nv.ptr(x), outer, length, inner, bits, gs, nv.ptr(packed),
+                                                    nv.ptr(scale), nv.ptr(mins), row_bytes, row_groups,
+                                                    nv.stream_of(dev)))
     return PackedTensor(packed=packed, scale=scale, mins=mins, bits=bits, axis=axis, group_size=gs,
                         orig_shape=orig_shape, axis_len=length)
 

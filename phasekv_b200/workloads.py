@@ -105,3 +105,32 @@ def decode_algorithmic_bytes(shape: Shape, prompt_len: int, prompt_bits: int, co
     total = hkv * (prompt_len * bpt(prompt_bits) + cold_len * bpt(cold_bits) + hot_len * 4 * hd)
     total += 2 * hq * hd * 2
     return int(total)
+
+
+def gpu_three_tier(shape: Shape, prompt_len: int, prompt_bits: int, cold_len: int, cold_bits: int,
+                   hot_len: int, seed: int, device, group: int = 32, hot_capacity: int | None = None):
+    """One sequence's packed three-tier KV of one layer, drawn and packed on ``device`` (same
+    distribution as the CPU generators, different bits: for timing and for rows that need no CPU
+    checker).  Returns ``(LayerTiers, q float16 [Hq, hd])``."""
+    from .kernels import packing
+    from .kernels.tiers import LayerTiers, PackedKVSegment
+    gen = torch.Generator(device=device).manual_seed(seed)
+
+    def kv(length):
+        k = torch.randn(1, shape.num_kv_heads, length, shape.head_dim, generator=gen, device=device).half()
+        v = torch.randn(1, shape.num_kv_heads, length, shape.head_dim, generator=gen, device=device).half()
+        for c in OUTLIER_CHANNELS.get(shape.head_dim, ()):
+            k[..., c] *= OUTLIER_GAIN
+        return k, v
+
+    def pack(length, bits):
+        k, v = kv(length)
+        return PackedKVSegment(packing.quantize_pack(k, bits, -2, group), packing.quantize_pack(v, bits, -1, group))
+
+    prompt = pack(prompt_len, prompt_bits)
+    cold = [pack(cold_len, cold_bits)] if cold_len > 0 else []
+    hk = hv = None
+    if hot_len > 0:
+        hk, hv = kv(hot_capacity or hot_len)
+    q = torch.randn(shape.num_q_heads, shape.head_dim, generator=gen, device=device).half()
+    return LayerTiers(prompt=prompt, cold=cold, hot_k=hk, hot_v=hv, hot_len=hot_len), q

@@ -272,3 +272,37 @@ def test_argument_errors(oracle, attn):
     from phasekv_b200.kernels.tiers import LayerTiers, PackedKVSegment
     with pytest.raises(ValueError):
         attn.fused_phasekv_decode(qg, LayerTiers(PackedKVSegment(batched, batched)), 14)
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+def test_padded_key_rows_take_any_length(oracle, attn, bits):
+    """Keys packed on the GPU come with rows padded to whole 64-token tiles (views with a row stride), which
+    lets segments of any length stream through the 16-byte copy path.  Codes, scales and zeros seen through
+    the views are the oracle's bit for bit, and the attention over them meets the same bars as the dense
+    layout does."""
+    from phasekv_b200 import workloads
+    from phasekv_b200.kernels import packing
+    from phasekv_b200.kernels.tiers import LayerTiers, PackedKVSegment
+    from tests.util import assert_packed_equal
+    shape = workloads.QWEN2_5_7B
+    for S in (1, 31, 65, 1000, 4097, 8193):
+        segs, hk, hv, q = _pack_tiers(oracle, shape, S, bits, [], 4, 0, seed=77 * bits + S)
+        (pk, pv), _, _, _ = workloads.three_tier_dense(77 * bits + S, shape, S, 0, 0)
+        key = packing.quantize_pack(pk.cuda(), bits, -2, 32)
+        value = packing.quantize_pack(pv.cuda(), bits, -1, 32)
+        assert_packed_equal(key, segs[0][0], f"K S={S}")
+        assert_packed_equal(value, segs[0][1], f"V S={S}")
+        if S >= 32:
+            assert key.packed.stride(2) % 16 == 0 and key.packed.stride(2) * (8 // bits) % 64 == 0
+            assert key.scale.stride(2) % 8 == 0 and key.scale.stride(2) == key.mins.stride(2)
+        q2 = q[0, :, 0, :]
+        ref = oracle.segments_decode_reference(q2, segs, None, None, shape.num_q_heads).float()
+        exact = _exact_attention(oracle, q2, segs[0][0], segs[0][1], shape.num_q_heads)
+        tiers = LayerTiers(prompt=PackedKVSegment(key, value))
+        out = attn.fused_phasekv_decode(q2.cuda(), tiers, shape.num_q_heads).float().cpu()
+        dense = attn.fused_phasekv_decode(q2.cuda(), make_tiers(segs), shape.num_q_heads).float().cpu()
+        assert torch.isfinite(out).all(), S
+        slack = (ref - exact).abs().max().item()
+        assert (out - exact).abs().max().item() <= 1.2e-3, f"S={S} bits={bits}"
+        assert (out - ref).abs().max().item() <= 2e-3 + slack, f"S={S} bits={bits}"
+        assert (out - dense).abs().max().item() <= 1e-3, f"S={S} bits={bits}: padded and dense rows disagree"

@@ -56,7 +56,7 @@ def test_library_exports_every_declared_symbol():
     L = _native.lib()
     assert L.pkv_abi_version() >= 1
     assert L.pkv_strerror(0) == b"ok" and b"bit width" in L.pkv_strerror(-1)
-    assert ctypes.sizeof(_native.Segment) == 6 * 8 + 2 * 8 + 6 * 4
+    assert ctypes.sizeof(_native.Segment) == 6 * 8 + 2 * 8 + 6 * 4 + 2 * 8
 
 
 def test_abi_rejects_bad_arguments_without_touching_a_gpu():
@@ -94,3 +94,63 @@ def test_algorithmic_bytes_table():
     assert w.decode_algorithmic_bytes(s, 4096, 2, 256, 4, 128) == 2_013_184
     assert w.decode_algorithmic_bytes(s, 32768, 2, 256, 4, 128) == 13_023_232
     assert w.decode_algorithmic_bytes(s, 131072, 2, 256, 4, 128) == 50_771_968
+
+
+def test_batch_plan_covers_every_tile_once():
+    """pkv_decode_batch_plan is host-only: with made-up (aligned) device addresses it must produce a table
+    whose work items cover every tile of every segment exactly once, longest first, with the partials of a
+    sequence contiguous."""
+    import ctypes
+    import struct
+
+    from phasekv_b200 import _native as nv
+    L = nv.lib()
+    lengths = [(8192, 512, 128), (6150, 384, 97), (64, 0, 0), (12288, 640, 192), (1, 0, 1)]
+    segs, offsets, base = [], [0], 0x10000000
+    for p, c, h in lengths:
+        for n, bits in ((p, 2), (c, 4)):
+            if n:
+                ptrs = [base + 0x100000 * k for k in range(6)]
+                base += 0x1000000
+                segs.append(nv.Segment(*ptrs, n, 0, nv.PKV_SEG_KIVI, bits, bits, 32, 32, 0))
+        if h:
+            segs.append(nv.Segment(base, None, None, base + 0x100000, None, None, h, 192 * 128, nv.PKV_SEG_FP16,
+                                   8, 8, 1, 1, 0))
+            base += 0x1000000
+        offsets.append(len(segs))
+    arr = (nv.Segment * len(segs))(*segs)
+    off = (ctypes.c_int32 * len(offsets))(*offsets)
+    tb, wb = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    nv.check(L.pkv_decode_batch_plan(arr, off, len(lengths), 28, 4, 128, 148, None, 0, ctypes.byref(tb), ctypes.byref(wb)))
+    buf = ctypes.create_string_buffer(tb.value + 16)
+    addr = (ctypes.addressof(buf) + 15) & ~15
+    assert L.pkv_decode_batch_plan(arr, off, len(lengths), 28, 4, 128, 148, addr, tb.value - 16, ctypes.byref(tb),
+                                   ctypes.byref(wb)) == nv.PKV_E_WORKSPACE
+    nv.check(L.pkv_decode_batch_plan(arr, off, len(lengths), 28, 4, 128, 148, addr, tb.value, ctypes.byref(tb), ctypes.byref(wb)))
+    raw = ctypes.string_at(addr, tb.value)
+    magic, batch, n_segs, n_work, n_parts, hq, hkv, hd, o_segs, o_work, o_ranges, nbytes = struct.unpack_from("<I7i4I", raw)
+    assert (magic, batch, n_segs, hq, hkv, hd, nbytes) == (0x42564B50, len(lengths), len(segs), 28, 4, 128, tb.value)
+    assert n_work == n_parts and wb.value == n_parts * 28 * 130 * 4
+    covered = [set() for _ in segs]
+    parts, prev = set(), None
+    seq_of_seg = [b for b in range(len(lengths)) for _ in range(offsets[b], offsets[b + 1])]
+    ranges = [struct.unpack_from("<2i", raw, o_ranges + 8 * b) for b in range(batch)]
+    for w in range(n_work):
+        seg, seq, t0, nt, part = struct.unpack_from("<5i", raw, o_work + 32 * w)
+        assert seq == seq_of_seg[seg] and nt > 0 and (prev is None or nt <= prev)
+        prev = nt
+        tiles = set(range(t0, t0 + nt))
+        assert not (tiles & covered[seg])
+        covered[seg] |= tiles
+        assert part not in parts and ranges[seq][0] <= part < ranges[seq][0] + ranges[seq][1]
+        parts.add(part)
+        if segs[seg].kind == nv.PKV_SEG_KIVI and nt > 4:
+            assert t0 % 4 == 0
+    for s, got in zip(segs, covered):
+        per = 32 if s.kind == nv.PKV_SEG_FP16 else 64
+        assert got == set(range((s.seq_len + per - 1) // per))
+    assert sorted(parts) == list(range(n_parts)) and sum(r[1] for r in ranges) == n_parts
+    # a per-token-layout segment is not a batched shape
+    bad = (nv.Segment * 1)(nv.Segment(*[0x1000 * (k + 1) for k in range(6)], 64, 0, nv.PKV_SEG_PER_TOKEN, 4, 4, 32, 32, 0))
+    one = (ctypes.c_int32 * 2)(0, 1)
+    assert L.pkv_decode_batch_plan(bad, one, 1, 28, 4, 128, 148, None, 0, ctypes.byref(tb), ctypes.byref(wb)) == nv.PKV_E_LAYOUT
