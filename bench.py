@@ -47,8 +47,11 @@ def parse_args():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--prompt", type=int, default=32768, help="prompt-tier tokens per layer")
     ap.add_argument("--layers", type=int, default=28)
-    ap.add_argument("--workload", choices=("decode", "pack"), default="decode",
-                    help="decode: the headline decode-attention step; pack: prefill quantise+pack and cold cooling")
+    ap.add_argument("--workload", choices=("decode", "pack", "serving", "longctx"), default="decode",
+                    help="decode: the headline decode-attention step; pack: prefill quantise+pack and cold cooling; "
+                         "serving: batch of 64 jittered sequences, batch-sharded over the GPUs; "
+                         "longctx: 262144-token batch-1 decode, sequence-sharded over the GPUs")
+    ap.add_argument("--batch", type=int, default=64, help="serving: sequences in the whole job")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the context sweep, the SDPA baselines and the CPU baseline")
     return ap.parse_args()
@@ -380,6 +383,250 @@ def run_pack_workload(args):
                       "cold_config": "64 aged of 192 hot tokens -> keep 32, 4-bit, 4 KV heads, one launch (python call included)"}))
 
 
+# ----------------------------------------------------------------------------- multi-GPU set-up shared by the sharded workloads
+def dist_setup():
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: phasekv_b200 has no CPU path")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    barrier = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        barrier = lambda: (dist.barrier(), torch.cuda.synchronize())  # noqa: E731
+    return torch, dist, world, rank, local_rank, device, barrier
+
+
+def max_over_ranks(torch, dist, world, device, values):
+    if world == 1:
+        return values
+    t = torch.tensor(values, device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(x) for x in t]
+
+
+# ----------------------------------------------------------------------------- batched serving workload
+def run_serving_workload(args):
+    """Batched serving decode: `--batch` sequences of 8192 prompt tokens @2-bit + 512 cold @4-bit + 128 hot
+    (each length jittered by +-25 %), all layers, sharded by batch over the GPUs with no collective (strong
+    scaling: the batch is fixed).  A step is one decode token: per layer ONE batched split-K launch + one merge
+    launch over this rank's sequences.  Also timed: the same step as a loop of batch-1 calls over the sequences,
+    which is how the reference's batch-1 entry point would be driven."""
+    torch, dist, world, rank, local_rank, device, barrier = dist_setup()
+    from phasekv_b200 import _native as nv
+    from phasekv_b200 import sharding, workloads
+    from phasekv_b200.kernels import attention_cuda as attn
+    s = workloads.QWEN2_5_7B
+    lengths = workloads.jittered_lengths(0, args.batch, 8192, 512, 128, hot_capacity=192)
+    mine = sharding.batch_shard(args.batch, world, rank)
+    plans, qs, tiers_all = [], [], []
+    for layer in range(args.layers):
+        tiers, q = [], []
+        for i in mine:
+            p, c, h = lengths[i]
+            t, qq = workloads.gpu_three_tier(s, p, PROMPT_BITS, c, COLD_BITS, h, workloads.layer_seed(1, layer, i), device)
+            tiers.append(t), q.append(qq)
+        plans.append(attn.BatchDecodePlan(tiers, s.num_q_heads))
+        qs.append(torch.stack(q))
+        tiers_all.append(tiers)
+    job_bytes = args.layers * sum(workloads.decode_algorithmic_bytes(s, p, PROMPT_BITS, c, COLD_BITS, h, GROUP, GROUP)
+                                  for p, c, h in lengths)
+    rank_layer_bytes = sum(workloads.decode_algorithmic_bytes(s, *_pch(lengths[i]), GROUP, GROUP) for i in mine)
+    L = nv.lib()
+    ws = torch.empty(max(p.workspace_bytes for p in plans), dtype=torch.uint8, device=device)
+    outs = [torch.empty_like(q) for q in qs]
+
+    def step():
+        stream = nv.stream_of(device)
+        for p, q, o in zip(plans, qs, outs):
+            nv.check(L.pkv_decode_attention_batched(q.data_ptr(), p.table_host.data_ptr(), p.table_device.data_ptr(),
+                                                    1.0 / (s.head_dim ** 0.5), ws.data_ptr(), ws.numel(), o.data_ptr(),
+                                                    stream))
+    torch.cuda.synchronize()
+    clocks = ClockSampler(local_rank)
+    ms = time_graph(torch, step, args.steps, max(args.warmup, 3), barrier, sampler=clocks)
+
+    # end to end through the Python entry point: q from pinned host memory, outputs back to the host
+    q_host = [q.cpu().pin_memory() for q in qs]
+    o_host = [torch.empty_like(q) for q in q_host]
+    o_host = [o.pin_memory() for o in o_host]
+    q_dev = [torch.empty_like(q) for q in qs]
+
+    def e2e_step():
+        for i, p in enumerate(plans):
+            q_dev[i].copy_(q_host[i], non_blocking=True)
+            o_host[i].copy_(attn.fused_phasekv_decode_batched(q_dev[i], p, s.num_q_heads), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    for _ in range(3):
+        e2e_step()
+    if barrier:
+        barrier()
+    n_e2e = max(3, min(args.steps, 20))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    e1.record()
+    e1.synchronize()
+    ms_e2e = e0.elapsed_time(e1) / n_e2e
+
+    # the same step as a loop of batch-1 calls (2 layers, scaled)
+    loop_layers = min(2, args.layers)
+
+    def loop_step():
+        for layer in range(loop_layers):
+            for i, t in enumerate(tiers_all[layer]):
+                attn.fused_phasekv_decode(qs[layer][i], t, s.num_q_heads)
+    ms_loop = time_graph(torch, loop_step, 10, 3) * args.layers / loop_layers
+
+    ms, ms_e2e, ms_loop = max_over_ranks(torch, dist, world, device, [ms, ms_e2e, ms_loop])
+    peak, peak_kind = measured_peak()
+    achieved = rank_layer_bytes / (ms / args.layers * 1e-3) / 1e9
+    h2d = sum(q.numel() * 2 for q in qs) * world
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": job_bytes / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16 codes x f16, f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"qwen2.5-7b batched serving decode, {args.layers} layers, batch {args.batch} "
+                                   "(8192 prompt tok @2-bit KIVI + 512 cold @4-bit + 128 hot fp16 per sequence, lengths "
+                                   "jittered +-25 %), 28q/4kv heads, hd 128, gs 32",
+                       "batch": args.batch, "layers": args.layers, "sequences_per_gpu": len(mine),
+                       "l2_policy": "inputs larger than L2 (distinct KV per layer and sequence)",
+                       "parallelism": "batch-sharded, no collective"},
+            "us_per_layer": ms / args.layers * 1e3, "tokens_per_s": args.batch / (ms * 1e-3),
+            "e2e": {"value": job_bytes / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": h2d, "ms_per_step": ms_e2e},
+            "gpu_launches": 2 * args.layers * args.steps,
+            "per_sequence_loop": {"ms_per_step": ms_loop, "speedup_of_batched": ms_loop / ms,
+                                  "sample": f"{loop_layers} of {args.layers} layers, scaled"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": f"of {peak_kind}",
+                         "kernel": "batched split-K decode + merge, per layer, rank 0's share",
+                         "algorithmic_bytes_per_launch": rank_layer_bytes},
+            "clocks": clocks.summary(),
+        }))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _pch(length):
+    p, c, h = length
+    return p, PROMPT_BITS, c, COLD_BITS, h
+
+
+# ----------------------------------------------------------------------------- long-context workload
+LONG_PROMPT, LONG_COLD = 262144, 1024
+
+
+def run_longctx_workload(args):
+    """Long-context batch-1 decode: 262144 prompt tokens @2-bit cut into one contiguous shard per GPU, 1024 cold
+    tokens @4-bit and 128 hot tokens on rank 0.  Per layer every rank computes the un-normalised partial of its
+    shard, the partials (Hq*(hd+2)*4 bytes per rank) are all-gathered over NVLink (NCCL) and merged on every
+    rank.  Strong scaling: the context is fixed.  The layers are chained through the stream as they would be in
+    a model (layer l+1 is launched behind layer l's exchange)."""
+    torch, dist, world, rank, local_rank, device, barrier = dist_setup()
+    from phasekv_b200 import sharding, workloads
+    s = workloads.QWEN2_5_7B
+    start, end = sharding.sequence_bounds(LONG_PROMPT, world)[rank]
+    if world == 1:
+        # one rank: the exchange is a loopback; a one-rank process group keeps the NCCL variant runnable
+        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:%d" % (29400 + os.getpid() % 500), rank=0,
+                                world_size=1, device_id=device)
+    exchange = sharding.PeerExchange(s.num_q_heads, s.head_dim, device, loopback=(world == 1),
+                                     world=world, rank=rank)
+    layers, layers_nccl, qs = [], [], []
+    for layer in range(args.layers):
+        t, q = workloads.gpu_three_tier(s, end - start, PROMPT_BITS, LONG_COLD if rank == 0 else 0, COLD_BITS,
+                                        HOT_LEN if rank == 0 else 0, workloads.layer_seed(2, layer, rank), device)
+        segs = [(t.prompt.key, t.prompt.value)] + [(c.key, c.value) for c in t.cold]
+        layers.append(sharding.ShardedDecodeLayer(segs, t.hot_k, t.hot_v, s.num_q_heads, s.head_dim, device,
+                                                  exchange=exchange))
+        layers_nccl.append(sharding.ShardedDecodeLayer(segs, t.hot_k, t.hot_v, s.num_q_heads, s.head_dim, device))
+        qs.append(q)
+    layer_bytes = workloads.decode_algorithmic_bytes(s, LONG_PROMPT, PROMPT_BITS, LONG_COLD, COLD_BITS, HOT_LEN, GROUP, GROUP)
+    rank_bytes = workloads.decode_algorithmic_bytes(s, end - start, PROMPT_BITS, LONG_COLD if rank == 0 else 0, COLD_BITS,
+                                                    HOT_LEN if rank == 0 else 0, GROUP, GROUP)
+
+    def step():
+        for lay, q in zip(layers, qs):
+            lay.run(q)
+
+    def step_nccl():
+        for lay, q in zip(layers_nccl, qs):
+            lay.run(q)
+    step(), step_nccl()
+    torch.cuda.synchronize()
+    same = all(bool(torch.equal(a.out, b.out)) for a, b in zip(layers, layers_nccl))
+    clocks = ClockSampler(local_rank)
+    ms = time_graph(torch, step, args.steps, max(args.warmup, 3), barrier, sampler=clocks)
+    how = "cuda graph"
+    try:
+        ms_nccl = time_graph(torch, step_nccl, args.steps, max(args.warmup, 3), barrier)
+    except Exception as exc:  # a collective that cannot be captured
+        ms_nccl, how = None, how + f"; NCCL variant not captured ({type(exc).__name__})"
+    timed_out = exchange.timed_out()
+    # end to end: q from pinned host memory per layer, merged output back to the host
+    q_host = [q.cpu().pin_memory() for q in qs]
+    o_host = [torch.empty_like(q).pin_memory() for q in q_host]
+    q_dev = [torch.empty_like(q) for q in qs]
+
+    def e2e_step():
+        for i, lay in enumerate(layers):
+            q_dev[i].copy_(q_host[i], non_blocking=True)
+            o_host[i].copy_(lay.run(q_dev[i]), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    for _ in range(3):
+        e2e_step()
+    if barrier:
+        barrier()
+    n_e2e = max(3, min(args.steps, 20))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    e1.record()
+    e1.synchronize()
+    ms_e2e = e0.elapsed_time(e1) / n_e2e
+    ms, ms_e2e, ms_nccl = max_over_ranks(torch, dist, world, device, [ms, ms_e2e, ms_nccl or 0.0])
+    peak, peak_kind = measured_peak()
+    achieved = rank_bytes / (ms / args.layers * 1e-3) / 1e9
+    io = args.layers * s.num_q_heads * s.head_dim * 2
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": layer_bytes * args.layers / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16 codes x f16, f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"qwen2.5-7b long-context batch-1 decode, {args.layers} layers x ({LONG_PROMPT} prompt tok "
+                                   f"@2-bit KIVI sequence-sharded + {LONG_COLD} cold @4-bit + {HOT_LEN} hot fp16 on rank 0), "
+                                   "28q/4kv heads, hd 128, gs 32",
+                       "layers": args.layers, "prompt_tokens_per_gpu": end - start,
+                       "l2_policy": "inputs larger than L2 (distinct KV per layer)",
+                       "parallelism": f"sequence-sharded x{world}; per layer every rank pushes its partial "
+                                      f"({s.num_q_heads * (s.head_dim + 2) * 4} B) into the peers' memory over NVLink and "
+                                      "merges what arrived, inside one kernel (no collective library)", "timed_as": how},
+            "us_per_layer": ms / args.layers * 1e3,
+            "nccl_all_gather_variant": {"ms_per_step": ms_nccl or None, "same_output_bits": same},
+            "exchange_wait_timed_out": timed_out,
+            "e2e": {"value": layer_bytes * args.layers / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": io,
+                    "d2h_bytes_per_step": io, "ms_per_step": ms_e2e},
+            "gpu_launches": 2 * args.layers * args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": f"of {peak_kind}",
+                         "kernel": "split-K decode of rank 0's shard + exchange/merge kernel, per layer",
+                         "algorithmic_bytes_per_launch": rank_bytes},
+            "clocks": clocks.summary(),
+        }))
+    dist.barrier()
+    exchange.close()
+    dist.destroy_process_group()
+
+
 # ----------------------------------------------------------------------------- main arm
 def main():
     args = parse_args()
@@ -388,6 +635,12 @@ def main():
         return
     if args.workload == "pack":
         run_pack_workload(args)
+        return
+    if args.workload == "serving":
+        run_serving_workload(args)
+        return
+    if args.workload == "longctx":
+        run_longctx_workload(args)
         return
     import torch
     import torch.distributed as dist

@@ -177,6 +177,48 @@ int pkv_merge_partials(const float* m, const float* l, const float* acc, int n_p
                        int head_dim, void* out, float* m_out, float* l_out, float* acc_out,
                        pkv_stream_t stream);
 
+/* The same merge over partials that are not packed densely: partial p has its m and l rows ml_stride floats
+ * after those of partial p-1 and its acc rows acc_stride floats after (ml_stride >= Hq, acc_stride >= Hq*hd,
+ * acc_stride % 4 == 0).  This is the layout an all-gather of one flat per-rank message
+ * [acc Hq*hd | m Hq | l Hq] leaves behind (both strides Hq*(hd+2)): the sequence-sharded decode merges the
+ * ranks' partials in place, without repacking. */
+int pkv_merge_partials_strided(const float* m, const float* l, const float* acc, int n_parts, int64_t ml_stride,
+                               int64_t acc_stride, int num_q_heads, int head_dim, void* out, float* m_out,
+                               float* l_out, float* acc_out, pkv_stream_t stream);
+
+/* ---------------------------------------------------------------- multi-GPU ------- */
+
+/* Sequence-sharded decode (long context, batch 1) without a collective library: no counterpart in the
+ * reference, which is single-GPU; the merge algebra is attention_triton.py:257-266, 300-307 across GPUs.
+ * Every rank (one process per GPU of one node) holds a contiguous shard of the prompt tier (one rank also the
+ * cold and hot tiers).  A call is one split-K launch over the local segments plus ONE kernel that merges the
+ * local partials, stores the result into every peer's exchange buffer over NVLink (plain peer stores into
+ * memory mapped with CUDA IPC), publishes an epoch flag, waits for the peers' rows to arrive in its OWN buffer
+ * and merges them; every rank ends with the full out [Hq, hd].  The wait is bounded: after the spin limit the
+ * kernel sets a status word, writes NaN to its output rows and returns (read it with pkv_exchange_status).
+ *
+ * Set-up (allocates; not for the request path): pkv_exchange_create allocates this rank's buffer on the current
+ * device and returns a 64-byte IPC handle; the caller gathers the handles of all ranks in rank order (any host
+ * transport) and passes the world*64 bytes to pkv_exchange_connect.  All ranks must make the same sequence of
+ * pkv_decode_attention_sharded calls on an exchange; calls on one exchange must not overlap on the GPU.
+ * pkv_exchange_connect_loopback maps every peer slot onto the local buffer (single-process testing: with
+ * world 1 it is a complete exchange, with world > 1 the peers never arrive and the bounded wait runs out). */
+typedef struct pkv_exchange pkv_exchange_t;
+#define PKV_IPC_HANDLE_BYTES 64
+#define PKV_MAX_WORLD 16
+int pkv_exchange_create(int world, int rank, int num_q_heads, int head_dim, pkv_exchange_t** ex /* host */,
+                        void* handle_out /* host, 64 bytes */);
+int pkv_exchange_connect(pkv_exchange_t* ex, const void* handles /* host, world * 64 bytes */);
+int pkv_exchange_connect_loopback(pkv_exchange_t* ex);
+int pkv_exchange_set_spin_limit(pkv_exchange_t* ex, unsigned polls);
+int pkv_exchange_status(pkv_exchange_t* ex, int* timed_out /* host; synchronises */);
+int pkv_exchange_destroy(pkv_exchange_t* ex);
+/* n_segs may be 0 (a rank without tokens contributes the neutral partial; q, segs, workspace are then unused). */
+int pkv_decode_attention_sharded(const void* q, const pkv_segment_t* segs /* host */, int n_segs,
+                                 int num_q_heads, int num_kv_heads, int head_dim, float sm_scale, int sm_count,
+                                 void* workspace, size_t workspace_bytes, pkv_exchange_t* ex, void* out,
+                                 pkv_stream_t stream);
+
 /* ---------------------------------------------------------------- cold tier -------- */
 
 /* phasekv_cache.py:322-340 _cool_aged_tokens for one layer: among the oldest `aged` tokens of the

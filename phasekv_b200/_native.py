@@ -65,6 +65,15 @@ _SIGNATURES = {
                                ctypes.POINTER(ctypes.c_size_t)], _I32),
     "pkv_decode_attention_batched": ([_VP, _VP, _VP, _F32, _VP, ctypes.c_size_t, _VP, _VP], _I32),
     "pkv_merge_partials": ([_VP, _VP, _VP, _I32, _I32, _I32, _VP, _VP, _VP, _VP, _VP], _I32),
+    "pkv_merge_partials_strided": ([_VP, _VP, _VP, _I32, _I64, _I64, _I32, _I32, _VP, _VP, _VP, _VP, _VP], _I32),
+    "pkv_exchange_create": ([_I32, _I32, _I32, _I32, ctypes.POINTER(_VP), _VP], _I32),
+    "pkv_exchange_connect": ([_VP, _VP], _I32),
+    "pkv_exchange_connect_loopback": ([_VP], _I32),
+    "pkv_exchange_set_spin_limit": ([_VP, ctypes.c_uint], _I32),
+    "pkv_exchange_status": ([_VP, ctypes.POINTER(_I32)], _I32),
+    "pkv_exchange_destroy": ([_VP], _I32),
+    "pkv_decode_attention_sharded": ([_VP, ctypes.POINTER(Segment), _I32, _I32, _I32, _I32, _F32, _I32, _VP,
+                                      ctypes.c_size_t, _VP, _VP, _VP], _I32),
     "pkv_cold_select_pack": ([_VP, _VP, _I64, _I64, _I32, _I64, _I64, _I64, _I32, _I64,
                               _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP], _I32),
 }

@@ -208,14 +208,14 @@ decode_generic_kernel(const __grid_constant__ DecodeArgs a) {
 
 __global__ void __launch_bounds__(kMergeThreads)
 merge_partials_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
-                      const float* __restrict__ pacc, int n_parts, int Hq, int hd,
+                      const float* __restrict__ pacc, int n_parts, size_t ml_stride, size_t acc_stride, int hd,
                       __half* __restrict__ out, float* __restrict__ m_out,
                       float* __restrict__ l_out, float* __restrict__ acc_out) {
     // When launched as a programmatic dependent of the split-K kernel this grid may already be resident while
     // that kernel finishes; wait here for its results (a no-op for an ordinary launch).
     cudaGridDependencySynchronize();
     cudaTriggerProgrammaticLaunchCompletion();  // the next kernel of the stream may start its own prologue
-    merge_parts(pm, pl, pacc, n_parts, Hq, hd, blockIdx.x, out, m_out, l_out, acc_out);
+    merge_parts(pm, pl, pacc, n_parts, ml_stride, acc_stride, hd, blockIdx.x, out, m_out, l_out, acc_out);
 }
 
 int check_segments(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int hd) {
@@ -346,14 +346,16 @@ int pkv_decode_workspace_bytes(const pkv_segment_t* segs, int n_segs, int num_q_
     return PKV_OK;
 }
 
-int pkv_decode_attention(const void* q, const pkv_segment_t* segs, int n_segs, int num_q_heads,
-                         int num_kv_heads, int head_dim, float sm_scale, int sm_count, void* workspace,
-                         size_t workspace_bytes, void* out, float* m, float* l, float* acc,
-                         pkv_stream_t stream) {
+}  // extern "C"
+
+namespace pkv {
+// Validation, planning and the split-K launches of one decode call; the partials land in `workspace`.
+int run_splitk(const void* q, const pkv_segment_t* segs, int n_segs, int num_q_heads, int num_kv_heads,
+               int head_dim, float sm_scale, int sm_count, void* workspace, size_t workspace_bytes,
+               cudaStream_t s, SplitKParts* parts) {
     const int rc = check_segments(segs, n_segs, num_q_heads, num_kv_heads, head_dim);
     if (rc != PKV_OK) return rc;
     if (!q || !workspace) return PKV_E_NULL;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
     const DecodePlan plan = plan_decode(segs, n_segs, num_q_heads, num_kv_heads, head_dim, sm_count);
     const size_t W = (size_t)plan.total_work();
     const size_t need = W * num_q_heads * (head_dim + 2) * sizeof(float);
@@ -424,6 +426,27 @@ int pkv_decode_attention(const void* q, const pkv_segment_t* segs, int n_segs, i
         decode_generic_kernel<<<grid, kThreads, smem, s>>>(a);
         PKV_LAUNCH_CHECK();
     }
+    parts->n = W;
+    parts->pm = pm;
+    parts->pl = pl;
+    parts->pacc = pacc;
+    return PKV_OK;
+}
+}  // namespace pkv
+
+extern "C" {
+
+int pkv_decode_attention(const void* q, const pkv_segment_t* segs, int n_segs, int num_q_heads,
+                         int num_kv_heads, int head_dim, float sm_scale, int sm_count, void* workspace,
+                         size_t workspace_bytes, void* out, float* m, float* l, float* acc,
+                         pkv_stream_t stream) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    SplitKParts parts;
+    const int rc = run_splitk(q, segs, n_segs, num_q_heads, num_kv_heads, head_dim, sm_scale, sm_count, workspace,
+                              workspace_bytes, s, &parts);
+    if (rc != PKV_OK) return rc;
+    const size_t W = parts.n;
+    float *pm = parts.pm, *pl = parts.pl, *pacc = parts.pacc;
     static const int dbg = getenv("PKV_DEBUG_SKIP") ? atoi(getenv("PKV_DEBUG_SKIP")) : 0;
     if (dbg & 1) return PKV_OK;
     {
@@ -442,8 +465,9 @@ int pkv_decode_attention(const void* q, const pkv_segment_t* segs, int n_segs, i
         const float* cpm = pm;
         const float* cpl = pl;
         const float* cpacc = pacc;
-        PKV_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partials_kernel, cpm, cpl, cpacc, (int)W, num_q_heads, head_dim,
-                                        static_cast<__half*>(out), m, l, acc));
+        PKV_CUDA_TRY(cudaLaunchKernelEx(&cfg, merge_partials_kernel, cpm, cpl, cpacc, (int)W, (size_t)num_q_heads,
+                                        (size_t)num_q_heads * head_dim, head_dim, static_cast<__half*>(out), m, l,
+                                        acc));
     }
     return PKV_OK;
 }
@@ -451,12 +475,21 @@ int pkv_decode_attention(const void* q, const pkv_segment_t* segs, int n_segs, i
 int pkv_merge_partials(const float* m, const float* l, const float* acc, int n_parts, int num_q_heads,
                        int head_dim, void* out, float* m_out, float* l_out, float* acc_out,
                        pkv_stream_t stream) {
+    return pkv_merge_partials_strided(m, l, acc, n_parts, num_q_heads, (int64_t)num_q_heads * head_dim,
+                                      num_q_heads, head_dim, out, m_out, l_out, acc_out, stream);
+}
+
+int pkv_merge_partials_strided(const float* m, const float* l, const float* acc, int n_parts, int64_t ml_stride,
+                               int64_t acc_stride, int num_q_heads, int head_dim, void* out, float* m_out,
+                               float* l_out, float* acc_out, pkv_stream_t stream) {
     if (!m || !l || !acc) return PKV_E_NULL;
     if (n_parts <= 0 || num_q_heads <= 0 || head_dim <= 0) return PKV_E_SHAPE;
+    if (ml_stride < num_q_heads || acc_stride < (int64_t)num_q_heads * head_dim) return PKV_E_SHAPE;
     if (head_dim > 256) return PKV_E_LIMIT;
-    if (head_dim % 4 || (reinterpret_cast<uintptr_t>(acc) & 15u)) return PKV_E_LAYOUT;
+    if (head_dim % 4 || acc_stride % 4 || (reinterpret_cast<uintptr_t>(acc) & 15u)) return PKV_E_LAYOUT;
     merge_partials_kernel<<<num_q_heads, kMergeThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        m, l, acc, n_parts, num_q_heads, head_dim, static_cast<__half*>(out), m_out, l_out, acc_out);
+        m, l, acc, n_parts, (size_t)ml_stride, (size_t)acc_stride, head_dim, static_cast<__half*>(out), m_out, l_out,
+        acc_out);
     PKV_LAUNCH_CHECK();
     return PKV_OK;
 }
@@ -538,7 +571,7 @@ merge_batched_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
     const int seq = blockIdx.y;
     const BatchRange r = ranges[seq];
     merge_parts(pm + (size_t)r.part_begin * Hq, pl + (size_t)r.part_begin * Hq,
-                pacc + (size_t)r.part_begin * Hq * hd, r.n_parts, Hq, hd, blockIdx.x,
+                pacc + (size_t)r.part_begin * Hq * hd, r.n_parts, (size_t)Hq, (size_t)Hq * hd, hd, blockIdx.x,
                 out + (size_t)seq * Hq * hd, nullptr, nullptr, nullptr);
 }
 

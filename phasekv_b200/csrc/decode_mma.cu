@@ -528,7 +528,7 @@ __device__ __forceinline__ void issue_hot_tile(const SegDev& sg, int kvh, long l
 
 __device__ __forceinline__ void compute_hot_tile(unsigned sa, const unsigned (&qh)[8][2], float c_qk, WarpState& st,
                                                  int valid, int lane) {
-    const int g = lane >> 2, t = lane & 3;
+    const int g = lane >> 2;
     const int mi = lane >> 3, mr = lane & 7;  // ldmatrix: this lane addresses row mr of matrix mi
     float sacc[2][4];
 #pragma unroll

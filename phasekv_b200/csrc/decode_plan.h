@@ -40,6 +40,18 @@ struct DecodePlan {
     int total_work() const { return fast_work + generic_work; }
 };
 
+// Where the split-K launches of one call left their partials: pm, pl [n][Hq], pacc [n][Hq][hd].
+struct SplitKParts {
+    size_t n;
+    float* pm;
+    float* pl;
+    float* pacc;
+};
+
+int run_splitk(const void* q, const pkv_segment_t* segs, int n_segs, int num_q_heads, int num_kv_heads,
+               int head_dim, float sm_scale, int sm_count, void* workspace, size_t workspace_bytes,
+               cudaStream_t stream, SplitKParts* parts);
+
 DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int hd, int sm_count);
 
 }  // namespace pkv

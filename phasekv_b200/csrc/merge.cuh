@@ -12,12 +12,19 @@ namespace pkv {
 constexpr int kMergeThreads = 256;
 constexpr int kMergeMaxInflight = 6;  // parts per thread held in registers at once
 
-// pm, pl, pacc point at the first of the n_parts partial rows ([part][Hq] and [part][Hq][hd]); out, m_out, l_out,
-// acc_out at the result rows of this query head's sequence ([Hq][hd] and [Hq]).
-__device__ __forceinline__ void merge_parts(const float* __restrict__ pm, const float* __restrict__ pl,
-                                            const float* __restrict__ pacc, int n_parts, int Hq, int hd, int h,
-                                            __half* __restrict__ out, float* __restrict__ m_out,
-                                            float* __restrict__ l_out, float* __restrict__ acc_out) {
+// pm, pl, pacc point at the first of the n_parts partials ([Hq] and [Hq][hd] each); consecutive partials are
+// ml_stride floats apart in pm and pl and acc_stride floats apart in pacc (Hq and Hq * hd when the arrays are
+// dense).  out, m_out, l_out, acc_out point at the result rows of this query head's sequence.
+// COHERENT: the partials may have been written by another GPU while this kernel runs; read them through L2
+// (ld.cg) instead of the non-coherent path.
+//
+// merge_reduce leaves the merged (M, L) in every thread and A[tid] in threads tid < hd; no partials at all give
+// the neutral element (-inf, 0, 0).  It uses static shared memory: put a __syncthreads() between two calls.
+template <bool COHERENT = false>
+__device__ __forceinline__ void merge_reduce(const float* __restrict__ pm, const float* __restrict__ pl,
+                                             const float* __restrict__ pacc, int n_parts, size_t ml_stride,
+                                             size_t acc_stride, int hd, int h, float& M_out, float& L_out,
+                                             float& A_out) {
     __shared__ float red_m[8];
     __shared__ float red_l[8];
     __shared__ __align__(16) float red_acc[8][256];
@@ -42,11 +49,11 @@ __device__ __forceinline__ void merge_parts(const float* __restrict__ pm, const 
             wm[u] = -INFINITY;
             wl[u] = 0.f;
             if (p < n_parts) {
-                const float4* row = reinterpret_cast<const float4*>(pacc + ((size_t)p * Hq + h) * hd);
-                if (v0) r0[u] = __ldg(row + lane);
-                if (v1) r1[u] = __ldg(row + lane + 32);
-                wm[u] = __ldg(pm + (size_t)p * Hq + h);
-                wl[u] = __ldg(pl + (size_t)p * Hq + h);
+                const float4* row = reinterpret_cast<const float4*>(pacc + (size_t)p * acc_stride + (size_t)h * hd);
+                if (v0) r0[u] = COHERENT ? __ldcg(row + lane) : __ldg(row + lane);
+                if (v1) r1[u] = COHERENT ? __ldcg(row + lane + 32) : __ldg(row + lane + 32);
+                wm[u] = COHERENT ? __ldcg(pm + (size_t)p * ml_stride + h) : __ldg(pm + (size_t)p * ml_stride + h);
+                wl[u] = COHERENT ? __ldcg(pl + (size_t)p * ml_stride + h) : __ldg(pl + (size_t)p * ml_stride + h);
             }
         }
 #pragma unroll
@@ -80,10 +87,26 @@ __device__ __forceinline__ void merge_parts(const float* __restrict__ pm, const 
     float L = 0.f;
 #pragma unroll
     for (int w = 0; w < 8; ++w) L += red_l[w];
+    float A = 0.f;
     if (tid < hd) {
-        float A = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; ++w) A += red_acc[w][tid];
+    }
+    M_out = mx;
+    L_out = L;
+    A_out = A;
+}
+
+template <bool COHERENT = false>
+__device__ __forceinline__ void merge_parts(const float* __restrict__ pm, const float* __restrict__ pl,
+                                            const float* __restrict__ pacc, int n_parts, size_t ml_stride,
+                                            size_t acc_stride, int hd, int h,
+                                            __half* __restrict__ out, float* __restrict__ m_out,
+                                            float* __restrict__ l_out, float* __restrict__ acc_out) {
+    float mx, L, A;
+    merge_reduce<COHERENT>(pm, pl, pacc, n_parts, ml_stride, acc_stride, hd, h, mx, L, A);
+    const int tid = threadIdx.x;
+    if (tid < hd) {
         if (out) out[(size_t)h * hd + tid] = __float2half_rn(A / L);
         if (acc_out) acc_out[(size_t)h * hd + tid] = A;
     }

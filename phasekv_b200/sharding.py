@@ -98,25 +98,128 @@ def empty_partial(num_q_heads: int, head_dim: int, device) -> Tuple[torch.Tensor
             torch.zeros((num_q_heads, head_dim), dtype=torch.float32, device=device))
 
 
+class PeerExchange:
+    """This rank's end of the peer-to-peer exchange used by the sequence-sharded decode: a buffer in this
+    GPU's memory that every other rank of the node maps through CUDA IPC and writes its partial into.  One
+    exchange serves all layers of a model (its calls are ordered by the stream).  With ``loopback=True`` no
+    other process is involved: every peer slot is the local buffer (``world == 1`` is then a complete
+    exchange; a larger ``world`` only exercises the bounded wait)."""
+
+    def __init__(self, num_q_heads: int, head_dim: int, device, group: Optional[dist.ProcessGroup] = None,
+                 loopback: bool = False, world: Optional[int] = None, rank: Optional[int] = None):
+        import ctypes
+        from . import _native as nv
+        self.nv, self.device = nv, device
+        self.world = world if world is not None else dist.get_world_size(group)
+        self.rank = rank if rank is not None else dist.get_rank(group)
+        self.handle = ctypes.c_void_p()
+        mine = ctypes.create_string_buffer(64)
+        with torch.cuda.device(device):
+            nv.check(nv.lib().pkv_exchange_create(self.world, self.rank, num_q_heads, head_dim,
+                                                  ctypes.byref(self.handle), mine))
+            if loopback:
+                nv.check(nv.lib().pkv_exchange_connect_loopback(self.handle))
+            else:
+                handles: List[Optional[bytes]] = [None] * self.world
+                dist.all_gather_object(handles, mine.raw, group=group)
+                nv.check(nv.lib().pkv_exchange_connect(self.handle, b"".join(handles)))
+                dist.barrier(group=group)  # every rank has mapped every buffer before anyone pushes
+
+    def set_spin_limit(self, polls: int) -> None:
+        self.nv.check(self.nv.lib().pkv_exchange_set_spin_limit(self.handle, polls))
+
+    def timed_out(self) -> bool:
+        """True once any wait of this rank has run out (synchronises the device)."""
+        import ctypes
+        flag = ctypes.c_int(0)
+        with torch.cuda.device(self.device):
+            self.nv.check(self.nv.lib().pkv_exchange_status(self.handle, ctypes.byref(flag)))
+        return bool(flag.value)
+
+    def close(self) -> None:
+        if self.handle:
+            with torch.cuda.device(self.device):
+                torch.cuda.synchronize(self.device)
+                self.nv.check(self.nv.lib().pkv_exchange_destroy(self.handle))
+            self.handle = None
+
+
+class ShardedDecodeLayer:
+    """One layer of the sequence-sharded decode on this rank, with every buffer allocated up front so that
+    a step is three launches: split-K decode of the local shard into a flat partial ``[acc Hq*hd | m Hq | l Hq]``
+    (float32), one all-gather of that message (``Hq * (hd + 2) * 4`` bytes per rank), and one merge that
+    reads the gathered partials in place (``pkv_merge_partials_strided``).
+
+    ``segments``: this rank's ``(key, value)`` pairs with batch dim 1 (its shard of the prompt tier and, on
+    one rank, the cold segments); ``hot_k``/``hot_v``: ``[1, Hkv, hot, hd]`` on the rank that owns the hot
+    tier, else ``None``.  A rank without any tokens contributes the neutral partial.
+
+    With ``exchange`` (a :class:`PeerExchange`) the all-gather and the merge become part of ONE kernel that
+    pushes the partial into the peers' memory over NVLink and merges what the peers pushed here: two launches
+    per step, no collective library on the path."""
+
+    def __init__(self, segments: Sequence, hot_k, hot_v, num_attention_heads: int, head_dim: int, device,
+                 group: Optional[dist.ProcessGroup] = None, exchange: Optional[PeerExchange] = None):
+        from . import _native as nv
+        from .kernels import attention_cuda as ac
+        from .kernels.tiers import LayerTiers, PackedKVSegment
+        import ctypes
+        self.nv, self.group, self.device, self.exchange = nv, group, device, exchange
+        self.hq, self.hd = num_attention_heads, head_dim
+        self.world = exchange.world if exchange is not None else dist.get_world_size(group)
+        n = self.hq * (self.hd + 2)
+        self.part = torch.zeros(n, dtype=torch.float32, device=device)
+        self.part[self.hq * self.hd:self.hq * self.hd + self.hq] = float("-inf")  # neutral element
+        self.gathered = torch.empty(self.world * n, dtype=torch.float32, device=device)
+        self.out = torch.empty((self.hq, self.hd), dtype=torch.float16, device=device)
+        segs = [PackedKVSegment(k, v) for k, v in segments]
+        hot_len = 0 if hot_k is None else hot_k.shape[-2]
+        self.segs, self.hkv, self.sms = None, 1, nv.sm_count(device)
+        self.ws = torch.empty(16, dtype=torch.uint8, device=device)
+        if segs or hot_len:
+            if segs:
+                tiers = LayerTiers(prompt=segs[0], cold=segs[1:], hot_k=hot_k, hot_v=hot_v, hot_len=hot_len)
+                seg_list, self._keep, self.hkv, _ = ac.layer_segments(tiers)
+            else:
+                s, self._keep = ac._fp16_segment(hot_k[0], hot_v[0])
+                seg_list, self.hkv = [s], hot_k.shape[1]
+            self.segs = (nv.Segment * len(seg_list))(*seg_list)
+            self.sms = nv.sm_count(device)
+            need = ctypes.c_size_t(0)
+            nv.check(nv.lib().pkv_decode_workspace_bytes(self.segs, len(seg_list), self.hq, self.hkv, self.hd, self.sms,
+                                                         ctypes.byref(need)))
+            self.ws = torch.empty(max(need.value, 16), dtype=torch.uint8, device=device)
+
+    def run(self, q: torch.Tensor) -> torch.Tensor:
+        nv, L = self.nv, self.nv.lib()
+        stream = nv.stream_of(self.device)
+        if self.exchange is not None:
+            n_segs = 0 if self.segs is None else len(self.segs)
+            nv.check(L.pkv_decode_attention_sharded(q.data_ptr(), self.segs, n_segs, self.hq, self.hkv, self.hd,
+                                                    1.0 / (self.hd ** 0.5), self.sms, self.ws.data_ptr(),
+                                                    self.ws.numel(), self.exchange.handle, self.out.data_ptr(), stream))
+            return self.out
+        base, f = self.part.data_ptr(), 4
+        if self.segs is not None:
+            nv.check(L.pkv_decode_attention(q.data_ptr(), self.segs, len(self.segs), self.hq, self.hkv, self.hd,
+                                            1.0 / (self.hd ** 0.5), self.sms, self.ws.data_ptr(), self.ws.numel(),
+                                            None, base + f * self.hq * self.hd, base + f * (self.hq * self.hd + self.hq),
+                                            base, stream))
+        dist.all_gather_into_tensor(self.gathered, self.part, group=self.group)
+        n = self.hq * (self.hd + 2)
+        g = self.gathered.data_ptr()
+        nv.check(L.pkv_merge_partials_strided(g + f * self.hq * self.hd, g + f * (self.hq * self.hd + self.hq), g,
+                                              self.world, n, n, self.hq, self.hd, self.out.data_ptr(), None, None,
+                                              None, stream))
+        return self.out
+
+
 def sequence_sharded_decode(q: torch.Tensor, segments: Sequence, hot_k, hot_v, num_attention_heads: int,
-                            group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+                            group: Optional[dist.ProcessGroup] = None,
+                            exchange: Optional[PeerExchange] = None) -> torch.Tensor:
     """Decode attention of ``q [Hq, hd]`` where this rank holds ``segments`` (its shard of the prompt
     tier and, on one rank, the cold segments; each a ``(key, value)`` pair with batch dim 1) and
     optionally the hot tier ``[1, Hkv, hot, hd]``.  Returns the merged ``[Hq, hd]`` float16 on every rank."""
-    from .kernels import attention_cuda as ac
-    from .kernels.tiers import LayerTiers, PackedKVSegment
-    hq, hd = q.shape
-    segs = [PackedKVSegment(k, v) for k, v in segments]
-    hot_len = 0 if hot_k is None else hot_k.shape[-2]
-    if segs or hot_len:
-        if segs:
-            tiers = LayerTiers(prompt=segs[0], cold=segs[1:], hot_k=hot_k, hot_v=hot_v, hot_len=hot_len)
-            seg_list, keep, hkv, _ = ac.layer_segments(tiers)
-        else:
-            s, keep = ac._fp16_segment(hot_k[0], hot_v[0])
-            seg_list, hkv = [s], hot_k.shape[1]
-        _, (m, l, acc) = ac._run_decode(q.contiguous(), seg_list, keep, num_attention_heads, hkv, False, True)
-    else:
-        m, l, acc = empty_partial(hq, hd, q.device)
-    gm, gl, gacc = gather_partials(m, l, acc, group)
-    return ac._merge_stacked(gm, gl, gacc, want_out=True)[0]
+    layer = ShardedDecodeLayer(segments, hot_k, hot_v, num_attention_heads, q.shape[-1], q.device, group, exchange)
+    with torch.cuda.device(q.device):
+        return layer.run(q.contiguous()).clone()

@@ -37,7 +37,23 @@ def _rank_main(rank, world, port, tmp):
                                       hv.to(dev) if rank == 0 else None, shape.num_q_heads)
         full = oracle.segments_decode_reference(q, [(gk, gv), cold], hk, hv, shape.num_q_heads).float()
         err = (out.float().cpu() - full).abs().max().item()
-        torch.save({"err": err, "ref": full.abs().max().item()}, os.path.join(tmp, f"r{rank}.pt"))
+        # the same through the peer-to-peer exchange kernel (plain peer stores, no NVLS, no collective library)
+        from phasekv_b200.sharding import PeerExchange, ShardedDecodeLayer
+        ex = PeerExchange(shape.num_q_heads, shape.head_dim, dev)
+        try:
+            layer = ShardedDecodeLayer(segs, hk.to(dev) if rank == 0 else None, hv.to(dev) if rank == 0 else None,
+                                       shape.num_q_heads, shape.head_dim, dev, exchange=ex)
+            err_p2p = 0.0
+            for _ in range(4):  # slots alternate with the call parity
+                got = layer.run(q.to(dev)).float().cpu()
+                err_p2p = max(err_p2p, (got - full).abs().max().item())
+            same = bool(torch.equal(layer.out, out))
+            timed_out = ex.timed_out()
+        finally:
+            dist.barrier()
+            ex.close()
+        torch.save({"err": err, "err_p2p": err_p2p, "same": same, "timed_out": timed_out,
+                    "ref": full.abs().max().item()}, os.path.join(tmp, f"r{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
@@ -51,3 +67,4 @@ def test_sequence_sharded_decode_over_nccl(tmp_path):
     for r in range(world):
         res = torch.load(os.path.join(tmp_path, f"r{r}.pt"))
         assert res["err"] <= 2e-3 and res["err"] <= 1e-2 * res["ref"], res
+        assert not res["timed_out"] and res["err_p2p"] <= 2e-3 and res["same"], res
