@@ -234,6 +234,37 @@ int pkv_cold_select_pack(void* hot_k, void* hot_v, int64_t rows, int64_t capacit
                          uint8_t* k_packed, void* k_scale, void* k_mins, uint8_t* v_packed,
                          void* v_scale, void* v_mins, int64_t* indices, pkv_stream_t stream);
 
+/* ---------------------------------------------------------------- stage A (dense cache) -------- */
+
+#define PKV_DTYPE_F16 0
+#define PKV_DTYPE_BF16 1
+#define PKV_DTYPE_F32 2
+
+/* quant.py:34-79 _grouped_affine_quant_dequant (behind quantize_key :82-91, quantize_value :94-101, used in
+ * place on cache slices by prompt_tier.py:107-118 and decode_tier.py:78-88): x viewed as [outer, axis_len, inner]
+ * with `outer_stride` elements between outer indices (0 = dense; larger for a token slice of a longer cache),
+ * groups of `group` (clamped to axis_len by the caller) along axis_len, float32 scale = max(max-min, 1e-8)/qmax
+ * and zero = min, out = round((x-min)/scale).clamp(0, qmax) * scale + min rounded to the element type.
+ * bits 1..15 (>= 16 is the caller's no-op).  out may equal x.  Bit-identical to the reference on a CPU. */
+int pkv_fake_quant(const void* x, void* out, int dtype, int64_t outer, int64_t axis_len, int64_t inner,
+                   int64_t outer_stride, int bits, int64_t group, pkv_stream_t stream);
+
+/* hetero_cache.py:98-113 value_norm_signal: out float32 [rows, n_tokens] = L2 norm over head_dim of the first
+ * n_tokens tokens of each row of v [rows, >= n_tokens, head_dim] (`row_stride` elements between rows). */
+int pkv_value_norm(const void* v, int dtype, int64_t rows, int64_t row_stride, int64_t n_tokens, int head_dim,
+                   float* out, pkv_stream_t stream);
+
+/* hetero_cache.py:157-167 topk_per_head followed by the ascending sort every consumer applies
+ * (hetero_cache.py:146, phasekv_cache.py:332): indices int64 [rows, keep] = positions of the `keep` largest
+ * entries of each row of signal float32 [rows, n], ties to the lower position.  n <= 4096 (PKV_E_LIMIT). */
+int pkv_topk_rows(const float* signal, int64_t rows, int64_t n, int64_t keep, int64_t* indices, pkv_stream_t stream);
+
+/* hetero_cache.py:120-154 evict_per_head / phasekv_cache.py:110-114 _gather_kv for one tensor:
+ * dst [rows, keep, token_bytes] = src [rows, src_tokens, token_bytes] gathered at indices int64 [rows, keep].
+ * token_bytes % 16 == 0, 16-byte aligned buffers. */
+int pkv_gather_tokens(const void* src, void* dst, const int64_t* indices, int64_t rows, int64_t src_tokens,
+                      int64_t keep, int64_t token_bytes, pkv_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -253,3 +253,44 @@ void pkvo_value_norm_topk(const uint16_t* V, int64_t rows, int64_t aged, int hd,
         free(n2);
     }
 }
+
+/*
+ * quant.py:34-79 _grouped_affine_quant_dequant ("fake quantisation" of stage A), on float32:
+ * x viewed as [outer, A, inner], groups of gs (already clamped to [1, A]) along A.  Unlike the packed
+ * path, scale and zero stay float32 and bits may be anything from 1 to 15.  The reference pads the tail
+ * group by repeating the last element (no effect on min / max).  out = q * scale + min with the product
+ * and the sum rounded separately, as torch evaluates `q * scale + g_min`.  The caller converts to and
+ * from the tensor's element type.
+ */
+void pkvo_fake_quant(const float* x, int64_t outer, int64_t A, int64_t inner, int bits, int64_t gs,
+                     float* out) {
+    const float qmax = (float)((1 << bits) - 1);
+    const int64_t ng = (A + gs - 1) / gs;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int64_t o = 0; o < outer; ++o) {
+        for (int64_t j = 0; j < inner; ++j) {
+            const float* xp = x + o * A * inner + j;
+            float* op = out + o * A * inner + j;
+            for (int64_t g = 0; g < ng; ++g) {
+                const int64_t a0 = g * gs;
+                const int64_t a1 = (a0 + gs < A) ? a0 + gs : A;
+                float lo = xp[a0 * inner], hi = lo;
+                for (int64_t a = a0 + 1; a < a1; ++a) {
+                    const float v = xp[a * inner];
+                    lo = v < lo ? v : lo;
+                    hi = v > hi ? v : hi;
+                }
+                float range = hi - lo;
+                if (range < 1e-8f) range = 1e-8f;
+                const float sc = range / qmax;
+                for (int64_t a = a0; a < a1; ++a) {
+                    float q = rintf((xp[a * inner] - lo) / sc);
+                    if (q < 0.f) q = 0.f;
+                    if (q > qmax) q = qmax;
+                    const float prod = q * sc;
+                    op[a * inner] = prod + lo;
+                }
+            }
+        }
+    }
+}

@@ -55,6 +55,8 @@ def lib() -> ctypes.CDLL:
         L.pkvo_unpack_dequantize.argtypes = [vp, vp, vp, i64, i64, i64, i32, i64, vp]
         L.pkvo_attention_dense.argtypes = [vp, vp, vp, i32, i32, i64, i32, vp, vp, vp, vp, vp]
         L.pkvo_value_norm_topk.argtypes = [vp, i64, i64, i32, i64, vp, vp]
+        L.pkvo_fake_quant.argtypes = [vp, i64, i64, i64, i32, i64, vp]
+        L.pkvo_fake_quant.restype = None
         for f in (L.pkvo_pack_low_bits, L.pkvo_unpack_low_bits, L.pkvo_quantize_pack,
                   L.pkvo_unpack_dequantize, L.pkvo_attention_dense, L.pkvo_value_norm_topk,
                   L.pkvo_set_num_threads):
@@ -267,3 +269,29 @@ def value_norm_topk(value: torch.Tensor, keep: int):
     gap = np.zeros(tuple(lead), dtype=np.float64)
     lib().pkvo_value_norm_topk(_ptr(v), rows, aged, hd, keep, _ptr(idx), _ptr(gap))
     return torch.from_numpy(idx), torch.from_numpy(gap)
+
+
+def fake_quant(x: torch.Tensor, bits: int, axis: int, group_size: int) -> torch.Tensor:
+    """quant.py:34-79 ``_grouped_affine_quant_dequant``: quantise and dequantise along ``axis`` with float32
+    scale and zero; same shape and dtype as ``x``; ``bits >= 16`` returns ``x``."""
+    if bits >= 16:
+        return x
+    if bits < 1:
+        raise ValueError(f"bits must be >= 1, got {bits}")
+    axis = axis % x.dim()
+    outer, length, inner = _axis_view(tuple(x.shape), axis)
+    gs = length if group_size is None or group_size <= 0 else min(int(group_size), length)
+    xf = np.ascontiguousarray(x.detach().cpu().float().contiguous().numpy())
+    out = np.empty_like(xf)
+    lib().pkvo_fake_quant(_ptr(xf), outer, length, inner, int(bits), gs, _ptr(out))
+    return torch.from_numpy(out).to(x.dtype)
+
+
+def quantize_key(key: torch.Tensor, bits: int, group_size: int = 32) -> torch.Tensor:
+    """quant.py:82-91: per channel, groups of tokens (axis -2)."""
+    return fake_quant(key, bits, -2, group_size)
+
+
+def quantize_value(value: torch.Tensor, bits: int, group_size: int = 32) -> torch.Tensor:
+    """quant.py:94-101: per token, groups along head_dim (axis -1)."""
+    return fake_quant(value, bits, -1, group_size)

@@ -74,6 +74,10 @@ _SIGNATURES = {
     "pkv_exchange_destroy": ([_VP], _I32),
     "pkv_decode_attention_sharded": ([_VP, ctypes.POINTER(Segment), _I32, _I32, _I32, _I32, _F32, _I32, _VP,
                                       ctypes.c_size_t, _VP, _VP, _VP], _I32),
+    "pkv_fake_quant": ([_VP, _VP, _I32, _I64, _I64, _I64, _I64, _I32, _I64, _VP], _I32),
+    "pkv_value_norm": ([_VP, _I32, _I64, _I64, _I64, _I32, _VP, _VP], _I32),
+    "pkv_topk_rows": ([_VP, _I64, _I64, _I64, _VP, _VP], _I32),
+    "pkv_gather_tokens": ([_VP, _VP, _VP, _I64, _I64, _I64, _I64, _VP], _I32),
     "pkv_cold_select_pack": ([_VP, _VP, _I64, _I64, _I32, _I64, _I64, _I64, _I32, _I64,
                               _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP], _I32),
 }

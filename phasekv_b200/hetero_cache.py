@@ -1,0 +1,129 @@
+"""Stage-A three-tier bookkeeping on a dense KV cache (any object with ``key_cache`` / ``value_cache`` lists of
+``[B, Hkv, S, hd]`` tensors), on CUDA.
+
+Same surface as the part of the reference's ``src/phasekv/hetero_cache.py`` that the decode tier needs:
+``cache_num_layers`` (:36), ``cache_seq_len`` (:40), ``value_norm_signal`` (:98), ``topk_per_head`` (:157),
+``evict_per_head`` (:120) and ``HeteroTierState`` (:175).  The selection signal, the top-k and the per-head
+compaction are one launch each instead of torch pipelines.  Attention-score based prompt selection
+(``observation_votes``, ``pool_scores``) needs the eager attention matrices of the evaluation pipeline and is
+not part of this package.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from . import _native as nv
+from . import quant
+
+
+def cache_num_layers(cache) -> int:
+    return len(cache.key_cache)
+
+
+def cache_seq_len(cache, layer_idx: int = 0) -> int:
+    if len(cache.key_cache) <= layer_idx or cache.key_cache[layer_idx] is None:
+        return 0
+    return cache.key_cache[layer_idx].shape[-2]
+
+
+def value_norm_signal(value_layer: torch.Tensor, token_slice: slice) -> torch.Tensor:
+    """Cheap importance of the tokens in ``token_slice`` of a ``[B, Hkv, S, hd]`` value tensor: the L2 norm of
+    each value vector, float32 ``[B, Hkv, len(slice)]``."""
+    nv.require_cuda(value_layer, "value_layer")
+    b, h, seq, hd = value_layer.shape
+    start, stop, step = token_slice.indices(seq)
+    if step != 1:
+        raise ValueError("token_slice must be contiguous")
+    n = max(0, stop - start)
+    out = torch.empty((b, h, n), dtype=torch.float32, device=value_layer.device)
+    if n == 0:
+        return out
+    v = value_layer if value_layer.is_contiguous() else value_layer.contiguous()
+    view = v[:, :, start:stop, :]
+    with torch.cuda.device(v.device):
+        nv.check(nv.lib().pkv_value_norm(view.data_ptr(), quant._dtype_code(v), b * h, seq * hd, n, hd, out.data_ptr(),
+                                         nv.stream_of(v.device)))
+    return out
+
+
+def topk_per_head(signal: torch.Tensor, select_k: int) -> torch.Tensor:
+    """Positions (relative to the slice) of the ``select_k`` largest entries of ``signal [B, Hkv, n]`` per head,
+    int64 ``[B, Hkv, min(select_k, n)]``.  They come back in ascending position order (the reference returns
+    them in score order and every consumer sorts them); ties go to the lower position."""
+    nv.require_cuda(signal, "signal")
+    b, h, n = signal.shape
+    k = max(0, min(int(select_k), n))
+    out = torch.empty((b, h, k), dtype=torch.long, device=signal.device)
+    if k == 0:
+        return out
+    sig = signal.float().contiguous()
+    with torch.cuda.device(sig.device):
+        nv.check(nv.lib().pkv_topk_rows(sig.data_ptr(), b * h, n, k, out.data_ptr(), nv.stream_of(sig.device)))
+    return out
+
+
+def gather_tokens(tensor: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+    """``tensor [B, Hkv, S, hd]`` gathered along tokens at ``indices [B, Hkv, K]`` (int64) -> ``[B, Hkv, K, hd]``."""
+    nv.require_cuda(tensor, "tensor")
+    b, h, seq, hd = tensor.shape
+    idx = indices.to(device=tensor.device, dtype=torch.long).contiguous()
+    if idx.shape[:2] != (b, h):
+        raise ValueError(f"indices must be [{b}, {h}, K], got {tuple(idx.shape)}")
+    keep = idx.shape[2]
+    src = tensor.contiguous()
+    out = torch.empty((b, h, keep, hd), dtype=tensor.dtype, device=tensor.device)
+    if keep:
+        with torch.cuda.device(src.device):
+            nv.check(nv.lib().pkv_gather_tokens(src.data_ptr(), out.data_ptr(), idx.data_ptr(), b * h, seq, keep,
+                                                hd * tensor.element_size(), nv.stream_of(src.device)))
+    return out
+
+
+def evict_per_head(cache, keep_indices: Sequence[Optional[torch.Tensor]]):
+    """Keep, per layer and per head, the tokens named by ``keep_indices[layer]`` (``[B, Hkv, budget]``; ``None``
+    leaves a layer alone); positions are put in ascending order first so time order is preserved."""
+    for layer in range(cache_num_layers(cache)):
+        idx = keep_indices[layer]
+        if idx is None:
+            continue
+        k = cache.key_cache[layer]
+        idx = torch.sort(idx.to(device=k.device, dtype=torch.long), dim=-1).values
+        cache.key_cache[layer] = gather_tokens(k, idx)
+        cache.value_cache[layer] = gather_tokens(cache.value_cache[layer], idx)
+    return cache
+
+
+@dataclass
+class HeteroTierState:
+    """Where the three tiers sit in the physical cache (prompt ``[0, K0)``, cold ``[K0, K0 + cold_len)``, hot the
+    rest) and how many bits each gets."""
+
+    prompt_len_phys: int = 0
+    cold_len: int = 0
+    prompt_bits: int = 2
+    cold_bits: int = 4
+    group_size: int = 32
+    recent_window: int = 32
+
+    def reset(self) -> None:
+        self.prompt_len_phys = 0
+        self.cold_len = 0
+
+    def hot_len(self, cache) -> int:
+        return max(0, cache_seq_len(cache) - self.prompt_len_phys - self.cold_len)
+
+    def logical_bytes(self, cache) -> int:
+        """Bytes the three tiers would take at their bit widths (the physical tensors stay 16-bit)."""
+        if cache_num_layers(cache) == 0 or cache.key_cache[0] is None:
+            return 0
+        b, hkv, seq, head_dim = cache.key_cache[0].shape
+        layers = cache_num_layers(cache)
+        k0 = max(0, min(self.prompt_len_phys, seq))
+        cold = max(0, min(self.cold_len, seq - k0))
+        hot = max(0, seq - k0 - cold)
+        return (quant.quantized_tier_bytes(k0, layers, hkv, head_dim, self.prompt_bits, self.prompt_bits, self.group_size, b)
+                + quant.quantized_tier_bytes(cold, layers, hkv, head_dim, self.cold_bits, self.cold_bits, self.group_size, b)
+                + quant.fp16_tier_bytes(hot, layers, hkv, head_dim, b))

@@ -213,6 +213,51 @@ def gen_cold(packing, out_dir):
     np.savez_compressed(os.path.join(out_dir, "cold_select.npz"), **out)
 
 
+FAKE_QUANT_CASES = [
+    # shape, axis, bits, group, dtype, seed, kind
+    ((1, 2, 20, 8), -2, 2, 4, "f16", 31, "randn"),
+    ((1, 2, 20, 8), -1, 2, 4, "f16", 32, "randn"),
+    ((1, 4, 100, 128), -2, 2, 32, "f16", 33, "outlier"),
+    ((1, 4, 100, 128), -1, 4, 32, "f16", 34, "outlier"),
+    ((2, 2, 77, 64), -2, 3, 32, "bf16", 35, "randn"),
+    ((2, 2, 77, 64), -1, 3, 32, "bf16", 36, "randn"),
+    ((1, 2, 33, 64), -2, 8, 32, "f16", 37, "halfgrid"),
+    ((1, 2, 64, 64), -1, 8, 64, "f32", 38, "randn"),
+    ((1, 1, 5, 16), -2, 1, 32, "f16", 39, "randn"),
+    ((1, 2, 40, 32), -2, 12, 0, "f32", 40, "randn"),
+    ((1, 2, 16, 32), -1, 4, 8, "f16", 41, "const"),
+]
+
+
+def gen_fake_quant(root, out_dir):
+    """Stage-A fake quantisation: the reference's quant.py executed as it is (it only needs torch)."""
+    spec = importlib.util.spec_from_file_location("refquant", os.path.join(root, "src", "phasekv", "quant.py"))
+    quant = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(quant)
+    dt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
+    out = {}
+    for i, (shape, axis, bits, gs, dtype, seed, kind) in enumerate(FAKE_QUANT_CASES):
+        x = make_pack_input(shape, seed, kind).float()
+        if dtype == "f32":
+            x = x + torch.randn(shape, generator=torch.Generator().manual_seed(seed + 1000)) * 1e-3
+        x = x.to(dt[dtype])
+        y = quant._grouped_affine_quant_dequant(x, bits, axis, gs)
+        assert y.dtype == x.dtype and y.shape == x.shape
+        out[f"c{i}.x"] = x.float().numpy()
+        out[f"c{i}.y"] = y.float().numpy()
+        out[f"c{i}.args"] = np.array([axis, bits, gs, ["f16", "bf16", "f32"].index(dtype)], dtype=np.int64)
+    # the two public wrappers on a cache-shaped tensor
+    k = make_pack_input((1, 4, 96, 128), 50, "outlier")
+    out["key.x"], out["key.y"] = f16(k), f16(quant.quantize_key(k, 2, 32))
+    out["value.x"], out["value.y"] = f16(k), f16(quant.quantize_value(k, 4, 32))
+    out["n_cases"] = np.array([len(FAKE_QUANT_CASES)], dtype=np.int64)
+    out["bytes"] = np.array([quant.quantized_tier_bytes(1000, 28, 4, 128, 2, 2, 32, 1),
+                             quant.quantized_tier_bytes(77, 2, 2, 64, 4, 16, 0, 3),
+                             quant.fp16_tier_bytes(128, 28, 4, 128, 2),
+                             *quant.kv_group_counts(1000, 128, 32), *quant.kv_group_counts(5, 8, 0)], dtype=np.int64)
+    np.savez_compressed(os.path.join(out_dir, "fake_quant.npz"), **out)
+
+
 def gen_planner(launch_config, out_dir):
     rows = []
     for length in (1, 7, 31, 127, 128, 129, 511, 512, 4096, 8193, 28672, 32768, 131072, 262144):
@@ -238,6 +283,7 @@ def main():
     gen_attention_small(packing, reference, args.out)
     gen_cold(packing, args.out)
     gen_planner(launch_config, args.out)
+    gen_fake_quant(args.reference, args.out)
     for name in sorted(os.listdir(args.out)):
         if name.endswith((".npz", ".json")):
             print(name, os.path.getsize(os.path.join(args.out, name)))

@@ -1,0 +1,42 @@
+"""Stage-A fake quantisation: the C oracle against vectors produced by the reference's quant.py."""
+import numpy as np
+import torch
+
+from tests.conftest import GOLDEN as GOLDEN_DIR
+
+DTYPES = [torch.float16, torch.bfloat16, torch.float32]
+
+
+def _cases():
+    z = np.load(f"{GOLDEN_DIR}/fake_quant.npz")
+    for i in range(int(z["n_cases"][0])):
+        axis, bits, gs, dt = (int(v) for v in z[f"c{i}.args"])
+        yield i, torch.from_numpy(z[f"c{i}.x"]).to(DTYPES[dt]), torch.from_numpy(z[f"c{i}.y"]), axis, bits, gs
+    return z
+
+
+def test_oracle_fake_quant_matches_the_reference_bit_for_bit(oracle):
+    n = 0
+    for i, x, y, axis, bits, gs in _cases():
+        got = oracle.fake_quant(x, bits, axis, gs)
+        assert got.dtype == x.dtype and got.shape == x.shape
+        assert torch.equal(got.float(), y), f"case {i}: {(got.float() != y).sum().item()} elements differ"
+        n += 1
+    assert n >= 10
+    z = np.load(f"{GOLDEN_DIR}/fake_quant.npz")
+    k = torch.from_numpy(z["key.x"].view(np.float16))
+    assert torch.equal(oracle.quantize_key(k, 2, 32), torch.from_numpy(z["key.y"].view(np.float16)))
+    assert torch.equal(oracle.quantize_value(k, 4, 32), torch.from_numpy(z["value.y"].view(np.float16)))
+    assert oracle.fake_quant(k, 16, -1, 32) is k
+
+
+def test_logical_byte_accounting_matches_the_reference():
+    from phasekv_b200 import quant
+    z = np.load(f"{GOLDEN_DIR}/fake_quant.npz")
+    want = [int(v) for v in z["bytes"]]
+    got = [quant.quantized_tier_bytes(1000, 28, 4, 128, 2, 2, 32, 1),
+           quant.quantized_tier_bytes(77, 2, 2, 64, 4, 16, 0, 3),
+           quant.fp16_tier_bytes(128, 28, 4, 128, 2),
+           *quant.kv_group_counts(1000, 128, 32), *quant.kv_group_counts(5, 8, 0)]
+    assert got == want
+    assert quant.quantized_tier_bytes(0, 1, 1, 8, 2, 2) == 0 and quant.kv_group_counts(0, 8, 32) == (0, 0)

@@ -1,0 +1,134 @@
+"""Stage-A operators on the GPU against the reference's vectors and the CPU oracle."""
+import types
+
+import numpy as np
+import pytest
+import torch
+
+from tests.conftest import GOLDEN as GOLDEN_DIR
+from tests.test_stage_a_cpu import _cases
+
+pytestmark = pytest.mark.gpu
+
+
+def test_fake_quant_matches_the_reference_bit_for_bit():
+    from phasekv_b200 import quant
+    for i, x, y, axis, bits, gs in _cases():
+        got = quant._grouped_affine_quant_dequant(x.cuda(), bits, axis, gs)
+        assert got.dtype == x.dtype and got.shape == x.shape
+        assert torch.equal(got.float().cpu(), y), f"case {i}: {(got.float().cpu() != y).sum().item()} elements differ"
+    z = np.load(f"{GOLDEN_DIR}/fake_quant.npz")
+    k = torch.from_numpy(z["key.x"].view(np.float16)).cuda()
+    assert torch.equal(quant.quantize_key(k, 2, 32).cpu(), torch.from_numpy(z["key.y"].view(np.float16)))
+    assert torch.equal(quant.quantize_value(k, 4, 32).cpu(), torch.from_numpy(z["value.y"].view(np.float16)))
+    qk, qv = quant.quantize_kv(k, k, 2, 4)
+    assert torch.equal(qk, quant.quantize_key(k, 2)) and torch.equal(qv, quant.quantize_value(k, 4))
+    assert quant.quantize_key(k, 16) is k
+    with pytest.raises(ValueError):
+        quant.quantize_key(k, 0)
+    with pytest.raises(RuntimeError):
+        quant.quantize_key(k.cpu(), 2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_in_place_slices_equal_the_copy_out_and_back_of_the_reference(oracle, dtype):
+    """t[:, :, a:b, :] = quantize(t[:, :, a:b, :]) for K and V, group sizes that do and do not divide head_dim."""
+    from phasekv_b200 import quant
+    gen = torch.Generator().manual_seed(5)
+    for (b, h, s, hd, a, e, bits, gs) in [(1, 4, 300, 128, 64, 203, 4, 32), (2, 2, 50, 64, 0, 50, 2, 32),
+                                          (1, 2, 40, 24, 3, 37, 3, 16), (1, 2, 64, 128, 10, 11, 8, 0)]:
+        k = torch.randn(b, h, s, hd, generator=gen).to(dtype)
+        v = torch.randn(b, h, s, hd, generator=gen).to(dtype)
+        want_k, want_v = k.clone(), v.clone()
+        want_k[:, :, a:e, :] = oracle.quantize_key(k[:, :, a:e, :], bits, gs)
+        want_v[:, :, a:e, :] = oracle.quantize_value(v[:, :, a:e, :], bits, gs)
+        gk, gv = k.cuda(), v.cuda()
+        quant.fake_quant_(gk, a, e, bits, -2, gs)
+        quant.fake_quant_(gv, a, e, bits, -1, gs)
+        assert torch.equal(gk.cpu(), want_k), (b, h, s, hd, a, e, bits, gs)
+        assert torch.equal(gv.cpu(), want_v), (b, h, s, hd, a, e, bits, gs)
+
+
+def test_signal_topk_and_gather(oracle):
+    from phasekv_b200 import hetero_cache as hc
+    gen = torch.Generator().manual_seed(8)
+    v = torch.randn(2, 4, 200, 128, generator=gen).half()
+    sig = hc.value_norm_signal(v.cuda(), slice(40, 104))
+    want = torch.linalg.vector_norm(v[:, :, 40:104, :].float(), dim=-1)
+    assert sig.shape == (2, 4, 64) and torch.allclose(sig.cpu(), want, rtol=1e-5, atol=1e-6)
+    idx = hc.topk_per_head(sig, 32)
+    want_idx, gap = oracle.value_norm_topk(v[:, :, 40:104, :], 32)
+    assert gap.min() > 1e-4, "seeded data has a near-tie at the selection boundary"
+    assert torch.equal(idx.cpu(), want_idx)
+    assert hc.topk_per_head(sig, 0).shape == (2, 4, 0) and hc.topk_per_head(sig, 1000).shape == (2, 4, 64)
+    # ties go to the lower position
+    flat = torch.zeros(1, 1, 10, device="cuda")
+    assert hc.topk_per_head(flat, 3).tolist() == [[[0, 1, 2]]]
+    g = hc.gather_tokens(v.cuda(), idx + 40)
+    want_g = v.gather(2, (want_idx + 40).unsqueeze(-1).expand(2, 4, 32, 128))
+    assert torch.equal(g.cpu(), want_g)
+
+
+def _fake_cache(layers, b, h, s, hd, seed, dtype=torch.float16):
+    gen = torch.Generator().manual_seed(seed)
+    c = types.SimpleNamespace(key_cache=[], value_cache=[])
+    for _ in range(layers):
+        c.key_cache.append(torch.randn(b, h, s, hd, generator=gen).to(dtype))
+        c.value_cache.append(torch.randn(b, h, s, hd, generator=gen).to(dtype))
+    return c
+
+
+def test_decode_tier_and_prompt_tier_lifecycle_against_a_cpu_restatement(oracle):
+    """Prompt packing, then decode steps that append a token per layer and call maintain(): the dense cache must end
+    up bit-identical to the same procedure restated on the CPU with the oracle's operators
+    (decode_tier.py:25-88, prompt_tier.py:78-118 of the reference)."""
+    from phasekv_b200 import decode_tier, hetero_cache as hc, prompt_tier
+    layers, b, h, hd, prompt = 2, 1, 2, 64, 70
+    cpu = _fake_cache(layers, b, h, prompt, hd, seed=3)
+    gpu = types.SimpleNamespace(key_cache=[t.cuda() for t in cpu.key_cache], value_cache=[t.cuda() for t in cpu.value_cache])
+    keep = [torch.stack([torch.randperm(prompt, generator=torch.Generator().manual_seed(10 + l + 7 * i))[:48]
+                         for i in range(h)]).unsqueeze(0) for l in range(layers)]
+    st_gpu = hc.HeteroTierState(prompt_bits=2, cold_bits=4, group_size=32, recent_window=4)
+    st_cpu = hc.HeteroTierState(prompt_bits=2, cold_bits=4, group_size=32, recent_window=4)
+    prompt_tier.pack_selected(gpu, [k.cuda() for k in keep], st_gpu)
+
+    def cpu_gather(t, idx):
+        return t.gather(2, idx.unsqueeze(-1).expand(*idx.shape, t.shape[-1])).contiguous()
+
+    for l in range(layers):
+        idx = keep[l].sort(dim=-1).values
+        cpu.key_cache[l], cpu.value_cache[l] = cpu_gather(cpu.key_cache[l], idx), cpu_gather(cpu.value_cache[l], idx)
+        cpu.key_cache[l] = oracle.quantize_key(cpu.key_cache[l], 2, 32)
+        cpu.value_cache[l] = oracle.quantize_value(cpu.value_cache[l], 2, 32)
+    st_cpu.prompt_len_phys = 48
+    assert st_gpu.prompt_len_phys == 48
+    gen = torch.Generator().manual_seed(77)
+    for step in range(14):
+        for l in range(layers):
+            nk, nv_ = torch.randn(b, h, 1, hd, generator=gen).half(), torch.randn(b, h, 1, hd, generator=gen).half()
+            cpu.key_cache[l] = torch.cat([cpu.key_cache[l], nk], dim=2)
+            cpu.value_cache[l] = torch.cat([cpu.value_cache[l], nv_], dim=2)
+            gpu.key_cache[l] = torch.cat([gpu.key_cache[l], nk.cuda()], dim=2)
+            gpu.value_cache[l] = torch.cat([gpu.value_cache[l], nv_.cuda()], dim=2)
+        decode_tier.maintain(gpu, step=step, model_config=None, state=st_gpu, decode_keep_ratio=0.5, lazy_g=4)
+        # the same on the CPU
+        seq = cpu.key_cache[0].shape[2]
+        aged = seq - st_cpu.prompt_len_phys - st_cpu.cold_len - st_cpu.recent_window
+        if aged >= 4:
+            base = st_cpu.prompt_len_phys + st_cpu.cold_len
+            keep_b = max(1, int(round(0.5 * aged)))
+            for l in range(layers):
+                sel, gap = oracle.value_norm_topk(cpu.value_cache[l][:, :, base:base + aged, :], keep_b)
+                assert gap.min() > 1e-4
+                idx = torch.cat([torch.arange(base).view(1, 1, -1).expand(b, h, -1), sel + base,
+                                 torch.arange(base + aged, seq).view(1, 1, -1).expand(b, h, -1)], dim=-1)
+                cpu.key_cache[l], cpu.value_cache[l] = cpu_gather(cpu.key_cache[l], idx), cpu_gather(cpu.value_cache[l], idx)
+                cpu.key_cache[l][:, :, base:base + keep_b, :] = oracle.quantize_key(cpu.key_cache[l][:, :, base:base + keep_b, :], 4, 32)
+                cpu.value_cache[l][:, :, base:base + keep_b, :] = oracle.quantize_value(cpu.value_cache[l][:, :, base:base + keep_b, :], 4, 32)
+            st_cpu.cold_len += keep_b
+        assert st_gpu.cold_len == st_cpu.cold_len, step
+    assert st_gpu.cold_len > 0
+    for l in range(layers):
+        assert torch.equal(gpu.key_cache[l].cpu(), cpu.key_cache[l]), l
+        assert torch.equal(gpu.value_cache[l].cpu(), cpu.value_cache[l]), l
+    assert st_gpu.logical_bytes(gpu) == st_cpu.logical_bytes(cpu) > 0
