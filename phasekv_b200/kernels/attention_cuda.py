@@ -93,30 +93,47 @@ def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
     return ws
 
 
-def _run_decode(q: torch.Tensor, segments: Sequence[nv.Segment], keep: list, num_attention_heads: int,
-                num_kv_heads: int, want_out: bool, want_partial: bool):
-    hq, hd = q.shape
-    dev = q.device
+def _prepare_call(segments: Sequence[nv.Segment], hq: int, num_kv_heads: int, hd: int, dev: torch.device):
+    """ctypes segment array and scratch size of one decode call (the plan is a function of lengths only)."""
     n = len(segments)
     arr = (nv.Segment * n)(*segments)
-    L = nv.lib()
-    sms = _device_sm_count(dev)
     need = ctypes.c_size_t(0)
-    nv.check(L.pkv_decode_workspace_bytes(arr, n, hq, num_kv_heads, hd, sms, ctypes.byref(need)))
+    nv.check(nv.lib().pkv_decode_workspace_bytes(arr, n, hq, num_kv_heads, hd, _device_sm_count(dev), ctypes.byref(need)))
+    return arr, n, int(need.value)
+
+
+def _launch_decode(q: torch.Tensor, arr, n: int, need: int, num_kv_heads: int, want_out: bool, want_partial: bool):
+    hq, hd = q.shape
+    dev = q.device
     out = torch.empty((hq, hd), dtype=torch.float16, device=dev) if want_out else None
     m = l = acc = None
     if want_partial:
         m = torch.empty((hq,), dtype=torch.float32, device=dev)
         l = torch.empty((hq,), dtype=torch.float32, device=dev)
         acc = torch.empty((hq, hd), dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    switch = dev.index is not None and torch.cuda.current_device() != dev.index
+    if switch:
+        prev = torch.cuda.current_device()
+        torch.cuda.set_device(dev)
+    try:
         stream = nv.stream_of(dev)
-        ws = _workspace(dev, stream, need.value)
-        nv.check(L.pkv_decode_attention(q.data_ptr(), arr, n, hq, num_kv_heads, hd, 1.0 / (hd ** 0.5), sms,
-                                        ws.data_ptr(), ws.numel(), nv.ptr(out), nv.ptr(m), nv.ptr(l),
-                                        nv.ptr(acc), stream))
-    del keep
+        ws = _workspace(dev, stream, need)
+        nv.check(nv.lib().pkv_decode_attention(q.data_ptr(), arr, n, hq, num_kv_heads, hd, 1.0 / (hd ** 0.5),
+                                               _device_sm_count(dev), ws.data_ptr(), ws.numel(), nv.ptr(out), nv.ptr(m),
+                                               nv.ptr(l), nv.ptr(acc), stream))
+    finally:
+        if switch:
+            torch.cuda.set_device(prev)
     return out, (m, l, acc)
+
+
+def _run_decode(q: torch.Tensor, segments: Sequence[nv.Segment], keep: list, num_attention_heads: int,
+                num_kv_heads: int, want_out: bool, want_partial: bool):
+    hq, hd = q.shape
+    arr, n, need = _prepare_call(segments, hq, num_kv_heads, hd, q.device)
+    res = _launch_decode(q, arr, n, need, num_kv_heads, want_out, want_partial)
+    del keep
+    return res
 
 
 def _check_query(q: torch.Tensor, num_attention_heads: int, hd: int, hkv: int) -> torch.Tensor:
@@ -303,15 +320,41 @@ def fused_phasekv_decode(q: torch.Tensor, tiers, num_attention_heads: int,
     """Batch-1 PhaseKV decode attention for one query token: ``q`` ``[Hq, hd]`` float16 against
     ``tiers`` (what ``PhaseKVCache.layer_tiers`` returns).  The packed tiers are never expanded in
     memory; all segments, however many cold segments have been frozen, go through one launch."""
-    segs, keep, hkv, hd = layer_segments(tiers, num_splits)
+    # A decode loop calls this once per layer and token with tiers that rarely change shape: the segment array
+    # and the scratch size are kept on the tiers object and reused while every segment object, the hot buffers
+    # and the hot length are the same.
+    hot = tiers.hot_k if tiers.hot_len else None
+    tag = (tuple((id(s), s.key.packed.data_ptr()) for s in (tiers.prompt, *tiers.prompt_extensions, *tiers.cold)),
+           None if hot is None else (hot.data_ptr(), tiers.hot_v.data_ptr(), tuple(hot.shape), hot.stride()),
+           num_splits, num_attention_heads)
+    cached = getattr(tiers, "_pkv_call", None)
+    if cached is None or cached[0] != tag:
+        segs, keep, hkv, hd = layer_segments(tiers, num_splits)
+        arr, n, need = _prepare_call(segs, num_attention_heads, hkv, hd, q.device)
+        cached = [tag, arr, n, need, keep, hkv, hd, tiers.hot_len]
+        # reusable only if the hot descriptor points into the caller's own buffers (a strided hot buffer is
+        # described through a dense copy, which the next call must refresh)
+        in_place = hot is None or (keep[-2].data_ptr() == hot.data_ptr() and keep[-1].data_ptr() == tiers.hot_v.data_ptr())
+        try:
+            tiers._pkv_call = cached if in_place else None
+        except AttributeError:
+            pass
+    elif cached[7] != tiers.hot_len:
+        # one more token in the same hot buffers: only the last descriptor's length and the scratch size change
+        arr, n, hkv, hd = cached[1], cached[2], cached[5], cached[6]
+        arr[n - 1].seq_len = tiers.hot_len
+        need = ctypes.c_size_t(0)
+        nv.check(nv.lib().pkv_decode_workspace_bytes(arr, n, num_attention_heads, hkv, hd, _device_sm_count(q.device),
+                                                     ctypes.byref(need)))
+        cached[3], cached[7] = int(need.value), tiers.hot_len
+    arr, n, need, hkv, hd = cached[1], cached[2], cached[3], cached[5], cached[6]
     q = _check_query(q, num_attention_heads, hd, hkv)
     if hd & (hd - 1):
         raise ValueError("head_dim must be a power of two")
     plan_kivi_decode(max(1, tiers.prompt.length), num_attention_heads, hd, _device_sm_count(q.device),
                      num_splits, block_n, num_warps)
-    out, _ = _run_decode(q, segs, keep, num_attention_heads, hkv, True, False)
+    out, _ = _launch_decode(q, arr, n, need, hkv, True, False)
     return out
-
 
 # --------------------------------------------------------------------------- batched serving
 class BatchDecodePlan:
