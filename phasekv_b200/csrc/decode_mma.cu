@@ -25,6 +25,14 @@ constexpr int kKUnroll = PKV_K_UNROLL;
 // B200 at 32768 / 131072 prompt tokens: keys as one bulk copy per row (384 small requests per super-tile)
 // 14.1 / 35.0 us, values only (ten requests per tile) 12.3 / 29.2 us, cp.async for both 11.8 / 28.4 us.
 // The descriptor-less requests are too small to pay off, so both default to cp.async.
+#ifndef PKV_PAIR_SPLIT
+#define PKV_PAIR_SPLIT 1
+#endif
+constexpr bool kPairSplit = PKV_PAIR_SPLIT != 0;  // warp pairs share the tiles of short super-tiles
+#ifndef PKV_SMALL_FIRST
+#define PKV_SMALL_FIRST 1
+#endif
+constexpr bool kSmallFirst = PKV_SMALL_FIRST != 0;  // the partial super-tile of a CTA's range is processed first
 constexpr bool kKeyBulk = PKV_KEY_BULK != 0;
 constexpr bool kValueBulk = PKV_VALUE_BULK != 0;
 constexpr int kAblate = PKV_ABLATE;  // timing experiments only: 1 no score loop, 2 no value loop, 4 no key copies, 8 no value copies  // k-steps of the score loop unrolled together
@@ -243,17 +251,21 @@ struct VSrc {
     }
 };
 
-template <int BITS>
+// NGRP = 2: the whole 64-token tile.  NGRP = 1: only its 32-token group `g_off` (two warps share a tile when a
+// super-tile has few tiles, so that the tail of a CTA's range is spread over all warps).
+template <int BITS, int NGRP = 2>
 __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char* sa, const char* q_lane, float c_qk,
-                                             WarpState& st, const LaneSel<BITS>& ls, int lane, int n_valid) {
+                                             WarpState& st, const LaneSel<BITS>& ls, int lane, int n_valid,
+                                             int g_off = 0) {
     using C = Cfg<BITS>;
+    static_assert(C::NG == 2 && (NGRP == 1 || NGRP == 2), "a tile is two key groups");
     const int g = lane >> 2, t = lane & 3;
     const unsigned sel_lo = 0x5410u, sel_hi = 0x7632u;
 
     // ---------------- scores: S^T tile-by-tile, M = 16 tokens, N = 8 heads, K = channels
-    float sacc[C::NG * 2][4];
+    float sacc[NGRP * 2][4];
 #pragma unroll
-    for (int i = 0; i < C::NG * 2; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
+    for (int i = 0; i < NGRP * 2; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
     float bacc[4] = {0.f, 0.f, 0.f, 0.f};
     const unsigned msel = (g & 1) ? sel_hi : sel_lo;
     // k-step kk contracts channels 16kk + {2t, 2t+1, 2t+8, 2t+9} in this lane (the natural MMA order)
@@ -279,9 +291,9 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
             s23.x = ldp32(s_lane + (16 * kk + 8) * C::MROW);
             s23.y = ldp32(s_lane + (16 * kk + 9) * C::MROW);
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int G = e;
-                const unsigned sel = e ? sel_hi : sel_lo;
+            for (int e = 0; e < NGRP; ++e) {
+                const int G = NGRP == 2 ? e : g_off;
+                const unsigned sel = G ? sel_hi : sel_lo;
                 const unsigned s0p = prmt(s01.x, s01.y, sel), s1p = prmt(s23.x, s23.y, sel);
                 const unsigned b0 = hmul2(qf0, s0p), b1 = hmul2(qf1, s1p);
                 uint4 kc;
@@ -292,14 +304,14 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
                 unsigned ra[4], rb[4];
                 extract4<BITS>(kc.x, kc.y, ls, ra);
                 extract4<BITS>(kc.z, kc.w, ls, rb);
-                mma16816(sacc[2 * G + 0], ra[0], ra[1], rb[0], rb[1], b0, b1);
-                mma16816(sacc[2 * G + 1], ra[2], ra[3], rb[2], rb[3], b0, b1);
+                mma16816(sacc[2 * e + 0], ra[0], ra[1], rb[0], rb[1], b0, b1);
+                mma16816(sacc[2 * e + 1], ra[2], ra[3], rb[2], rb[3], b0, b1);
                 // q*scale does not fit float16 exactly; its rounding error (2^-11 of products that reach
                 // tens on outlier channels) would dominate the score error, so the residual goes through
                 // the tensor core as well (the A operands are already built)
                 const unsigned b0l = hfma2_residual(qf0, s0p, b0), b1l = hfma2_residual(qf1, s1p, b1);
-                mma16816(sacc[2 * G + 0], ra[0], ra[1], rb[0], rb[1], b0l, b1l);
-                mma16816(sacc[2 * G + 1], ra[2], ra[3], rb[2], rb[3], b0l, b1l);
+                mma16816(sacc[2 * e + 0], ra[0], ra[1], rb[0], rb[1], b0l, b1l);
+                mma16816(sacc[2 * e + 1], ra[2], ra[3], rb[2], rb[3], b0l, b1l);
             }
         }
     }
@@ -307,12 +319,13 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
     // ---------------- online softmax in the log2 domain
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int G = 0; G < C::NG; ++G) {
+    for (int e = 0; e < NGRP; ++e) {
+        const int G = NGRP == 2 ? e : g_off;
         const float bias0 = __shfl_sync(0xffffffffu, bacc[0], 4 * G + t);
         const float bias1 = __shfl_sync(0xffffffffu, bacc[1], 4 * G + t);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            float* s = sacc[2 * G + j];
+            float* s = sacc[2 * e + j];
             s[0] = (s[0] * unscale<BITS>(2 * j) + bias0) * c_qk;
             s[1] = (s[1] * unscale<BITS>(2 * j) + bias1) * c_qk;
             s[2] = (s[2] * unscale<BITS>(2 * j + 1) + bias0) * c_qk;
@@ -337,7 +350,7 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
     st.m[1] = m1;
     float ls0 = 0.f, ls1 = 0.f;
 #pragma unroll
-    for (int i = 0; i < C::NG * 2; ++i) {
+    for (int i = 0; i < NGRP * 2; ++i) {
         sacc[i][0] = ex2(sacc[i][0] - m0);
         sacc[i][1] = ex2(sacc[i][1] - m1);
         sacc[i][2] = ex2(sacc[i][2] - m0);
@@ -367,10 +380,11 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
     const char* vs_lane = sa + C::OFF_VS + 64 * t;
     const char* vm_lane = sa + C::OFF_VM + 64 * t + 4 * ((g >> 1) & 1);  // word holding zero[.][g], g < 4
 #pragma unroll
-    for (int G = 0; G < ((kAblate & 2) ? 0 : C::NG); ++G) {
+    for (int e = 0; e < ((kAblate & 2) ? 0 : NGRP); ++e) {
+        const int G = NGRP == 2 ? e : g_off;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            const float* p = sacc[2 * G + j];
+            const float* p = sacc[2 * e + j];
             const unsigned pb0 = movmatrix_trans(pack_half2(p[0], p[1]));  // tokens of rows 2t, 2t+1; head g
             const unsigned pb1 = movmatrix_trans(pack_half2(p[2], p[3]));  // tokens of rows 2t+8, 2t+9
             // tokens of rows 2t, 2t+1, 2t+8, 2t+9 of this score tile: 32G + 8t + {2j, 2j+4, 2j+1, 2j+5}
@@ -652,11 +666,32 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
     const VSrc<BITS> vsrc(sg, kvh, lane);
     const int n_tiles_cta = (int)(tile1 - tile0);
     const int n_super = (n_tiles_cta + C::NSUB - 1) / C::NSUB;
+    // The partial super-tile goes FIRST: nothing can be computed until the first super-tile has landed, and every
+    // SM asks for its first one at the same moment, so a short first fetch shortens the exposed start, while the
+    // full ones behind it are fetched under compute.  (Only when the partial one is a multiple of four tiles, so
+    // that the later super-tiles keep their key scale rows 16-byte aligned.)
+    const int rem_tiles = n_tiles_cta - (n_super - 1) * C::NSUB;  // 1 .. NSUB
+    const bool small_first = kSmallFirst && n_super > 1 && rem_tiles < C::NSUB && (rem_tiles & 3) == 0;
+    auto sp_count = [&](int sp) {
+        return small_first ? (sp == 0 ? rem_tiles : C::NSUB) : min(C::NSUB, n_tiles_cta - sp * C::NSUB);
+    };
+    auto sp_first = [&](int sp) {
+        return small_first ? (sp == 0 ? tile0 : tile0 + rem_tiles + (long long)(sp - 1) * C::NSUB)
+                           : tile0 + (long long)sp * C::NSUB;
+    };
     // Bulk (TMA) copies when every row chunk is 16-byte aligned and sized; cp.async otherwise.
     const bool bulk = (kKeyBulk || kValueBulk) && ksrc.meta16 && (n_tiles_cta & 3) == 0 && !(kAblate & 12);
     const unsigned kbar = smem_base;                        // [2] key buffers
     const unsigned vbar = smem_base + 16 + wid * 16;        // [2] value stages of this warp
     bool timed_out = false;
+    // A super-tile with at most NSUB / 2 tiles (the tail of a CTA's range, or all of a short one) is computed by
+    // warp pairs: warp w takes key group (w & 1) of tile (w >> 1), and the pair shares the value stage of its
+    // even warp, which alone fetches it.  v_tile_of: the tile whose values this warp fetches, or -1.
+    auto split_of = [&](int n) { return kPairSplit && !bulk && 2 * n <= C::NSUB; };
+    auto v_tile_of = [&](int n) {
+        if (split_of(n)) return ((wid & 1) == 0 && wid < 2 * n) ? (wid >> 1) : -1;
+        return wid < n ? wid : -1;
+    };
     if (bulk) {
         if (tid == 0) {
             mbar_init(kbar, NTHREADS);
@@ -672,7 +707,7 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
 
     // super-tile 0 (frozen packed data: may be fetched before the dependency wait)
     if (ksrc.aligned) {
-        const int n_sub = min(C::NSUB, n_tiles_cta);
+        const int n_sub = sp_count(0);
         if (bulk) {
             if (kKeyBulk) ksrc.issue_bulk(tile0, n_sub, kbuf, tid, kbar);
             else ksrc.issue(tile0, n_sub, kbuf, tid);
@@ -683,7 +718,8 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
             cp_async_commit();
         } else {
             ksrc.issue(tile0, n_sub, kbuf, tid);
-            if (wid < n_sub) vsrc.issue(tile0 + wid, vring, valid_of(tile0 + wid));
+            const int vt = v_tile_of(n_sub);
+            if (vt >= 0) vsrc.issue(tile0 + vt, vring, valid_of(tile0 + vt));
             cp_async_commit();
         }
     }
@@ -702,8 +738,8 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
     const LaneSel<BITS> ls(g);
     const float c_qk = a.sm_scale * kLog2e;
     for (int sp = 0; sp < n_super; ++sp) {
-        const int n_sub = min(C::NSUB, n_tiles_cta - sp * C::NSUB);
-        const long long first = tile0 + (long long)sp * C::NSUB;
+        const int n_sub = sp_count(sp);
+        const long long first = sp_first(sp);
         int buf = sp & 1;
         if (ksrc.aligned) {
             if (bulk) {
@@ -719,8 +755,8 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
             }
             __syncthreads();  // super-tile sp has landed for everyone; everyone is done with sp - 1
             if (sp + 1 < n_super) {
-                const long long next = first + C::NSUB;
-                const int n_next = min(C::NSUB, n_tiles_cta - (sp + 1) * C::NSUB);
+                const long long next = sp_first(sp + 1);
+                const int n_next = sp_count(sp + 1);
                 const int nb = (sp + 1) & 1;
                 if (bulk) {
                     fence_proxy_async();  // the buffers were last read through the generic proxy
@@ -733,7 +769,8 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
                     cp_async_commit();
                 } else {
                     ksrc.issue(next, n_next, kbuf + nb * C::KBUF_BYTES, tid);
-                    if (wid < n_next) vsrc.issue(next + wid, vring + nb * C::VSTAGE_BYTES, valid_of(next + wid));
+                    const int vt = v_tile_of(n_next);
+                    if (vt >= 0) vsrc.issue(next + vt, vring + nb * C::VSTAGE_BYTES, valid_of(next + vt));
                     cp_async_commit();
                 }
             }
@@ -741,16 +778,28 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
             // ragged segment: keys through ordinary loads into buffer 0, no overlap with the compute
             buf = 0;
             __syncthreads();  // everyone is done with the previous super-tile
-            if (wid < n_sub) vsrc.issue(first + wid, vring, valid_of(first + wid));
+            const int vt = v_tile_of(n_sub);
+            if (vt >= 0) vsrc.issue(first + vt, vring, valid_of(first + vt));
             cp_async_commit();
             ksrc.load_sync(first, n_sub, reinterpret_cast<char*>(smem_f) + kHeadBytes, tid);
             cp_async_wait<0>();
             __syncthreads();
         }
-        if (wid < n_sub)
-            compute_tile<BITS>(smem_c + kHeadBytes + buf * C::KBUF_BYTES, wid,
-                               smem_c + kHeadBytes + 2 * C::KBUF_BYTES + (wid * NSTAGE + buf) * C::VSTAGE_BYTES,
-                               smem_c + kBarBytes + g * kQRowBytes + 4 * t, c_qk, st, ls, lane, valid_of(first + wid));
+        const char* kb_c = smem_c + kHeadBytes + buf * C::KBUF_BYTES;
+        const char* v0_c = smem_c + kHeadBytes + 2 * C::KBUF_BYTES + buf * C::VSTAGE_BYTES;  // stage `buf` of warp 0's ring
+        const char* q_c = smem_c + kBarBytes + g * kQRowBytes + 4 * t;
+        if (split_of(n_sub)) {
+            const int sub = wid >> 1, half = wid & 1;
+            if (wid < 2 * n_sub) {
+                const int nv = valid_of(first + sub);
+                if (32 * half < nv)  // a group without a single token contributes nothing
+                    compute_tile<BITS, 1>(kb_c, sub, v0_c + (wid & ~1) * (NSTAGE * C::VSTAGE_BYTES), q_c, c_qk, st, ls, lane,
+                                          nv, half);
+            }
+        } else if (wid < n_sub) {
+            compute_tile<BITS>(kb_c, wid, v0_c + wid * (NSTAGE * C::VSTAGE_BYTES), q_c, c_qk, st, ls, lane,
+                               valid_of(first + wid));
+        }
     }
     if (bulk) {
         __syncthreads();  // nobody waits on the barriers any more: release their memory
