@@ -157,6 +157,27 @@ cold_select_pack_kernel(__half* __restrict__ hot_k, __half* __restrict__ hot_v, 
     //    read completely before it is written, so overlapping ranges are safe.
     const int total = (hot_len - aged) * hd;  // elements; rows are dense so this is a flat shift
     const int shift = aged * hd;
+    if ((hd & 7) == 0 && ((reinterpret_cast<uintptr_t>(hk) | reinterpret_cast<uintptr_t>(hv)) & 15u) == 0) {
+        // 16-byte words (row starts are 16-byte aligned when hd is a multiple of 8 and the buffers are)
+        const int words = total >> 3, wshift = shift >> 3;
+        uint4* k4 = reinterpret_cast<uint4*>(hk);
+        uint4* v4 = reinterpret_cast<uint4*>(hv);
+        for (int base = 0; base < words; base += kColdThreads) {
+            const int i = base + tid;
+            uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
+            if (i < words) {
+                a = k4[i + wshift];
+                b = v4[i + wshift];
+            }
+            __syncthreads();
+            if (i < words) {
+                k4[i] = a;
+                v4[i] = b;
+            }
+            __syncthreads();
+        }
+        return;
+    }
     for (int base = 0; base < total; base += kColdThreads) {
         const int i = base + tid;
         __half a = __float2half(0.f), b = a;
