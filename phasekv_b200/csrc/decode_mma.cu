@@ -28,7 +28,10 @@ constexpr int kKUnroll = PKV_K_UNROLL;
 #ifndef PKV_PAIR_SPLIT
 #define PKV_PAIR_SPLIT 1
 #endif
-constexpr bool kPairSplit = PKV_PAIR_SPLIT != 0;  // warp pairs share the tiles of short super-tiles
+// warp pairs share the tiles of short super-tiles.  (Giving EVERY tile to a warp pair, 16 warps of 121 registers,
+// measured 13.4 / 35.2 us at 32768 / 131072 tokens against 12.2 / 28.4: each half pays the per-tile q loads, zero-term
+// MMAs and state rescale again.)
+constexpr bool kPairSplit = PKV_PAIR_SPLIT != 0;
 #ifndef PKV_SMALL_FIRST
 #define PKV_SMALL_FIRST 1
 #endif
@@ -661,7 +664,9 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
     // smem: [mbarriers][q][K buffer 0][K buffer 1][value stages of warp 0][of warp 1]...
     const char* smem_c = reinterpret_cast<const char*>(smem_f);
     const unsigned kbuf = smem_base + kHeadBytes;
-    const unsigned vring = kbuf + 2 * C::KBUF_BYTES + wid * (NSTAGE * C::VSTAGE_BYTES);
+    const unsigned vring = kbuf + 2 * C::KBUF_BYTES + wid * (NSTAGE * C::VSTAGE_BYTES);  // bulk path: one ring per warp
+    // value ring of tile `vt` of a super-tile (the ring of the warp, or of the warp pair, that computes it)
+    auto ring_of = [&](int vt) { return kbuf + 2 * C::KBUF_BYTES + vt * (NSTAGE * C::VSTAGE_BYTES); };
     const KSrc<BITS> ksrc(sg, kvh, tile0);
     const VSrc<BITS> vsrc(sg, kvh, lane);
     const int n_tiles_cta = (int)(tile1 - tile0);
@@ -719,7 +724,7 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
         } else {
             ksrc.issue(tile0, n_sub, kbuf, tid);
             const int vt = v_tile_of(n_sub);
-            if (vt >= 0) vsrc.issue(tile0 + vt, vring, valid_of(tile0 + vt));
+            if (vt >= 0) vsrc.issue(tile0 + vt, ring_of(vt), valid_of(tile0 + vt));
             cp_async_commit();
         }
     }
@@ -770,7 +775,7 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
                 } else {
                     ksrc.issue(next, n_next, kbuf + nb * C::KBUF_BYTES, tid);
                     const int vt = v_tile_of(n_next);
-                    if (vt >= 0) vsrc.issue(next + vt, vring + nb * C::VSTAGE_BYTES, valid_of(next + vt));
+                    if (vt >= 0) vsrc.issue(next + vt, ring_of(vt) + nb * C::VSTAGE_BYTES, valid_of(next + vt));
                     cp_async_commit();
                 }
             }
@@ -779,7 +784,7 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
             buf = 0;
             __syncthreads();  // everyone is done with the previous super-tile
             const int vt = v_tile_of(n_sub);
-            if (vt >= 0) vsrc.issue(first + vt, vring, valid_of(first + vt));
+            if (vt >= 0) vsrc.issue(first + vt, ring_of(vt), valid_of(first + vt));
             cp_async_commit();
             ksrc.load_sync(first, n_sub, reinterpret_cast<char*>(smem_f) + kHeadBytes, tid);
             cp_async_wait<0>();
@@ -793,7 +798,7 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
             if (wid < 2 * n_sub) {
                 const int nv = valid_of(first + sub);
                 if (32 * half < nv)  // a group without a single token contributes nothing
-                    compute_tile<BITS, 1>(kb_c, sub, v0_c + (wid & ~1) * (NSTAGE * C::VSTAGE_BYTES), q_c, c_qk, st, ls, lane,
+                    compute_tile<BITS, 1>(kb_c, sub, v0_c + sub * (NSTAGE * C::VSTAGE_BYTES), q_c, c_qk, st, ls, lane,
                                           nv, half);
             }
         } else if (wid < n_sub) {
