@@ -312,6 +312,7 @@ DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, i
             d.work_begin = plan.fast_work;
             plan.fast_work += d.n_splits;
             plan.fast.push_back(d);
+            plan.fast_index.push_back(i);
         } else {
             if (s.num_splits > 0) {
                 // plan_kivi_decode's manual convention (launch_config.py:58-60 of the reference)
@@ -374,8 +375,9 @@ int run_splitk(const void* q, const pkv_segment_t* segs, int n_segs, int num_q_h
         carved = true;
     }
     const int G = num_q_heads / num_kv_heads;
+    static const bool use_tma = getenv("PKV_NO_TMA") == nullptr;  // tuning aid: keys through cp.async everywhere
 
-    // tensor-core kernel over the aligned KIVI segments
+    // tensor-core kernel over the KIVI and float16 segments it takes
     for (size_t first = 0; first < plan.fast.size(); first += kMaxInlineSegs) {
         const int cnt = (int)std::min<size_t>(kMaxInlineSegs, plan.fast.size() - first);
         mma::MmaArgs a;
@@ -394,7 +396,21 @@ int run_splitk(const void* q, const pkv_segment_t* segs, int n_segs, int num_q_h
             a.segs[i] = plan.fast[first + i];
             a.segs[i].work_begin -= a.work_offset;
             launch_work += a.segs[i].n_splits;
+            a.segs[i].key_tma = 0;
         }
+        // the longest KIVI segments of the launch get tensor maps (a short cold segment is one small super-tile)
+        for (int slot = 0; use_tma && slot < mma::kMaxKeyMaps; ++slot) {
+            int best = -1;
+            for (int i = 0; i < cnt; ++i)
+                if (a.segs[i].kind == PKV_SEG_KIVI && !a.segs[i].key_tma && a.segs[i].S >= 256 &&
+                    (best < 0 || a.segs[i].S > a.segs[best].S))
+                    best = i;
+            if (best < 0) break;
+            a.segs[best].key_tma = mma::make_key_maps(segs[plan.fast_index[first + best]], num_kv_heads, &a.kmaps[slot])
+                                       ? slot + 1 : -1;
+        }
+        for (int i = 0; i < cnt; ++i)
+            if (a.segs[i].key_tma < 0) a.segs[i].key_tma = 0;  // could not be described: cp.async
         static const int dbg2 = getenv("PKV_DEBUG_SKIP") ? atoi(getenv("PKV_DEBUG_SKIP")) : 0;
         if (dbg2 & 2) continue;
         const int rc2 = mma::launch(a, launch_work, num_kv_heads, s);

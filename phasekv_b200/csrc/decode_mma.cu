@@ -15,16 +15,20 @@ constexpr int kKUnroll = PKV_K_UNROLL;
 #ifndef PKV_ABLATE
 #define PKV_ABLATE 0
 #endif
-#ifndef PKV_KEY_BULK
-#define PKV_KEY_BULK 0
+#ifndef PKV_KEY_TMA
+#define PKV_KEY_TMA 1
 #endif
-#ifndef PKV_VALUE_BULK
-#define PKV_VALUE_BULK 0
+// Keys through tiled TMA copies (tensor maps made on the host) where the layout allows; 0 = cp.async everywhere.
+// Untiled bulk copies (cp.async.bulk, one request per key row or per 8 value rows) were measured before this and
+// lost to cp.async: 384 requests of 192 bytes per super-tile 14.1 / 35.0 us at 32768 / 131072 tokens, values only
+// 12.3 / 29.2 us, cp.async for both 11.8 / 28.4 us.
+constexpr bool kKeyTma = PKV_KEY_TMA != 0;
+#ifndef PKV_TMA_MIN_SUPER
+#define PKV_TMA_MIN_SUPER 3
 #endif
-// Bulk (TMA, mbarrier-tracked) copies are implemented for both operands and were measured against cp.async on
-// B200 at 32768 / 131072 prompt tokens: keys as one bulk copy per row (384 small requests per super-tile)
-// 14.1 / 35.0 us, values only (ten requests per tile) 12.3 / 29.2 us, cp.async for both 11.8 / 28.4 us.
-// The descriptor-less requests are too small to pay off, so both default to cp.async.
+// CTAs with fewer super-tiles than this keep cp.async: with one or two super-tiles the barrier set-up costs what
+// the copies save (32768 tokens: 12.35 us with TMA, 12.23 without; 131072 tokens: 27.99 against 28.6)
+constexpr int kTmaMinSuper = PKV_TMA_MIN_SUPER;
 #ifndef PKV_PAIR_SPLIT
 #define PKV_PAIR_SPLIT 1
 #endif
@@ -36,9 +40,7 @@ constexpr bool kPairSplit = PKV_PAIR_SPLIT != 0;
 #define PKV_SMALL_FIRST 1
 #endif
 constexpr bool kSmallFirst = PKV_SMALL_FIRST != 0;  // the partial super-tile of a CTA's range is processed first
-constexpr bool kKeyBulk = PKV_KEY_BULK != 0;
-constexpr bool kValueBulk = PKV_VALUE_BULK != 0;
-constexpr int kAblate = PKV_ABLATE;  // timing experiments only: 1 no score loop, 2 no value loop, 4 no key copies, 8 no value copies  // k-steps of the score loop unrolled together
+constexpr int kAblate = PKV_ABLATE;  // timing experiments only: 1 no score loop, 2 no value loop, 4 no key copies, 8 no value copies
 
 struct WarpState {
     float m[2];        // running max (log2 domain) of heads 2t, 2t+1
@@ -50,7 +52,7 @@ struct WarpState {
 // ---- loads.  Shared-memory layouts are the memory layouts (16-byte cp.async; 4-byte copies throttled
 // the load/store unit, and a copy costs one shared-memory write per 32-byte sector it gathers, so the
 // scattered key rows are fetched in chunks as long as the super-tile allows):
-//   K buffer : codes [channel][KROW bytes], scale [channel][MROW bytes], zero likewise   (CTA-wide)
+//   K buffer : codes as boxes [channel][64 bytes, chunks swizzled], scale [channel][MROW bytes], zero likewise   (CTA-wide)
 //   V stage  : codes [token row, one pad row per 8 tokens][hd*BITS/8 bytes], scale [token][4 f16], zero likewise
 template <int BITS>
 struct KSrc {
@@ -101,7 +103,7 @@ struct KSrc {
                 v.z = __funnelshift_r(w[2], w[3], sh);
                 v.w = __funnelshift_r(w[3], w[4], sh);
             }
-            *reinterpret_cast<uint4*>(kb + row * C::KROW + 16 * ch) = v;
+            *reinterpret_cast<uint4*>(kb + key_chunk_offset(row, ch)) = v;
         }
         const long long moff = tile * (C::NG * 2);
         for (int idx = tid; idx < HD * n_sub; idx += NTHREADS) {
@@ -133,7 +135,7 @@ struct KSrc {
         const uint8_t* src = kp + tile * C::KRB;
         for (int idx = tid; idx < HD * cpr; idx += NTHREADS) {
             const int row = idx / cpr, ch = idx - row * cpr;
-            cp_async16(kb + row * C::KROW + 16 * ch, src + (size_t)row * nbK + 16 * ch);
+            cp_async16(kb + key_chunk_offset(row, ch), src + (size_t)row * nbK + 16 * ch);
         }
         const long long moff = tile * (C::NG * 2);
         if (meta16) {
@@ -154,25 +156,19 @@ struct KSrc {
             }
         }
     }
-    // The same image through bulk copies, one row per thread: 128 code rows, 128 scale rows, 128 zero rows.
-    // Every thread of the CTA arrives on `bar` exactly once (with the bytes it asked for), so the phase
-    // completes when all copies have landed.  Needs 16-byte aligned rows and n_sub % 4 == 0.
-    __device__ __forceinline__ void issue_bulk(long long tile, int n_sub, unsigned kb, int tid, unsigned bar) const {
-        unsigned bytes = 0;
-        for (int idx = tid; idx < 3 * HD; idx += NTHREADS) bytes += idx < HD ? n_sub * C::KRB : n_sub * C::NG * 2;
-        mbar_arrive_expect_tx(bar, bytes);
-        const long long moff = tile * (C::NG * 2);
-        for (int idx = tid; idx < 3 * HD; idx += NTHREADS) {
-            if (idx < HD) {
-                bulk_g2s(kb + idx * C::KROW, kp + (size_t)idx * nbK + tile * C::KRB, n_sub * C::KRB, bar);
-            } else if (idx < 2 * HD) {
-                const int row = idx - HD;
-                bulk_g2s(kb + C::OFF_KS + row * C::MROW, ks + (size_t)row * ngK2 + moff, n_sub * C::NG * 2, bar);
-            } else {
-                const int row = idx - 2 * HD;
-                bulk_g2s(kb + C::OFF_KM + row * C::MROW, km + (size_t)row * ngK2 + moff, n_sub * C::NG * 2, bar);
-            }
-        }
+    // The same image through tiled TMA copies, issued by ONE thread: one 128-row x 64-byte box per 64 bytes of
+    // the super-tile's rows (delivered with the 64-byte swizzle, i.e. in the layout key_chunk_offset describes)
+    // and one box each for the scales and zeros.  Bytes that lie past the end of a row arrive as zeros.  The
+    // first coordinate of every box is a multiple of 16 bytes because super-tiles start on multiples of 4 tiles.
+    __device__ __forceinline__ void issue_tma(const KeyMaps* maps, int kvh, long long tile, int n_sub, unsigned kb,
+                                              unsigned bar) const {
+        const int nbox = (n_sub * C::KRB + C::KBOX - 1) / C::KBOX;
+        mbar_arrive_expect_tx(bar, (unsigned)(nbox * C::KBOX_BYTES + 2 * HD * C::MROW));
+        const int y = kvh * HD;
+        for (int b = 0; b < nbox; ++b)
+            tma_load_2d(kb + b * C::KBOX_BYTES, &maps->codes, (int)(tile * C::KRB) + b * C::KBOX, y, bar);
+        tma_load_2d(kb + C::OFF_KS, &maps->scale, (int)(tile * C::NG), y, bar);
+        tma_load_2d(kb + C::OFF_KM, &maps->mins, (int)(tile * C::NG), y, bar);
     }
 
     __device__ __forceinline__ void issue(long long tile, int n_sub, unsigned kb, int tid) const {
@@ -201,21 +197,6 @@ struct VSrc {
         d_vc = (lt + lt / 8) * (C::VWPT * 4) + 16 * (lane % CPT);
         vs = reinterpret_cast<const char*>(sg.vs + (size_t)kvh * sg.S * 4) + 16 * lane;
         vm = reinterpret_cast<const char*>(sg.vm + (size_t)kvh * sg.S * 4) + 16 * lane;
-    }
-
-    // A full tile through bulk copies: lanes 0..7 one block of 8 token rows each (the pad row follows each
-    // block), lane 8 the scales, lane 9 the zeros; every lane arrives on `bar` once.
-    __device__ __forceinline__ void issue_bulk(long long tile, unsigned sa, unsigned bar) const {
-        constexpr unsigned kBlock = 8 * C::VWPT * 4;
-        const unsigned bytes = lane < 8 ? kBlock : lane < 10 ? (unsigned)(C::T * 8) : 0u;
-        mbar_arrive_expect_tx(bar, bytes);
-        if (lane < 8) {
-            bulk_g2s(sa + 9 * lane * (C::VWPT * 4), vc - 16 * lane + tile * (C::T * C::VWPT * 4) + kBlock * lane, kBlock, bar);
-        } else if (lane == 8) {
-            bulk_g2s(sa + C::OFF_VS, vs - 16 * lane + tile * (C::T * 8), C::T * 8, bar);
-        } else if (lane == 9) {
-            bulk_g2s(sa + C::OFF_VM, vm - 16 * lane + tile * (C::T * 8), C::T * 8, bar);
-        }
     }
 
     // values of one tile into the stage at `sa`; one warp.  Rows of tokens >= n_valid are zero-filled
@@ -272,7 +253,15 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
     float bacc[4] = {0.f, 0.f, 0.f, 0.f};
     const unsigned msel = (g & 1) ? sel_hi : sel_lo;
     // k-step kk contracts channels 16kk + {2t, 2t+1, 2t+8, 2t+9} in this lane (the natural MMA order)
-    const char* k_lane = kb + 2 * t * C::KROW + sub * C::KRB + 4 * ls.word;
+    // key codes of this lane: channel rows 2t (+1, +8, +9) + 16kk; the lane's word of group G of tile `sub` lies in
+    // 16-byte chunk ck of the super-tile row, stored at chunk (ck & 3) ^ ((row >> 1) & 3) = (ck & 3) ^ t of box ck >> 2
+    const char* k_lane[2];
+#pragma unroll
+    for (int G = 0; G < 2; ++G) {
+        const int in_tile = 4 * G * BITS + 4 * (int)ls.word;  // byte offset inside the tile's KRB bytes of a row
+        const int ck = sub * (C::KRB / 16) + (in_tile >> 4);
+        k_lane[G] = kb + (ck >> 2) * C::KBOX_BYTES + 2 * t * C::KBOX + ((((ck & 3) ^ t) & 3) << 4) + (in_tile & 15);
+    }
     const char* s_lane = kb + C::OFF_KS + 2 * t * C::MROW + 4 * sub;
     const char* m_lane = kb + C::OFF_KM + 2 * t * C::MROW + 4 * sub;
     // partially unrolled: the fully unrolled loop made the kernel instruction-fetch bound on short contexts
@@ -300,10 +289,11 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
                 const unsigned s0p = prmt(s01.x, s01.y, sel), s1p = prmt(s23.x, s23.y, sel);
                 const unsigned b0 = hmul2(qf0, s0p), b1 = hmul2(qf1, s1p);
                 uint4 kc;
-                kc.x = ldp32(k_lane + (16 * kk + 0) * C::KROW + 4 * G * BITS);
-                kc.y = ldp32(k_lane + (16 * kk + 1) * C::KROW + 4 * G * BITS);
-                kc.z = ldp32(k_lane + (16 * kk + 8) * C::KROW + 4 * G * BITS);
-                kc.w = ldp32(k_lane + (16 * kk + 9) * C::KROW + 4 * G * BITS);
+                const char* kl = NGRP == 2 ? k_lane[e] : (g_off ? k_lane[1] : k_lane[0]);
+                kc.x = ldp32(kl + (16 * kk + 0) * C::KBOX);
+                kc.y = ldp32(kl + (16 * kk + 1) * C::KBOX);
+                kc.z = ldp32(kl + (16 * kk + 8) * C::KBOX);
+                kc.w = ldp32(kl + (16 * kk + 9) * C::KBOX);
                 unsigned ra[4], rb[4];
                 extract4<BITS>(kc.x, kc.y, ls, ra);
                 extract4<BITS>(kc.z, kc.w, ls, rb);
@@ -648,8 +638,8 @@ __device__ __forceinline__ void run_cta_fp16(const CtaCtx& a, const SegDev& sg, 
 }
 
 template <int BITS>
-__device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long long tile0, long long tile1, int kvh,
-                                        float* smem_f) {
+__device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const KeyMaps* kmaps, long long tile0,
+                                        long long tile1, int kvh, float* smem_f) {
     using C = Cfg<BITS>;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -664,7 +654,6 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
     // smem: [mbarriers][q][K buffer 0][K buffer 1][value stages of warp 0][of warp 1]...
     const char* smem_c = reinterpret_cast<const char*>(smem_f);
     const unsigned kbuf = smem_base + kHeadBytes;
-    const unsigned vring = kbuf + 2 * C::KBUF_BYTES + wid * (NSTAGE * C::VSTAGE_BYTES);  // bulk path: one ring per warp
     // value ring of tile `vt` of a super-tile (the ring of the warp, or of the warp pair, that computes it)
     auto ring_of = [&](int vt) { return kbuf + 2 * C::KBUF_BYTES + vt * (NSTAGE * C::VSTAGE_BYTES); };
     const KSrc<BITS> ksrc(sg, kvh, tile0);
@@ -684,50 +673,43 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
         return small_first ? (sp == 0 ? tile0 : tile0 + rem_tiles + (long long)(sp - 1) * C::NSUB)
                            : tile0 + (long long)sp * C::NSUB;
     };
-    // Bulk (TMA) copies when every row chunk is 16-byte aligned and sized; cp.async otherwise.
-    const bool bulk = (kKeyBulk || kValueBulk) && ksrc.meta16 && (n_tiles_cta & 3) == 0 && !(kAblate & 12);
-    const unsigned kbar = smem_base;                        // [2] key buffers
-    const unsigned vbar = smem_base + 16 + wid * 16;        // [2] value stages of this warp
+    // Keys come through tiled TMA copies when the host could describe the segment with tensor maps (rows and scale
+    // rows a multiple of 16 bytes apart) and this CTA's super-tiles start on multiples of four tiles; otherwise
+    // every thread issues 16-byte cp.async copies into the same shared-memory image.
+    const bool ktma = kKeyTma && kmaps != nullptr && ksrc.aligned && (tile0 & 3) == 0 && n_super >= kTmaMinSuper &&
+                      !(kAblate & 4);
+    const unsigned kbar = smem_base;  // [2] mbarriers, one per key buffer
     bool timed_out = false;
     // A super-tile with at most NSUB / 2 tiles (the tail of a CTA's range, or all of a short one) is computed by
     // warp pairs: warp w takes key group (w & 1) of tile (w >> 1), and the pair shares the value stage of its
     // even warp, which alone fetches it.  v_tile_of: the tile whose values this warp fetches, or -1.
-    auto split_of = [&](int n) { return kPairSplit && !bulk && 2 * n <= C::NSUB; };
+    auto split_of = [&](int n) { return kPairSplit && 2 * n <= C::NSUB; };
     auto v_tile_of = [&](int n) {
         if (split_of(n)) return ((wid & 1) == 0 && wid < 2 * n) ? (wid >> 1) : -1;
         return wid < n ? wid : -1;
     };
-    if (bulk) {
-        if (tid == 0) {
-            mbar_init(kbar, NTHREADS);
-            mbar_init(kbar + 8, NTHREADS);
-        }
-        if (lane == 0) {
-            mbar_init(vbar, 32);
-            mbar_init(vbar + 8, 32);
-        }
+    if (ktma && tid == 0) {  // the same thread issues the first copies; everyone else meets the barriers after
+        mbar_init(kbar, 1);  // the __syncthreads() below
+        mbar_init(kbar + 8, 1);
         fence_mbar_init();
-        __syncthreads();
     }
+    auto issue_keys = [&](long long tile, int n, int buf) {
+        if (ktma) {
+            if (tid == 0) ksrc.issue_tma(kmaps, kvh, tile, n, kbuf + buf * C::KBUF_BYTES, kbar + 8 * buf);
+        } else {
+            ksrc.issue(tile, n, kbuf + buf * C::KBUF_BYTES, tid);
+        }
+    };
 
     // super-tile 0 (frozen packed data: may be fetched before the dependency wait)
     if (ksrc.aligned) {
         const int n_sub = sp_count(0);
-        if (bulk) {
-            if (kKeyBulk) ksrc.issue_bulk(tile0, n_sub, kbuf, tid, kbar);
-            else ksrc.issue(tile0, n_sub, kbuf, tid);
-            if (wid < n_sub) {
-                if (kValueBulk) vsrc.issue_bulk(tile0 + wid, vring, vbar);
-                else vsrc.issue(tile0 + wid, vring, valid_of(tile0 + wid));
-            }
-            cp_async_commit();
-        } else {
-            ksrc.issue(tile0, n_sub, kbuf, tid);
-            const int vt = v_tile_of(n_sub);
-            if (vt >= 0) vsrc.issue(tile0 + vt, ring_of(vt), valid_of(tile0 + vt));
-            cp_async_commit();
-        }
+        issue_keys(tile0, n_sub, 0);
+        const int vt = v_tile_of(n_sub);
+        if (vt >= 0) vsrc.issue(tile0 + vt, ring_of(vt), valid_of(tile0 + vt));
+        cp_async_commit();
     }
+    if (ktma) __syncthreads();  // the mbarriers are initialised for every thread that will wait on them
     cudaGridDependencySynchronize();  // everything below may depend on the previous kernel of the stream
     // q of the GQA group, staged once per CTA behind the first copies (rows padded against bank
     // conflicts; zero rows for heads >= G)
@@ -747,37 +729,19 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
         const long long first = sp_first(sp);
         int buf = sp & 1;
         if (ksrc.aligned) {
-            if (bulk) {
-                const unsigned parity = (sp >> 1) & 1;
-                if (kKeyBulk) {
-                    if (!mbar_wait(kbar + 8 * buf, parity)) timed_out = true;
-                } else {
-                    cp_async_wait<0>();
-                }
-                if (kValueBulk && wid < n_sub && !mbar_wait(vbar + 8 * buf, parity)) timed_out = true;
-            } else {
-                cp_async_wait<0>();
-            }
+            cp_async_wait<0>();
+            // bounded: a copy that never completes poisons this CTA's partial instead of hanging the GPU
+            if (ktma && !mbar_wait(kbar + 8 * buf, (sp >> 1) & 1)) timed_out = true;  // (one polling lane per warp measured slower)
             __syncthreads();  // super-tile sp has landed for everyone; everyone is done with sp - 1
             if (sp + 1 < n_super) {
                 const long long next = sp_first(sp + 1);
                 const int n_next = sp_count(sp + 1);
                 const int nb = (sp + 1) & 1;
-                if (bulk) {
-                    fence_proxy_async();  // the buffers were last read through the generic proxy
-                    if (kKeyBulk) ksrc.issue_bulk(next, n_next, kbuf + nb * C::KBUF_BYTES, tid, kbar + 8 * nb);
-                    else ksrc.issue(next, n_next, kbuf + nb * C::KBUF_BYTES, tid);
-                    if (wid < n_next) {
-                        if (kValueBulk) vsrc.issue_bulk(next + wid, vring + nb * C::VSTAGE_BYTES, vbar + 8 * nb);
-                        else vsrc.issue(next + wid, vring + nb * C::VSTAGE_BYTES, valid_of(next + wid));
-                    }
-                    cp_async_commit();
-                } else {
-                    ksrc.issue(next, n_next, kbuf + nb * C::KBUF_BYTES, tid);
-                    const int vt = v_tile_of(n_next);
-                    if (vt >= 0) vsrc.issue(next + vt, ring_of(vt) + nb * C::VSTAGE_BYTES, valid_of(next + vt));
-                    cp_async_commit();
-                }
+                if (ktma && tid == 0) fence_proxy_async();  // the buffer was last read through the generic proxy
+                issue_keys(next, n_next, nb);
+                const int vt = v_tile_of(n_next);
+                if (vt >= 0) vsrc.issue(next + vt, ring_of(vt) + nb * C::VSTAGE_BYTES, valid_of(next + vt));
+                cp_async_commit();
             }
         } else {
             // ragged segment: keys through ordinary loads into buffer 0, no overlap with the compute
@@ -806,15 +770,11 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long 
                                valid_of(first + wid));
         }
     }
-    if (bulk) {
+    if (ktma) {
         __syncthreads();  // nobody waits on the barriers any more: release their memory
         if (tid == 0) {
             mbar_inval(kbar);
             mbar_inval(kbar + 8);
-        }
-        if (lane == 0) {
-            mbar_inval(vbar);
-            mbar_inval(vbar + 8);
         }
         // a wait that gave up means the result of this CTA cannot be trusted: poison it rather than hang
         if (timed_out) st.m[0] = st.m[1] = __int_as_float(0x7fc00000);
@@ -828,35 +788,35 @@ __device__ __forceinline__ long long tiles_in(const SegDev& sg) {
 }
 
 // Tiles [tile0, tile0 + n_tiles) of segment `sg` for KV head `kvh`, one partial written to row a.widx.
-__device__ __forceinline__ void run_item(const CtaCtx& a, const SegDev& sg, long long tile0, long long n_tiles,
-                                         int kvh, float* smem_f) {
+__device__ __forceinline__ void run_item(const CtaCtx& a, const SegDev& sg, const KeyMaps* kmaps, long long tile0,
+                                         long long n_tiles, int kvh, float* smem_f) {
     const long long tile1 = min(tiles_in(sg), tile0 + n_tiles);
     if (sg.kind == PKV_SEG_FP16) run_cta_fp16(a, sg, tile0, tile1, kvh, smem_f);
-    else if (sg.kbits == 2) run_cta<2>(a, sg, tile0, tile1, kvh, smem_f);
-    else if (sg.kbits == 4) run_cta<4>(a, sg, tile0, tile1, kvh, smem_f);
-    else run_cta<8>(a, sg, tile0, tile1, kvh, smem_f);
+    else if (sg.kbits == 2) run_cta<2>(a, sg, kmaps, tile0, tile1, kvh, smem_f);
+    else if (sg.kbits == 4) run_cta<4>(a, sg, kmaps, tile0, tile1, kvh, smem_f);
+    else run_cta<8>(a, sg, kmaps, tile0, tile1, kvh, smem_f);
 }
 
 // One sequence, segment descriptors inside the parameter block; work item w of a segment covers
 // split_len tiles.
 __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_mma_kernel(const __grid_constant__ MmaArgs a) {
-    extern __shared__ __align__(16) float smem_f[];
+    extern __shared__ __align__(1024) float smem_f[];
     const int w = blockIdx.x, kvh = blockIdx.y;
     int si = 0;
     while (si + 1 < a.n_segs && w >= a.segs[si + 1].work_begin) ++si;
     const SegDev& sg = a.segs[si];
     const int split = w - sg.work_begin;
     const CtaCtx ctx = {a.q, a.pm, a.pl, a.pacc, (size_t)a.work_offset + blockIdx.x, a.Hq, a.G, a.sm_scale};
-    run_item(ctx, sg, (long long)split * sg.split_len, sg.split_len, kvh, smem_f);
+    run_item(ctx, sg, sg.key_tma ? &a.kmaps[sg.key_tma - 1] : nullptr, (long long)split * sg.split_len, sg.split_len, kvh, smem_f);
 }
 
 // Many sequences, descriptors and an explicit work list in device memory (see BatchTable).
 __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_mma_batched_kernel(const __grid_constant__ BatchArgs a) {
-    extern __shared__ __align__(16) float smem_f[];
+    extern __shared__ __align__(1024) float smem_f[];
     const BatchWork wk = a.work[blockIdx.x];
     const SegDev& sg = a.segs[wk.seg];
     const CtaCtx ctx = {a.q + (size_t)wk.seq * a.Hq * HD, a.pm, a.pl, a.pacc, (size_t)wk.part, a.Hq, a.G, a.sm_scale};
-    run_item(ctx, sg, wk.tile_begin, wk.n_tiles, blockIdx.y, smem_f);
+    run_item(ctx, sg, nullptr, wk.tile_begin, wk.n_tiles, blockIdx.y, smem_f);
 }
 
 }  // namespace

@@ -17,6 +17,8 @@
 // the end into ONE un-normalised partial (m, l, acc) per CTA.
 #pragma once
 
+#include <cuda.h>  // CUtensorMap (types only: the encoder is fetched from the driver at run time)
+
 #include "common.cuh"
 #include "decode_plan.h"
 
@@ -53,10 +55,16 @@ struct Cfg {
                                                       : (BITS == 2 ? NWARPS : BITS == 4 ? 4 : 2);
     static constexpr int NSUB = NSUB_WANT < NWARPS ? NSUB_WANT : NWARPS;
     static constexpr int KRB = T * BITS / 8;        // key code bytes per channel row of a tile (16/32/64)
-    static constexpr int KROW = NSUB * KRB + 16;    // key code row of a super-tile; the 16 pad bytes stagger banks
+    // Key codes of a super-tile sit in shared memory as boxes of 128 channel rows x 64 bytes (the shape a tiled
+    // TMA copy delivers), with the four 16-byte chunks of a row permuted by (row >> 1) & 3 (the 64-byte swizzle
+    // pattern): the four channel rows a lane reads per step then fall into different banks without padding.
+    static constexpr int KBOX = 64;                 // bytes of a key code row inside a box
+    static constexpr int KBOX_BYTES = HD * KBOX;    // 8 KB
+    static constexpr int NBOX = NSUB * KRB / KBOX;  // boxes per super-tile
+    static_assert(NSUB * KRB % KBOX == 0, "a super-tile is a whole number of boxes");
     static constexpr int MROW = (NSUB * NG * 2 + 15) / 16 * 16;  // key scale (or zero) row of a super-tile: f16 per group, 16-byte rows
-    static constexpr int KBUF_BYTES = HD * (KROW + 2 * MROW);
-    static constexpr int OFF_KS = HD * KROW;        // byte offsets inside a K buffer
+    static constexpr int KBUF_BYTES = NBOX * KBOX_BYTES + 2 * HD * MROW;
+    static constexpr int OFF_KS = NBOX * KBOX_BYTES;  // byte offsets inside a K buffer
     static constexpr int OFF_KM = OFF_KS + HD * MROW;
     static constexpr int VWPT = HD * BITS / 32;     // value code words per token (8/16/32)
     static constexpr int VROWS = T + T / 8;         // one pad row per 8 tokens spreads the four token
@@ -70,9 +78,29 @@ struct Cfg {
 constexpr int kMergeBytes = NWARPS * (8 * HD + 16) * 4;  // per-warp O[8][128] + m[8] + l[8]
 static_assert(kMergeBytes + kHeadBytes <= kSmemBytes && Cfg<2>::SMEM_BYTES <= kSmemBytes &&
               Cfg<4>::SMEM_BYTES <= kSmemBytes && Cfg<8>::SMEM_BYTES <= kSmemBytes, "shared memory budget");
-static_assert(Cfg<2>::NG == 2 && Cfg<2>::KBUF_BYTES % 16 == 0 && Cfg<2>::VSTAGE_BYTES % 16 == 0, "tile geometry");
+static_assert(Cfg<2>::NG == 2 && Cfg<2>::VSTAGE_BYTES % 16 == 0, "tile geometry");
+static_assert(kHeadBytes % 512 == 0 && Cfg<2>::KBUF_BYTES % 512 == 0 && Cfg<4>::KBUF_BYTES % 512 == 0 &&
+              Cfg<8>::KBUF_BYTES % 512 == 0, "key boxes start on 512 bytes (the swizzle period)");
+
+// Byte offset of 16-byte chunk `chunk` (counted along the super-tile's row) of channel row `row` inside the
+// key code area of a K buffer.
+__host__ __device__ constexpr int key_chunk_offset(int row, int chunk) {
+    return (chunk >> 2) * (HD * 64) + row * 64 + ((((chunk & 3) ^ (row >> 1)) & 3) << 4);
+}
 
 inline int tile_tokens(int) { return 64; }
+
+// Tensor maps of one KIVI segment's keys: codes as uint8 [Hkv*128 rows][row bytes] with 64-byte x 128-row boxes
+// and the 64-byte swizzle; scales and zeros as float16 [Hkv*128 rows][groups] with boxes of one super-tile's
+// groups x 128 rows.
+struct KeyMaps {
+    CUtensorMap codes;
+    CUtensorMap scale;
+    CUtensorMap mins;
+};
+
+// Segments of a launch whose keys travel through TMA (the longest ones; every map adds 384 bytes of parameters).
+constexpr int kMaxKeyMaps = 4;
 
 struct MmaArgs {
     const __half* q;
@@ -84,6 +112,7 @@ struct MmaArgs {
     int n_segs;
     int work_offset;
     SegDev segs[kMaxInlineSegs];  // split_len counts TILES here
+    KeyMaps kmaps[kMaxKeyMaps];  // segs[i].key_tma - 1 indexes this array (0 = no map)
 };
 
 // What a CTA needs besides its segment: the query rows of its sequence and where its partial goes.
@@ -126,6 +155,12 @@ __device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void tma_load_2d(unsigned smem_dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+        ::"r"(smem_dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
 }
 __device__ __forceinline__ unsigned prmt(unsigned a, unsigned b, unsigned sel) {
     unsigned r;
@@ -173,8 +208,8 @@ __device__ __forceinline__ void cp_async16_zfill(unsigned smem_addr, const void*
 __device__ __forceinline__ void cp_async8_zfill(unsigned smem_addr, const void* g, unsigned src_bytes) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(smem_addr), "l"(g), "r"(src_bytes));
 }
-// ---- bulk (TMA) copies global -> shared, completion counted in bytes on an mbarrier.  They are issued by
-// one thread per copy and bypass the load/store unit, which ordinary cp.async copies at HBM rate saturate.
+// ---- TMA copies global -> shared complete on an mbarrier that counts bytes.  One thread issues them and they
+// bypass the load/store unit, which 16-byte cp.async copies at HBM rate keep busy.
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
@@ -200,10 +235,6 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
         if (ok) return true;
     }
     return false;
-}
-__device__ __forceinline__ void bulk_g2s(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
@@ -297,5 +328,9 @@ long long tiles_of(const pkv_segment_t& s);
 int launch(const MmaArgs& a, int work, int Hkv, cudaStream_t stream);
 // Launch over a device-resident work list of `work` items per KV head.
 int launch_batched(const BatchArgs& a, int work, int Hkv, cudaStream_t stream);
+// Tensor maps for the keys of `s` (a KIVI segment the tensor-core kernel takes).  False when the layout cannot be
+// described (rows or scale rows not a multiple of 16 bytes apart) or the driver refuses: the kernel then
+// fetches the keys with cp.async.  Maps are cached per thread by pointers and sizes.
+bool make_key_maps(const pkv_segment_t& s, int Hkv, KeyMaps* out);
 }  // namespace mma
 }  // namespace pkv

@@ -27,6 +27,7 @@ struct SegDev {
     int kind, kbits, vbits, kgs, vgs;
     int work_begin;  // index of the segment's first work item
     int n_splits;    // work items of this segment
+    int key_tma;     // 1 + index of this segment's key tensor maps in the launch parameters, 0 = none
 };
 
 // Segments are routed to one of two kernels: the tensor-core kernel (`fast`, split_len counts
@@ -34,6 +35,7 @@ struct SegDev {
 // numbered fast first, generic after; work_begin is relative to the start of each list.
 struct DecodePlan {
     std::vector<SegDev> fast;
+    std::vector<int> fast_index;  // position of each `fast` entry in the caller's segment array
     std::vector<SegDev> generic;
     int fast_work = 0;
     int generic_work = 0;
