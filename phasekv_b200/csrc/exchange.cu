@@ -61,6 +61,22 @@ __device__ __forceinline__ uint2 ld_word(const uint2* p) {
     asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
     return v;
 }
+// Poll one element until it carries epoch e; false when the poll budget is spent.  (The words of a rank are
+// polled one after the other, rank after rank: three dependent round trips per rank.  Issuing the loads of all
+// ranks together would shorten the wait at eight ranks; that variant has not been verified on several GPUs.)
+__device__ __forceinline__ bool wait_word(const uint2* p, uint32_t e, unsigned limit, float& v) {
+    unsigned polls = 0;
+    for (;;) {
+        const uint2 w = ld_word(p);
+        if (w.y == e) {
+            v = __uint_as_float(w.x);
+            return true;
+        }
+        if (++polls >= limit) return false;
+        if (polls > 16) __nanosleep(polls < 256 ? 32 : 256);
+    }
+}
+
 __global__ void __launch_bounds__(kMergeThreads)
 merge_exchange_kernel(const float* __restrict__ pm, const float* __restrict__ pl, const float* __restrict__ pacc,
                       int n_parts, const __grid_constant__ ExchangeArgs x, __half* __restrict__ out) {
@@ -89,51 +105,17 @@ merge_exchange_kernel(const float* __restrict__ pm, const float* __restrict__ pl
     //    separately, as the split merge does, so that both give the same bits)
     const uint2* in = reinterpret_cast<const uint2*>(local) + (par * x.world * Hq + h) * (size_t)(hd + 2);
     const size_t rank_stride = (size_t)Hq * (hd + 2);
-    // The three words a thread needs from every rank are polled together: one round of independent loads per
-    // pass (four ranks at a time), not one round trip per word.
-    float mr[kMaxWorld], lr[kMaxWorld], ar[kMaxWorld];
-    const bool has_dim = tid < hd;
-    unsigned pending = x.world >= 32 ? 0xffffffffu : ((1u << x.world) - 1u);
-    unsigned polls = 0;
     bool ok = true;
-    while (pending) {
-#pragma unroll 1
-        for (int r0 = 0; r0 < x.world; r0 += 4) {
-            uint2 wm[4], wl[4], wa[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int r = r0 + k;
-                wm[k] = wl[k] = wa[k] = make_uint2(0u, e);
-                if (r < x.world && (pending >> r & 1u)) {
-                    const uint2* src = in + r * rank_stride;
-                    wm[k] = ld_word(src + hd);
-                    wl[k] = ld_word(src + hd + 1);
-                    if (has_dim) wa[k] = ld_word(src + tid);
-                }
-            }
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int r = r0 + k;
-                if (r < x.world && (pending >> r & 1u) && wm[k].y == e && wl[k].y == e && wa[k].y == e) {
-                    mr[r] = __uint_as_float(wm[k].x);
-                    lr[r] = __uint_as_float(wl[k].x);
-                    ar[r] = __uint_as_float(wa[k].x);
-                    pending &= ~(1u << r);
-                }
-            }
-        }
-        if (pending) {
-            if (++polls >= x.spin_limit) {
-                ok = false;
-                break;
-            }
-            if (polls > 16) __nanosleep(polls < 256 ? 32 : 256);
-        }
-    }
+    float mr[kMaxWorld], lr[kMaxWorld], ar[kMaxWorld];
     float mx = -INFINITY;
-    if (ok) {
 #pragma unroll 1
-        for (int r = 0; r < x.world; ++r) mx = fmaxf(mx, mr[r]);
+    for (int r = 0; r < x.world; ++r) {
+        const uint2* src = in + r * rank_stride;
+        ar[r] = 0.f;
+        ok = ok && wait_word(src + hd, e, x.spin_limit, mr[r]) && wait_word(src + hd + 1, e, x.spin_limit, lr[r]);
+        if (ok && tid < hd) ok = wait_word(src + tid, e, x.spin_limit, ar[r]);
+        if (!ok) break;
+        mx = fmaxf(mx, mr[r]);
     }
     if (ok) {
         float acc = 0.f, den = 0.f;
