@@ -3,10 +3,10 @@
 
 Same surface as the part of the reference's ``src/phasekv/hetero_cache.py`` that the decode tier needs:
 ``cache_num_layers`` (:36), ``cache_seq_len`` (:40), ``value_norm_signal`` (:98), ``topk_per_head`` (:157),
-``evict_per_head`` (:120) and ``HeteroTierState`` (:175).  The selection signal, the top-k and the per-head
-compaction are one launch each instead of torch pipelines.  Attention-score based prompt selection
-(``observation_votes``, ``pool_scores``) needs the eager attention matrices of the evaluation pipeline and is
-not part of this package.
+``evict_per_head`` (:120), ``HeteroTierState`` (:175), and the attention-vote helpers of the prompt selection
+(``aggregate_to_kv_heads`` :56, ``observation_votes`` :67, ``pool_scores`` :80).  The selection signal, the top-k
+of a lazy batch and the per-head compaction are one launch each instead of torch pipelines; the vote helpers
+operate on the eager attention matrices of the evaluation pipeline with tensor operations.
 """
 from __future__ import annotations
 
@@ -19,6 +19,10 @@ from . import _native as nv
 from . import quant
 
 
+#: rows longer than this exceed the shared memory of the rank-counting top-k kernel
+_TOPK_KERNEL_MAX = 4096
+
+
 def cache_num_layers(cache) -> int:
     return len(cache.key_cache)
 
@@ -27,6 +31,46 @@ def cache_seq_len(cache, layer_idx: int = 0) -> int:
     if len(cache.key_cache) <= layer_idx or cache.key_cache[layer_idx] is None:
         return 0
     return cache.key_cache[layer_idx].shape[-2]
+
+
+def num_kv_heads_of(model_config) -> int:
+    return getattr(model_config, "num_key_value_heads", getattr(model_config, "num_attention_heads"))
+
+
+# The three functions below turn the attention matrices of an eager prefill into per-head importance scores.
+# They are host-side glue of the evaluation pipeline (the matrices are [B, Hq, q, kv] float tensors a model
+# returned) and are written with tensor operations that run wherever those matrices live.
+def aggregate_to_kv_heads(scores: torch.Tensor, num_kv_heads: int) -> torch.Tensor:
+    """Sum scores given per query head ``[B, Hq, ...]`` over each GQA group -> ``[B, Hkv, ...]``."""
+    b, hq = scores.shape[0], scores.shape[1]
+    if hq == num_kv_heads:
+        return scores
+    if hq % num_kv_heads != 0:
+        raise ValueError(f"{hq} query heads are not a multiple of {num_kv_heads} KV heads")
+    return scores.view(b, num_kv_heads, hq // num_kv_heads, *scores.shape[2:]).sum(dim=2)
+
+
+def observation_votes(attn_layer: torch.Tensor, num_kv_heads: int, obs_window: int) -> torch.Tensor:
+    """Votes of the last ``obs_window`` query rows of a prefill attention matrix for every key position, summed
+    over each GQA group: ``[B, Hkv, kv_len]`` float32."""
+    w = max(1, min(obs_window, attn_layer.shape[-2]))
+    return aggregate_to_kv_heads(attn_layer[:, :, -w:, :].float().sum(dim=2), num_kv_heads)
+
+
+def pool_scores(scores: torch.Tensor, kernel: Optional[int], mode: str = "maxpool") -> torch.Tensor:
+    """1-D pooling along the sequence (stride 1, zero padding of ``kernel // 2``) so that selected tokens form
+    contiguous clusters; ``kernel`` of ``None`` or <= 1 returns the scores unchanged."""
+    if kernel is None or kernel <= 1:
+        return scores
+    b, h, length = scores.shape
+    x = scores.reshape(b * h, 1, length)
+    if mode == "maxpool":
+        pooled = torch.nn.functional.max_pool1d(x, kernel_size=kernel, stride=1, padding=kernel // 2)
+    elif mode == "avgpool":
+        pooled = torch.nn.functional.avg_pool1d(x, kernel_size=kernel, stride=1, padding=kernel // 2)
+    else:
+        raise ValueError(f"unknown pooling {mode!r}: maxpool or avgpool")
+    return pooled[..., :length].reshape(b, h, length)
 
 
 def value_norm_signal(value_layer: torch.Tensor, token_slice: slice) -> torch.Tensor:
@@ -53,9 +97,13 @@ def topk_per_head(signal: torch.Tensor, select_k: int) -> torch.Tensor:
     """Positions (relative to the slice) of the ``select_k`` largest entries of ``signal [B, Hkv, n]`` per head,
     int64 ``[B, Hkv, min(select_k, n)]``.  They come back in ascending position order (the reference returns
     them in score order and every consumer sorts them); ties go to the lower position."""
-    nv.require_cuda(signal, "signal")
     b, h, n = signal.shape
     k = max(0, min(int(select_k), n))
+    if k and (not signal.is_cuda or n > _TOPK_KERNEL_MAX):
+        # a whole prompt's candidates (tens of thousands per head) or host-resident scores: a library selection
+        # (same positions; equal scores may be ordered differently than the kernel's lower-position rule)
+        return torch.topk(signal, k=k, dim=-1).indices.long().sort(dim=-1).values
+    nv.require_cuda(signal, "signal")
     out = torch.empty((b, h, k), dtype=torch.long, device=signal.device)
     if k == 0:
         return out

@@ -258,6 +258,49 @@ def gen_fake_quant(root, out_dir):
     np.savez_compressed(os.path.join(out_dir, "fake_quant.npz"), **out)
 
 
+PROMPT_SELECT_CASES = [
+    # prompt_len, Hq, Hkv, layers, batch, keep_ratio, sink, obs_window, pool_kernel, pooling, seed
+    (20, 4, 2, 2, 1, 0.5, 2, 4, 3, "maxpool", 61),
+    (64, 14, 2, 1, 2, 0.25, 4, 8, 7, "maxpool", 62),
+    (50, 8, 8, 1, 1, 0.6, 0, 16, 5, "avgpool", 63),
+    (12, 4, 4, 1, 1, 1.0, 4, 32, 7, "maxpool", 64),
+    (9, 2, 1, 1, 1, 0.1, 4, 2, 1, "maxpool", 65),
+    (128, 28, 4, 1, 1, 0.3, 4, 32, 7, "maxpool", 66),
+]
+
+
+def gen_prompt_select(root, out_dir):
+    """Stage-A prompt selection: the reference's prompt_tier.select_prompt_indices on seeded causal attention."""
+    pkg = types.ModuleType("refphasekv")
+    pkg.__path__ = [os.path.join(root, "src", "phasekv")]
+    sys.modules["refphasekv"] = pkg
+    mods = {}
+    for name in ("quant", "hetero_cache", "prompt_tier"):
+        spec = importlib.util.spec_from_file_location(f"refphasekv.{name}", os.path.join(root, "src", "phasekv", f"{name}.py"))
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[f"refphasekv.{name}"] = mod
+        spec.loader.exec_module(mod)
+        mods[name] = mod
+    out = {}
+    for i, (plen, hq, hkv, layers, batch, ratio, sink, obs, kernel, pooling, seed) in enumerate(PROMPT_SELECT_CASES):
+        gen = torch.Generator().manual_seed(seed)
+        cfg = types.SimpleNamespace(num_key_value_heads=hkv, num_attention_heads=hq)
+        atts = []
+        for _ in range(layers):
+            logits = torch.randn(batch, hq, plen, plen, generator=gen) * 2.0
+            mask = torch.ones(plen, plen, dtype=torch.bool).tril()
+            atts.append(torch.softmax(logits.masked_fill(~mask, float("-inf")), dim=-1))
+        keep = mods["prompt_tier"].select_prompt_indices(
+            atts, prompt_len=plen, model_config=cfg, prefill_keep_ratio=ratio, sink_tokens=sink, obs_window=obs,
+            pool_kernel=kernel, pooling=pooling)
+        out[f"c{i}.att"] = torch.stack(atts).numpy()
+        out[f"c{i}.keep"] = torch.stack(keep).numpy()
+        out[f"c{i}.args"] = np.array([plen, hq, hkv, layers, batch, sink, obs, kernel, int(pooling == "avgpool")], dtype=np.int64)
+        out[f"c{i}.ratio"] = np.array([ratio])
+    out["n_cases"] = np.array([len(PROMPT_SELECT_CASES)], dtype=np.int64)
+    np.savez_compressed(os.path.join(out_dir, "prompt_select.npz"), **out)
+
+
 def gen_planner(launch_config, out_dir):
     rows = []
     for length in (1, 7, 31, 127, 128, 129, 511, 512, 4096, 8193, 28672, 32768, 131072, 262144):
@@ -284,6 +327,7 @@ def main():
     gen_cold(packing, args.out)
     gen_planner(launch_config, args.out)
     gen_fake_quant(args.reference, args.out)
+    gen_prompt_select(args.reference, args.out)
     for name in sorted(os.listdir(args.out)):
         if name.endswith((".npz", ".json")):
             print(name, os.path.getsize(os.path.join(args.out, name)))
