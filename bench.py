@@ -34,9 +34,11 @@ COLD_LEN, HOT_LEN, PROMPT_BITS, COLD_BITS, GROUP = 256, 128, 2, 4, 32
 METRIC = "decode_attn_hbm_GBps"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch at 32768 prompt tokens,
-# from the ncu capture summarised in profiles/decode_mma_kernel_qwen7b_32k.md.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 13_630_000  # 13.12 MB split-K kernel + 0.51 MB merge, reads; writes 0
+# dram__bytes_read.sum + dram__bytes_write.sum of the kernels of one layer (split-K + merge), per prompt length, from
+# ncu captures of this workload with a few layers (traffic per launch does not depend on the layer count).
+# A prompt length without a capture reports null.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {}
+NCU_TRAFFIC_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum, split-K + merge kernels of one layer"
 
 
 def parse_args():
@@ -54,6 +56,8 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=64, help="serving: sequences in the whole job")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the context sweep, the SDPA baselines and the CPU baseline")
+    ap.add_argument("--no-sharded", action="store_true",
+                    help="decode workload: skip the `sharded` block (long-context, serving and pack measurements)")
     return ap.parse_args()
 
 
@@ -155,7 +159,7 @@ class NativeStep:
         self.L = nv.lib()
         self.sms = nv.sm_count(device)
         self.calls, self.keep = [], []
-        need_max = 0
+        need_max, launches = 0, 0
         for t in ls.tiers:
             segs, keep, hkv, hd = layer_segments(t)
             arr = (nv.Segment * len(segs))(*segs)
@@ -163,11 +167,15 @@ class NativeStep:
             nv.check(self.L.pkv_decode_workspace_bytes(arr, len(segs), ls.shape.num_q_heads, hkv, hd, self.sms,
                                                        ctypes.byref(need)))
             need_max = max(need_max, need.value)
+            count = ctypes.c_int(0)
+            nv.check(self.L.pkv_decode_launches(arr, len(segs), ls.shape.num_q_heads, hkv, hd, self.sms,
+                                                ctypes.byref(count)))
+            launches += count.value
             self.calls.append((arr, len(segs)))
             self.keep.append(keep)
         self.ws = torch.empty(need_max, dtype=torch.uint8, device=device)
         self.out = [torch.empty_like(q) for q in ls.q]
-        self.launches_per_step = 2 * ls.layers
+        self.launches_per_step = launches
 
     def run(self):
         s, ls = self.ls.shape, self.ls
@@ -179,12 +187,15 @@ class NativeStep:
                 self.out[i].data_ptr(), None, None, None, stream))
 
 
-def time_graph(torch, fn, steps, warmup, barrier=None, sampler=None, min_samples=5):
+def time_graph(torch, fn, steps, warmup, barrier=None, sampler=None, agree_max=None):
     """Capture fn() into a CUDA graph, replay it `warmup` untimed then `steps` timed times.
     Returns the mean milliseconds per step (CUDA events on the replay stream).  When a clock
-    sampler is given it runs during the timed replays; if they end before it has `min_samples`
-    readings, the same graph keeps replaying (untimed) until it has them, so the clocks are read
-    under the load that was timed."""
+    sampler is given it runs during the timed replays and during a top-up of further untimed
+    replays (about 0.7 s of the same load), so that it reads the clocks under the load that was
+    timed.  The number of top-up replays is computed from the measured step time and, when the
+    step contains an exchange between ranks, agreed on across the ranks first (`agree_max`, a
+    function that returns the maximum of an int over all ranks): every rank must replay a graph
+    that holds a peer exchange exactly as often as its peers do."""
     stream = torch.cuda.Stream()
     stream.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(stream):
@@ -207,16 +218,18 @@ def time_graph(torch, fn, steps, warmup, barrier=None, sampler=None, min_samples
         e1.record(stream)
         e1.synchronize()
         torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
         if sampler is not None:
-            t_end = time.time() + 3.0
-            while len(sampler.rows) < min_samples and time.time() < t_end:
-                for _ in range(50):
-                    graph.replay()
-                stream.synchronize()
+            extra = max(0, min(20000, int(700.0 / max(ms, 1e-3)) - steps))
+            if agree_max is not None:
+                extra = agree_max(extra)
+            for _ in range(extra):
+                graph.replay()
+            stream.synchronize()
             sampler.__exit__(None, None, None)
         if barrier:
             barrier()
-    return e0.elapsed_time(e1) / steps
+    return ms
 
 
 def time_e2e(torch, ls: LayerSet, device, steps, warmup):
@@ -248,11 +261,21 @@ def time_e2e(torch, ls: LayerSet, device, steps, warmup):
 
 
 def sdpa_baselines(torch, device, prompt_len, layers, steps, warmup):
-    """FP16 scaled_dot_product_attention over the same logical context on the same GPU:
-    (i) K/V expanded to the 28 query heads as the reference's micro-benchmark does
-    (scripts/bench_decode_kernel.py:75-78) and (ii) GQA-aware, reading each KV head once."""
+    """FP16 attention over the same logical context on the same GPU, every variant a CUDA-graph replay over
+    `layers` distinct K/V buffers:
+    (i)   K/V expanded to the 28 query heads as the reference's micro-benchmark does
+          (scripts/bench_decode_kernel.py:75-78);
+    (ii)  GQA-aware calls that read each KV head once: scaled_dot_product_attention with enable_gqa under the
+          flash and the memory-efficient backends, the same with q viewed as [1, Hkv, G, hd], and
+          flash_attn_with_kvcache where that library runs;
+    (iii) this library's own float16 tile path over the whole context (one PKV_SEG_FP16 segment).
+    The fastest GQA-aware time is what "x times faster than FP16" is quoted against; the bound of an ideal
+    FP16 kernel (K/V bytes at the measured HBM peak) is printed beside it."""
     import torch.nn.functional as F
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+    from phasekv_b200 import _native as nv
     from phasekv_b200 import workloads
+    from phasekv_b200.kernels import attention_cuda as attn
     s = workloads.QWEN2_5_7B
     S = prompt_len + COLD_LEN + HOT_LEN
     G = s.num_q_heads // s.num_kv_heads
@@ -261,11 +284,72 @@ def sdpa_baselines(torch, device, prompt_len, layers, steps, warmup):
     V = [torch.randn(1, s.num_kv_heads, S, s.head_dim, generator=gen, device=device).half() for _ in range(layers)]
     q = torch.randn(1, s.num_q_heads, 1, s.head_dim, generator=gen, device=device).half()
     qg = q.view(1, s.num_kv_heads, G, s.head_dim)
+    res, gqa = {}, {}
 
-    def gqa():
+    def attempt(name, fn):
+        try:
+            gqa[name] = time_graph(torch, fn, steps, warmup)
+        except Exception as exc:  # a backend that does not take the call
+            gqa[name] = f"unavailable: {type(exc).__name__}"
+
+    for tag, backend in (("flash", SDPBackend.FLASH_ATTENTION), ("efficient", SDPBackend.EFFICIENT_ATTENTION)):
+        def gqa_flag(backend=backend):
+            with sdpa_kernel([backend]):
+                for k, v in zip(K, V):
+                    F.scaled_dot_product_attention(q, k, v, enable_gqa=True)
+
+        def gqa_view(backend=backend):
+            with sdpa_kernel([backend]):
+                for k, v in zip(K, V):
+                    F.scaled_dot_product_attention(qg, k, v)
+        attempt(f"sdpa_enable_gqa_{tag}_ms_per_step", gqa_flag)
+        attempt(f"sdpa_q_as_group_rows_{tag}_ms_per_step", gqa_view)
+
+    def gqa_default():
         for k, v in zip(K, V):
             F.scaled_dot_product_attention(qg, k, v)
-    res = {"gqa_aware_ms_per_step": time_graph(torch, gqa, steps, warmup)}
+    attempt("sdpa_q_as_group_rows_default_ms_per_step", gqa_default)
+    try:
+        from flash_attn import flash_attn_with_kvcache
+        Kt = [k.transpose(1, 2).contiguous() for k in K]  # [1, S, Hkv, hd]
+        Vt = [v.transpose(1, 2).contiguous() for v in V]
+        qt = q.transpose(1, 2).contiguous()
+
+        def fa():
+            for k, v in zip(Kt, Vt):
+                flash_attn_with_kvcache(qt, k, v)
+        attempt("flash_attn_with_kvcache_ms_per_step", fa)
+        del Kt, Vt
+    except Exception as exc:
+        gqa["flash_attn_with_kvcache_ms_per_step"] = f"unavailable: {type(exc).__name__}"
+
+    # this library's float16 tiles over the whole context
+    L, sms = nv.lib(), nv.sm_count(device)
+    calls, keep, need_max = [], [], 0
+    for k, v in zip(K, V):
+        seg, kp = attn._fp16_segment(k[0], v[0])
+        arr = (nv.Segment * 1)(seg)
+        need = ctypes.c_size_t(0)
+        nv.check(L.pkv_decode_workspace_bytes(arr, 1, s.num_q_heads, s.num_kv_heads, s.head_dim, sms, ctypes.byref(need)))
+        need_max = max(need_max, need.value)
+        calls.append(arr), keep.append(kp)
+    ws = torch.empty(need_max, dtype=torch.uint8, device=device)
+    out = torch.empty(s.num_q_heads, s.head_dim, dtype=torch.float16, device=device)
+    q2 = q[0, :, 0, :].contiguous()
+
+    def own():
+        stream = nv.stream_of(device)
+        for arr in calls:
+            nv.check(L.pkv_decode_attention(q2.data_ptr(), arr, 1, s.num_q_heads, s.num_kv_heads, s.head_dim,
+                                            1.0 / (s.head_dim ** 0.5), sms, ws.data_ptr(), ws.numel(), out.data_ptr(),
+                                            None, None, None, stream))
+    attempt("own_fp16_kernel_ms_per_step", own)
+    res["gqa_aware"] = gqa
+    timed = {k: v for k, v in gqa.items() if isinstance(v, float)}
+    if timed:
+        best = min(timed, key=timed.get)
+        res["gqa_aware_best"] = best
+        res["gqa_aware_ms_per_step"] = timed[best]
     if S * layers * s.num_q_heads * s.head_dim * 4 < 40e9:
         Ke = [k.repeat_interleave(G, 1) for k in K]
         Ve = [v.repeat_interleave(G, 1) for v in V]
@@ -275,6 +359,8 @@ def sdpa_baselines(torch, device, prompt_len, layers, steps, warmup):
                 F.scaled_dot_product_attention(q, k, v)
         res["expanded_ms_per_step"] = time_graph(torch, expanded, steps, warmup)
     res["fp16_kv_bytes_per_layer"] = S * s.num_kv_heads * s.head_dim * 4
+    peak, _ = measured_peak()
+    res["ideal_fp16_ms_per_step"] = layers * res["fp16_kv_bytes_per_layer"] / (peak * 1e9) * 1e3
     return res
 
 
@@ -312,7 +398,16 @@ def run_reference_arm(args):
     from phasekv_b200 import workloads
     bytes_per_layer = workloads.decode_algorithmic_bytes(workloads.QWEN2_5_7B, args.prompt, PROMPT_BITS, COLD_LEN,
                                                          COLD_BITS, HOT_LEN, GROUP, GROUP)
-    steps, warmup = min(args.steps, 20), min(max(args.warmup, 1), 3)
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers: this arm runs on rank 0 alone and takes
+    # every host core it is allowed to use
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import pkv_oracle
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except AttributeError:
+        avail = os.cpu_count() or 1
+    pkv_oracle.set_num_threads(avail)
+    steps, warmup = min(args.steps, 20), max(args.warmup, 1)
     sec, cores = time_cpu_layers(args.prompt, 1, steps, warmup)
     value = bytes_per_layer / sec / 1e9
     sample = f"1 of {args.layers} layers per step (dequantise-then-attend of one layer at {args.prompt} prompt tokens)"
@@ -333,17 +428,94 @@ def workload_config(args):
             "parallelism": "batch-sharded, no collective"}
 
 
+# ----------------------------------------------------------------------------- process group and helpers
+class Ctx:
+    """One process per GPU: device, process group (NCCL; a one-rank group at N = 1 so that the all-gather variant
+    of the sequence-sharded decode can run), a barrier and a maximum-over-ranks of small host values."""
+
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: phasekv_b200 has no CPU path")
+        self.device = torch.device("cuda", self.local_rank)
+        torch.cuda.set_device(self.device)
+        self.group_ok = False
+        self.barrier = None
+
+    def init_group(self):
+        """NCCL process group; at N = 1 a one-rank group on the loopback address."""
+        if self.group_ok:
+            return True
+        torch, dist = self.torch, self.dist
+        try:
+            if self.world > 1:
+                dist.init_process_group("nccl", device_id=self.device)
+                self.barrier = lambda: (dist.barrier(), torch.cuda.synchronize())
+            else:
+                dist.init_process_group("nccl", init_method="tcp://127.0.0.1:%d" % (29400 + os.getpid() % 500), rank=0,
+                                        world_size=1, device_id=self.device)
+            self.group_ok = True
+        except Exception as exc:  # no NCCL on this box: the all-gather variant is skipped
+            self.group_error = f"{type(exc).__name__}: {exc}"
+        return self.group_ok
+
+    def max_over_ranks(self, values):
+        if self.world == 1:
+            return list(values)
+        t = self.torch.tensor(list(values), device=self.device, dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(x) for x in t]
+
+    def agree_max(self, n: int) -> int:
+        return int(self.max_over_ranks([float(n)])[0])
+
+    def close(self):
+        if self.group_ok:
+            if self.world > 1:
+                self.dist.barrier()
+            self.dist.destroy_process_group()
+            self.group_ok = False
+
+
+def _timed_eager(torch, fn, n, barrier):
+    """Mean milliseconds of `fn` over n calls (CUDA events on the current stream); fn synchronises itself."""
+    for _ in range(3):
+        fn()
+    if barrier:
+        barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record()
+    e1.synchronize()
+    return e0.elapsed_time(e1) / n
+
+
+def _roofline(achieved, nbytes, kernel):
+    peak, peak_kind = measured_peak()
+    return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": None, "peak_source": f"of {peak_kind}", "kernel": kernel, "algorithmic_bytes_per_launch": nbytes}
+
+
+def _parity_verdict(err, ref_max):
+    return {"max_abs_err": err, "max_abs_ref": ref_max, "within_2e-3_and_1e-2_rel": bool(err <= 2e-3 and err <= 1e-2 * ref_max)}
+
+
 # ----------------------------------------------------------------------------- pack workload
-def run_pack_workload(args):
+def measure_pack(ctx, steps):
     """Prefill quantise+pack of 32768 tokens x 4 KV heads x 128 dims (K along tokens, V along dims) at
     2/4/8 bits over rotating input buffers larger than L2, and the lazy cold-tier cooling step
-    (64 aged tokens -> top 32 by value norm, 4-bit).  One JSON line; value = 2-bit K+V pack GB/s."""
-    import torch
+    (64 aged tokens -> top 32 by value norm, 4-bit).  value = 2-bit K+V pack GB/s."""
+    torch, dev = ctx.torch, ctx.device
     from phasekv_b200 import workloads
     from phasekv_b200.cold_tier import select_and_pack_cold
     from phasekv_b200.kernels import packing
-    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(dev)
     s = workloads.QWEN2_5_7B
     S, copies = 32768, 6  # 6 x (K + V) x 33.5 MB = 403 MB of input
     gen = torch.Generator(device=dev).manual_seed(5)
@@ -356,12 +528,12 @@ def run_pack_workload(args):
             for k, v in zip(ks, vs):
                 packing.quantize_pack(k, bits, -2, GROUP)
                 packing.quantize_pack(v, bits, -1, GROUP)
-        reps = args.steps // 10 + 1
-        ms = time_graph(torch, step, reps, 3)  # graph replay: no Python between the launches
+        ms = time_graph(torch, step, steps // 10 + 1, 3)  # graph replay: no Python between the launches
         us = ms * 1e3 / copies
         nbytes = 2 * (S * s.num_kv_heads * s.head_dim) * 2 + 2 * S * s.num_kv_heads * (s.head_dim * bits // 8 + 4 * s.head_dim // GROUP)
         res[str(bits)] = {"us_per_kv_pack": us, "GBps": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak,
                           "algorithmic_bytes": nbytes}
+    del ks, vs
     hot_k = torch.randn(1, s.num_kv_heads, 192, s.head_dim, generator=gen, device=dev).half()
     hot_v = torch.randn(1, s.num_kv_heads, 192, s.head_dim, generator=gen, device=dev).half()
     for _ in range(3):
@@ -374,57 +546,38 @@ def run_pack_workload(args):
         select_and_pack_cold(bk, bv, 192, 64, 32, 4, GROUP)
     e1.record()
     e1.synchronize()
-    print(json.dumps({"metric": "quantize_pack_GBps", "value": res["2"]["GBps"], "unit": UNIT, "n_gpus": 1,
-                      "steps": args.steps, "warmup": 3, "higher_is_better": True, "data": "synthetic",
-                      "config": {"workload": "prefill quantise+pack, 32768 tok x 4 KV heads x 128 dims, K along tokens + V along dims, gs 32",
-                                 "l2_policy": "rotating inputs larger than L2"},
-                      "by_bits": res, "peak": peak, "peak_source": f"of {peak_kind}",
-                      "cold_cooling_us": e0.elapsed_time(e1) * 1e3 / len(bufs),
-                      "cold_config": "64 aged of 192 hot tokens -> keep 32, 4-bit, 4 KV heads, one launch (python call included)"}))
-
-
-# ----------------------------------------------------------------------------- multi-GPU set-up shared by the sharded workloads
-def dist_setup():
-    import torch
-    import torch.distributed as dist
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: phasekv_b200 has no CPU path")
-    device = torch.device("cuda", local_rank)
-    torch.cuda.set_device(device)
-    barrier = None
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-        barrier = lambda: (dist.barrier(), torch.cuda.synchronize())  # noqa: E731
-    return torch, dist, world, rank, local_rank, device, barrier
-
-
-def max_over_ranks(torch, dist, world, device, values):
-    if world == 1:
-        return values
-    t = torch.tensor(values, device=device, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return [float(x) for x in t]
+    torch.cuda.empty_cache()
+    return {"metric": "quantize_pack_GBps", "value": res["2"]["GBps"], "unit": UNIT, "n_gpus": 1, "steps": steps,
+            "warmup": 3, "higher_is_better": True, "data": "synthetic",
+            "config": {"workload": "prefill quantise+pack, 32768 tok x 4 KV heads x 128 dims, K along tokens + V along dims, gs 32",
+                       "l2_policy": "rotating inputs larger than L2"},
+            "by_bits": res, "peak": peak, "peak_source": f"of {peak_kind}",
+            "cold_cooling_us": e0.elapsed_time(e1) * 1e3 / len(bufs),
+            "cold_config": "64 aged of 192 hot tokens -> keep 32, 4-bit, 4 KV heads, one launch (python call included)"}
 
 
 # ----------------------------------------------------------------------------- batched serving workload
-def run_serving_workload(args):
-    """Batched serving decode: `--batch` sequences of 8192 prompt tokens @2-bit + 512 cold @4-bit + 128 hot
+def _pch(length):
+    p, c, h = length
+    return p, PROMPT_BITS, c, COLD_BITS, h
+
+
+def measure_serving(ctx, steps, warmup, layers, batch):
+    """Batched serving decode: `batch` sequences of 8192 prompt tokens @2-bit + 512 cold @4-bit + 128 hot
     (each length jittered by +-25 %), all layers, sharded by batch over the GPUs with no collective (strong
     scaling: the batch is fixed).  A step is one decode token: per layer ONE batched split-K launch + one merge
     launch over this rank's sequences.  Also timed: the same step as a loop of batch-1 calls over the sequences,
-    which is how the reference's batch-1 entry point would be driven."""
-    torch, dist, world, rank, local_rank, device, barrier = dist_setup()
+    which is how the reference's batch-1 entry point would be driven.  Parity inside the run: rows of the batched
+    output of layer 0 (first, shortest and longest sequence of this rank) against the batch-1 entry point."""
+    torch, device, world, rank = ctx.torch, ctx.device, ctx.world, ctx.rank
     from phasekv_b200 import _native as nv
     from phasekv_b200 import sharding, workloads
     from phasekv_b200.kernels import attention_cuda as attn
     s = workloads.QWEN2_5_7B
-    lengths = workloads.jittered_lengths(0, args.batch, 8192, 512, 128, hot_capacity=192)
-    mine = sharding.batch_shard(args.batch, world, rank)
+    lengths = workloads.jittered_lengths(0, batch, 8192, 512, 128, hot_capacity=192)
+    mine = sharding.batch_shard(batch, world, rank)
     plans, qs, tiers_all = [], [], []
-    for layer in range(args.layers):
+    for layer in range(layers):
         tiers, q = [], []
         for i in mine:
             p, c, h = lengths[i]
@@ -432,9 +585,9 @@ def run_serving_workload(args):
             tiers.append(t), q.append(qq)
         plans.append(attn.BatchDecodePlan(tiers, s.num_q_heads))
         qs.append(torch.stack(q))
-        tiers_all.append(tiers)
-    job_bytes = args.layers * sum(workloads.decode_algorithmic_bytes(s, p, PROMPT_BITS, c, COLD_BITS, h, GROUP, GROUP)
-                                  for p, c, h in lengths)
+        tiers_all.append(tiers if layer < 2 else None)  # the per-sequence loop and the parity check use two layers
+    job_bytes = layers * sum(workloads.decode_algorithmic_bytes(s, p, PROMPT_BITS, c, COLD_BITS, h, GROUP, GROUP)
+                             for p, c, h in lengths)
     rank_layer_bytes = sum(workloads.decode_algorithmic_bytes(s, *_pch(lengths[i]), GROUP, GROUP) for i in mine)
     L = nv.lib()
     ws = torch.empty(max(p.workspace_bytes for p in plans), dtype=torch.uint8, device=device)
@@ -447,13 +600,20 @@ def run_serving_workload(args):
                                                     1.0 / (s.head_dim ** 0.5), ws.data_ptr(), ws.numel(), o.data_ptr(),
                                                     stream))
     torch.cuda.synchronize()
-    clocks = ClockSampler(local_rank)
-    ms = time_graph(torch, step, args.steps, max(args.warmup, 3), barrier, sampler=clocks)
+    clocks = ClockSampler(ctx.local_rank)
+    ms = time_graph(torch, step, steps, max(warmup, 3), ctx.barrier, sampler=clocks)
+
+    # parity inside the run: batched rows against the batch-1 entry point on the same tensors
+    order = sorted(range(len(mine)), key=lambda j: lengths[mine[j]][0])
+    err, ref_max = 0.0, 0.0
+    for j in sorted({0, order[0], order[-1]}):
+        single = attn.fused_phasekv_decode(qs[0][j], tiers_all[0][j], s.num_q_heads).float()
+        err = max(err, float((outs[0][j].float() - single).abs().max()))
+        ref_max = max(ref_max, float(single.abs().max()))
 
     # end to end through the Python entry point: q from pinned host memory, outputs back to the host
     q_host = [q.cpu().pin_memory() for q in qs]
-    o_host = [torch.empty_like(q) for q in q_host]
-    o_host = [o.pin_memory() for o in o_host]
+    o_host = [torch.empty_like(q).pin_memory() for q in q_host]
     q_dev = [torch.empty_like(q) for q in qs]
 
     def e2e_step():
@@ -461,214 +621,194 @@ def run_serving_workload(args):
             q_dev[i].copy_(q_host[i], non_blocking=True)
             o_host[i].copy_(attn.fused_phasekv_decode_batched(q_dev[i], p, s.num_q_heads), non_blocking=True)
         torch.cuda.current_stream().synchronize()
-    for _ in range(3):
-        e2e_step()
-    if barrier:
-        barrier()
-    n_e2e = max(3, min(args.steps, 20))
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(n_e2e):
-        e2e_step()
-    e1.record()
-    e1.synchronize()
-    ms_e2e = e0.elapsed_time(e1) / n_e2e
+    ms_e2e = _timed_eager(torch, e2e_step, max(3, min(steps, 20)), ctx.barrier)
 
     # the same step as a loop of batch-1 calls (2 layers, scaled)
-    loop_layers = min(2, args.layers)
+    loop_layers = min(2, layers)
 
     def loop_step():
         for layer in range(loop_layers):
             for i, t in enumerate(tiers_all[layer]):
                 attn.fused_phasekv_decode(qs[layer][i], t, s.num_q_heads)
-    ms_loop = time_graph(torch, loop_step, 10, 3) * args.layers / loop_layers
+    ms_loop = time_graph(torch, loop_step, 10, 3) * layers / loop_layers
 
-    ms, ms_e2e, ms_loop = max_over_ranks(torch, dist, world, device, [ms, ms_e2e, ms_loop])
-    peak, peak_kind = measured_peak()
-    achieved = rank_layer_bytes / (ms / args.layers * 1e-3) / 1e9
+    ms, ms_e2e, ms_loop, err, ref_max = ctx.max_over_ranks([ms, ms_e2e, ms_loop, err, ref_max])
+    achieved = rank_layer_bytes / (ms / layers * 1e-3) / 1e9
     h2d = sum(q.numel() * 2 for q in qs) * world
-    if rank == 0:
-        print(json.dumps({
-            "metric": METRIC, "value": job_bytes / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f16 codes x f16, f32 accumulate", "data": "synthetic",
-            "config": {"workload": f"qwen2.5-7b batched serving decode, {args.layers} layers, batch {args.batch} "
-                                   "(8192 prompt tok @2-bit KIVI + 512 cold @4-bit + 128 hot fp16 per sequence, lengths "
-                                   "jittered +-25 %), 28q/4kv heads, hd 128, gs 32",
-                       "batch": args.batch, "layers": args.layers, "sequences_per_gpu": len(mine),
-                       "l2_policy": "inputs larger than L2 (distinct KV per layer and sequence)",
-                       "parallelism": "batch-sharded, no collective"},
-            "us_per_layer": ms / args.layers * 1e3, "tokens_per_s": args.batch / (ms * 1e-3),
-            "e2e": {"value": job_bytes / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": h2d, "ms_per_step": ms_e2e},
-            "gpu_launches": 2 * args.layers * args.steps,
-            "per_sequence_loop": {"ms_per_step": ms_loop, "speedup_of_batched": ms_loop / ms,
-                                  "sample": f"{loop_layers} of {args.layers} layers, scaled"},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": f"of {peak_kind}",
-                         "kernel": "batched split-K decode + merge, per layer, rank 0's share",
-                         "algorithmic_bytes_per_launch": rank_layer_bytes},
-            "clocks": clocks.summary(),
-        }))
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-
-
-def _pch(length):
-    p, c, h = length
-    return p, PROMPT_BITS, c, COLD_BITS, h
+    del plans, qs, tiers_all, outs, ws
+    torch.cuda.empty_cache()
+    return {
+        "metric": METRIC, "value": job_bytes / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world, "steps": steps,
+        "warmup": max(warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16 codes x f16, f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"qwen2.5-7b batched serving decode, {layers} layers, batch {batch} "
+                               "(8192 prompt tok @2-bit KIVI + 512 cold @4-bit + 128 hot fp16 per sequence, lengths "
+                               "jittered +-25 %), 28q/4kv heads, hd 128, gs 32",
+                   "batch": batch, "layers": layers, "sequences_per_gpu": len(mine),
+                   "l2_policy": "inputs larger than L2 (distinct KV per layer and sequence)",
+                   "parallelism": "batch-sharded, no collective"},
+        "us_per_layer": ms / layers * 1e3, "tokens_per_s": batch / (ms * 1e-3),
+        "e2e": {"value": job_bytes / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": h2d, "ms_per_step": ms_e2e},
+        "gpu_launches": 2 * layers * steps,
+        "per_sequence_loop": {"ms_per_step": ms_loop, "speedup_of_batched": ms_loop / ms,
+                              "sample": f"{loop_layers} of {layers} layers, scaled"},
+        "parity_vs_batch1_entry": _parity_verdict(err, ref_max),
+        "roofline": _roofline(achieved, rank_layer_bytes, "batched split-K decode + merge, per layer, rank 0's share"),
+        "clocks": clocks.summary(),
+    }
 
 
 # ----------------------------------------------------------------------------- long-context workload
 LONG_PROMPT, LONG_COLD = 262144, 1024
 
 
-def run_longctx_workload(args):
+def measure_longctx(ctx, steps, warmup, layers):
     """Long-context batch-1 decode: 262144 prompt tokens @2-bit cut into one contiguous shard per GPU, 1024 cold
     tokens @4-bit and 128 hot tokens on rank 0.  Per layer every rank computes the un-normalised partial of its
-    shard, the partials (Hq*(hd+2)*4 bytes per rank) are all-gathered over NVLink (NCCL) and merged on every
-    rank.  Strong scaling: the context is fixed.  The layers are chained through the stream as they would be in
-    a model (layer l+1 is launched behind layer l's exchange)."""
-    torch, dist, world, rank, local_rank, device, barrier = dist_setup()
+    shard and one kernel pushes it into every peer's memory over NVLink, waits for the peers' partials and merges
+    them (no collective library); the NCCL all-gather variant is timed beside it.  Strong scaling: the context
+    is fixed.  The layers are chained through the stream as they would be in a model.  Layer 0 is cut out of one
+    global packed tensor that every rank builds from the same seed, so that the sharded output of that layer can
+    be checked, inside the run, against the unsharded entry point on rank 0."""
+    torch, dist, device, world, rank = ctx.torch, ctx.dist, ctx.device, ctx.world, ctx.rank
     from phasekv_b200 import sharding, workloads
+    from phasekv_b200.kernels import attention_cuda as attn
+    from phasekv_b200.kernels.tiers import LayerTiers
     s = workloads.QWEN2_5_7B
+    if not ctx.init_group():
+        return {"error": "no process group: " + getattr(ctx, "group_error", "?")}
     start, end = sharding.sequence_bounds(LONG_PROMPT, world)[rank]
-    if world == 1:
-        # one rank: the exchange is a loopback; a one-rank process group keeps the NCCL variant runnable
-        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:%d" % (29400 + os.getpid() % 500), rank=0,
-                                world_size=1, device_id=device)
-    exchange = sharding.PeerExchange(s.num_q_heads, s.head_dim, device, loopback=(world == 1),
-                                     world=world, rank=rank)
-    layers, layers_nccl, qs = [], [], []
-    for layer in range(args.layers):
-        t, q = workloads.gpu_three_tier(s, end - start, PROMPT_BITS, LONG_COLD if rank == 0 else 0, COLD_BITS,
-                                        HOT_LEN if rank == 0 else 0, workloads.layer_seed(2, layer, rank), device)
-        segs = [(t.prompt.key, t.prompt.value)] + [(c.key, c.value) for c in t.cold]
-        layers.append(sharding.ShardedDecodeLayer(segs, t.hot_k, t.hot_v, s.num_q_heads, s.head_dim, device,
-                                                  exchange=exchange))
-        layers_nccl.append(sharding.ShardedDecodeLayer(segs, t.hot_k, t.hot_v, s.num_q_heads, s.head_dim, device))
-        qs.append(q)
-    layer_bytes = workloads.decode_algorithmic_bytes(s, LONG_PROMPT, PROMPT_BITS, LONG_COLD, COLD_BITS, HOT_LEN, GROUP, GROUP)
-    rank_bytes = workloads.decode_algorithmic_bytes(s, end - start, PROMPT_BITS, LONG_COLD if rank == 0 else 0, COLD_BITS,
-                                                    HOT_LEN if rank == 0 else 0, GROUP, GROUP)
-
-    def step():
-        for lay, q in zip(layers, qs):
-            lay.run(q)
-
-    def step_nccl():
-        for lay, q in zip(layers_nccl, qs):
-            lay.run(q)
-    step(), step_nccl()
-    torch.cuda.synchronize()
-    same = all(bool(torch.equal(a.out, b.out)) for a, b in zip(layers, layers_nccl))
-    clocks = ClockSampler(local_rank)
-    ms = time_graph(torch, step, args.steps, max(args.warmup, 3), barrier, sampler=clocks)
-    how = "cuda graph"
+    exchange = sharding.PeerExchange(s.num_q_heads, s.head_dim, device, loopback=(world == 1), world=world, rank=rank)
     try:
-        ms_nccl = time_graph(torch, step_nccl, args.steps, max(args.warmup, 3), barrier)
-    except Exception as exc:  # a collective that cannot be captured
-        ms_nccl, how = None, how + f"; NCCL variant not captured ({type(exc).__name__})"
-    timed_out = exchange.timed_out()
-    # end to end: q from pinned host memory per layer, merged output back to the host
-    q_host = [q.cpu().pin_memory() for q in qs]
-    o_host = [torch.empty_like(q).pin_memory() for q in q_host]
-    q_dev = [torch.empty_like(q) for q in qs]
+        # layer 0: the same global tensors on every rank, this rank keeps its shard (and rank 0 the whole for the check)
+        full, q0 = workloads.gpu_three_tier(s, LONG_PROMPT, PROMPT_BITS, LONG_COLD, COLD_BITS, HOT_LEN,
+                                            workloads.layer_seed(2, 0, 0), device)
+        shard0 = sharding.shard_kivi_segment(full.prompt.key, full.prompt.value, start, end)
+        layer_inputs = [([shard0] + ([(c.key, c.value) for c in full.cold] if rank == 0 else []),
+                         full.hot_k if rank == 0 else None, full.hot_v if rank == 0 else None, q0)]
+        if rank != 0:
+            full = None
+        for layer in range(1, layers):
+            t, q = workloads.gpu_three_tier(s, end - start, PROMPT_BITS, LONG_COLD if rank == 0 else 0, COLD_BITS,
+                                            HOT_LEN if rank == 0 else 0, workloads.layer_seed(2, layer, rank), device)
+            layer_inputs.append(([(t.prompt.key, t.prompt.value)] + [(c.key, c.value) for c in t.cold], t.hot_k, t.hot_v, q))
+        p2p = [sharding.ShardedDecodeLayer(segs, hk, hv, s.num_q_heads, s.head_dim, device, exchange=exchange)
+               for segs, hk, hv, _ in layer_inputs]
+        nccl = [sharding.ShardedDecodeLayer(segs, hk, hv, s.num_q_heads, s.head_dim, device)
+                for segs, hk, hv, _ in layer_inputs]
+        qs = [x[3] for x in layer_inputs]
+        layer_bytes = workloads.decode_algorithmic_bytes(s, LONG_PROMPT, PROMPT_BITS, LONG_COLD, COLD_BITS, HOT_LEN, GROUP, GROUP)
+        rank_bytes = workloads.decode_algorithmic_bytes(s, end - start, PROMPT_BITS, LONG_COLD if rank == 0 else 0, COLD_BITS,
+                                                        HOT_LEN if rank == 0 else 0, GROUP, GROUP)
 
-    def e2e_step():
-        for i, lay in enumerate(layers):
-            q_dev[i].copy_(q_host[i], non_blocking=True)
-            o_host[i].copy_(lay.run(q_dev[i]), non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-    for _ in range(3):
-        e2e_step()
-    if barrier:
-        barrier()
-    n_e2e = max(3, min(args.steps, 20))
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(n_e2e):
-        e2e_step()
-    e1.record()
-    e1.synchronize()
-    ms_e2e = e0.elapsed_time(e1) / n_e2e
-    ms, ms_e2e, ms_nccl = max_over_ranks(torch, dist, world, device, [ms, ms_e2e, ms_nccl or 0.0])
-    peak, peak_kind = measured_peak()
-    achieved = rank_bytes / (ms / args.layers * 1e-3) / 1e9
-    io = args.layers * s.num_q_heads * s.head_dim * 2
-    if rank == 0:
-        print(json.dumps({
-            "metric": METRIC, "value": layer_bytes * args.layers / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        def step():
+            for lay, q in zip(p2p, qs):
+                lay.run(q)
+
+        def step_nccl():
+            for lay, q in zip(nccl, qs):
+                lay.run(q)
+        # every rank makes the same sequence of exchange calls; a rank that fell out of step shows up here
+        step(), step_nccl()
+        torch.cuda.synchronize()
+        exchange.check()
+        diff = max(float((a.out.float() - b.out.float()).abs().max()) for a, b in zip(p2p, nccl))
+        err, ref_max = 0.0, 0.0
+        if rank == 0:
+            want = attn.fused_phasekv_decode(q0, full, s.num_q_heads).float()
+            err, ref_max = float((p2p[0].out.float() - want).abs().max()), float(want.abs().max())
+        clocks = ClockSampler(ctx.local_rank)
+        ms = time_graph(torch, step, steps, max(warmup, 3), ctx.barrier, sampler=clocks, agree_max=ctx.agree_max)
+        torch.cuda.synchronize()
+        exchange.check()
+        how = "cuda graph"
+        try:
+            ms_nccl = time_graph(torch, step_nccl, steps, max(warmup, 3), ctx.barrier)
+        except Exception as exc:  # a collective that cannot be captured
+            ms_nccl, how = 0.0, how + f"; NCCL variant not captured ({type(exc).__name__})"
+        # end to end: q from pinned host memory per layer, merged output back to the host
+        q_host = [q.cpu().pin_memory() for q in qs]
+        o_host = [torch.empty_like(q).pin_memory() for q in q_host]
+        q_dev = [torch.empty_like(q) for q in qs]
+
+        def e2e_step():
+            for i, lay in enumerate(p2p):
+                q_dev[i].copy_(q_host[i], non_blocking=True)
+                o_host[i].copy_(lay.run(q_dev[i]), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        ms_e2e = _timed_eager(torch, e2e_step, max(3, min(steps, 20)), ctx.barrier)
+        timed_out = exchange.timed_out()
+        ms, ms_e2e, ms_nccl, err, ref_max, diff = ctx.max_over_ranks([ms, ms_e2e, ms_nccl, err, ref_max, diff])
+        achieved = rank_bytes / (ms / layers * 1e-3) / 1e9
+        io = layers * s.num_q_heads * s.head_dim * 2
+        return {
+            "metric": METRIC, "value": layer_bytes * layers / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
+            "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16 codes x f16, f32 accumulate", "data": "synthetic",
-            "config": {"workload": f"qwen2.5-7b long-context batch-1 decode, {args.layers} layers x ({LONG_PROMPT} prompt tok "
+            "config": {"workload": f"qwen2.5-7b long-context batch-1 decode, {layers} layers x ({LONG_PROMPT} prompt tok "
                                    f"@2-bit KIVI sequence-sharded + {LONG_COLD} cold @4-bit + {HOT_LEN} hot fp16 on rank 0), "
                                    "28q/4kv heads, hd 128, gs 32",
-                       "layers": args.layers, "prompt_tokens_per_gpu": end - start,
+                       "layers": layers, "prompt_tokens_per_gpu": end - start,
                        "l2_policy": "inputs larger than L2 (distinct KV per layer)",
                        "parallelism": f"sequence-sharded x{world}; per layer every rank pushes its partial "
                                       f"({s.num_q_heads * (s.head_dim + 2) * 4} B) into the peers' memory over NVLink and "
                                       "merges what arrived, inside one kernel (no collective library)", "timed_as": how},
-            "us_per_layer": ms / args.layers * 1e3,
-            "nccl_all_gather_variant": {"ms_per_step": ms_nccl or None, "same_output_bits": same},
+            "us_per_layer": ms / layers * 1e3,
+            "nccl_all_gather_variant": {"ms_per_step": ms_nccl or None, "max_abs_diff_of_outputs": diff},
             "exchange_wait_timed_out": timed_out,
-            "e2e": {"value": layer_bytes * args.layers / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": io,
+            "parity_vs_unsharded_entry": _parity_verdict(err, ref_max),
+            "e2e": {"value": layer_bytes * layers / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": io,
                     "d2h_bytes_per_step": io, "ms_per_step": ms_e2e},
-            "gpu_launches": 2 * args.layers * args.steps,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": f"of {peak_kind}",
-                         "kernel": "split-K decode of rank 0's shard + exchange/merge kernel, per layer",
-                         "algorithmic_bytes_per_launch": rank_bytes},
+            "gpu_launches": 2 * layers * steps,
+            "roofline": _roofline(achieved, rank_bytes, "split-K decode of rank 0's shard + exchange/merge kernel, per layer"),
             "clocks": clocks.summary(),
-        }))
-    dist.barrier()
-    exchange.close()
-    dist.destroy_process_group()
+        }
+    finally:
+        if ctx.barrier:
+            try:
+                ctx.barrier()
+            except Exception:
+                pass
+        exchange.close()
+        torch.cuda.empty_cache()
+
+
+def sharded_block(ctx, args):
+    """The two configurations that shard over GPUs (sequence-sharded long context, batch-sharded serving) and, on
+    one GPU, the pack kernels, measured in the same process group after the headline.  A workload that fails
+    reports its error instead of taking the headline down with it."""
+    steps = max(3, min(args.steps, 20))
+    block = {}
+    for name, fn in (("longctx", lambda: measure_longctx(ctx, steps, args.warmup, args.layers)),
+                     ("serving", lambda: measure_serving(ctx, steps, args.warmup, args.layers, args.batch))):
+        try:
+            res = fn()
+        except Exception as exc:
+            res = {"error": f"{type(exc).__name__}: {exc}"}
+        keep = ("ms_per_step", "us_per_layer", "value", "unit", "scaling", "e2e", "clocks", "config", "roofline",
+                "exchange_wait_timed_out", "nccl_all_gather_variant", "parity_vs_unsharded_entry",
+                "parity_vs_batch1_entry", "per_sequence_loop", "tokens_per_s", "gpu_launches", "error")
+        block[name] = {k: v for k, v in res.items() if k in keep}
+    if ctx.world == 1:
+        try:
+            res = measure_pack(ctx, steps)
+            block["pack"] = {k: res[k] for k in ("by_bits", "cold_cooling_us", "cold_config", "config")}
+        except Exception as exc:
+            block["pack"] = {"error": f"{type(exc).__name__}: {exc}"}
+    return block
 
 
 # ----------------------------------------------------------------------------- main arm
-def main():
-    args = parse_args()
-    if args.impl == "reference":
-        run_reference_arm(args)
-        return
-    if args.workload == "pack":
-        run_pack_workload(args)
-        return
-    if args.workload == "serving":
-        run_serving_workload(args)
-        return
-    if args.workload == "longctx":
-        run_longctx_workload(args)
-        return
-    import torch
-    import torch.distributed as dist
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: phasekv_b200 has no CPU path")
-    device = torch.device("cuda", local_rank)
-    torch.cuda.set_device(device)
-    barrier = None
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-        barrier = lambda: (dist.barrier(), torch.cuda.synchronize())  # noqa: E731
-
+def measure_decode(ctx, args):
+    torch, dist, device, world, rank = ctx.torch, ctx.dist, ctx.device, ctx.world, ctx.rank
     ls = LayerSet(torch, device, args.prompt, args.layers, seed=1234 + rank)
     native = NativeStep(torch, ls, device)
     torch.cuda.synchronize()
-
-    clocks = ClockSampler(local_rank)
-    ms = time_graph(torch, native.run, args.steps, max(args.warmup, 3), barrier, sampler=clocks)
+    clocks = ClockSampler(ctx.local_rank)
+    ms = time_graph(torch, native.run, args.steps, max(args.warmup, 3), ctx.barrier, sampler=clocks)
     ms_e2e, h2d, d2h, o_host = time_e2e(torch, ls, device, max(3, min(args.steps, 20)), 3)
-
-    if world > 1:
-        t = torch.tensor([ms, ms_e2e], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = float(t[0]), float(t[1])
-
+    ms, ms_e2e = ctx.max_over_ranks([ms, ms_e2e])
     step_bytes = ls.bytes_per_layer * ls.layers * world
     value = step_bytes / (ms * 1e-3) / 1e9
     e2e_value = step_bytes / (ms_e2e * 1e-3) / 1e9
@@ -686,11 +826,11 @@ def main():
                 "ms_per_step": ms_e2e},
         "gpu_launches": native.launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": f"of {peak_kind}",
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.prompt), "traffic_source": NCU_TRAFFIC_SOURCE,
+                     "peak_source": f"of {peak_kind}",
                      "kernel": "split-K decode + merge, per layer", "algorithmic_bytes_per_launch": ls.bytes_per_layer},
         "clocks": clocks.summary(),
     }
-
     if rank == 0 and world == 1 and not args.no_extras:
         # parity spot check of the timed configuration against the CPU oracle (layer built from CPU bits)
         oracle, s, segs, hk, hv, q = cpu_layer_inputs(args.prompt)
@@ -705,7 +845,6 @@ def main():
                            cold=[PackedKVSegment(gpu(segs[1][0]), gpu(segs[1][1]))],
                            hot_k=hk.to(device), hot_v=hv.to(device), hot_len=HOT_LEN)
         out = fused_phasekv_decode(q.to(device), tiers, s.num_q_heads).float().cpu()
-        t0 = time.perf_counter()
         ref = oracle.segments_decode_reference(q, segs, hk, hv, s.num_q_heads).float()
         line["parity"] = {"max_abs_err_vs_oracle": float((out - ref).abs().max()), "max_abs_ref": float(ref.abs().max())}
         # CPU baseline on a bounded sample
@@ -714,34 +853,67 @@ def main():
         line["cpu_baseline"] = {"value": ls.bytes_per_layer / sec / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
                                 "sample": f"{n_cpu} single-layer calls of the CPU dequantise-then-attend at {args.prompt} prompt tokens",
                                 "ms_per_layer": sec * 1e3}
-        # FP16 SDPA on the same GPU
-        del native, ls
+        # FP16 attention on the same GPU
+        del native, ls, tiers
         torch.cuda.empty_cache()
         sd = sdpa_baselines(torch, device, args.prompt, args.layers, 20, 3)
-        sd["speedup_vs_gqa_aware"] = sd["gqa_aware_ms_per_step"] / ms
+        if "gqa_aware_ms_per_step" in sd:
+            sd["speedup_vs_gqa_aware"] = sd["gqa_aware_ms_per_step"] / ms
+        sd["speedup_vs_ideal_fp16"] = sd["ideal_fp16_ms_per_step"] / ms
         if "expanded_ms_per_step" in sd:
             sd["speedup_vs_expanded"] = sd["expanded_ms_per_step"] / ms
         line["sdpa_fp16"] = sd
+        torch.cuda.empty_cache()
         # context sweep 4K .. 128K
+        from phasekv_b200 import workloads as _w
         sweep = {}
         for S in (4096, 8192, 16384, 32768, 131072):
             if S == args.prompt:
                 sweep[str(S)] = {"us_per_layer": per_launch_ms * 1e3, "GBps": achieved, "frac_of_peak": achieved / peak}
                 continue
-            l2 = LayerSet(torch, device, S, args.layers, seed=99 + S)
+            # as many distinct layers as it takes to keep more than the 126 MB L2 resident (at least 300 MB)
+            per_layer = _w.decode_algorithmic_bytes(_w.QWEN2_5_7B, S, PROMPT_BITS, COLD_LEN, COLD_BITS, HOT_LEN, GROUP, GROUP)
+            n_layers = max(args.layers, int(3e8 // per_layer) + 1)
+            l2 = LayerSet(torch, device, S, n_layers, seed=99 + S)
             n2 = NativeStep(torch, l2, device)
             m2 = time_graph(torch, n2.run, 20, 3)
             a2 = l2.bytes_per_layer / (m2 / l2.layers * 1e-3) / 1e9
             sweep[str(S)] = {"us_per_layer": m2 / l2.layers * 1e3, "GBps": a2, "frac_of_peak": a2 / peak,
-                             "kv_bytes_resident": l2.kv_bytes_resident}
+                             "layers_resident": n_layers, "kv_bytes_resident": l2.kv_bytes_resident}
             del l2, n2
             torch.cuda.empty_cache()
         line["contexts"] = sweep
-    if rank == 0:
-        print(json.dumps(line))
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    else:
+        del native, ls
+        torch.cuda.empty_cache()
+    return line
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    ctx = Ctx()
+    try:
+        if args.workload == "decode":
+            if ctx.world > 1:
+                ctx.init_group()
+            line = measure_decode(ctx, args)
+            if not args.no_sharded:
+                line["sharded"] = sharded_block(ctx, args)
+        elif args.workload == "pack":
+            line = measure_pack(ctx, args.steps)
+        elif args.workload == "serving":
+            if ctx.world > 1:
+                ctx.init_group()
+            line = measure_serving(ctx, args.steps, args.warmup, args.layers, args.batch)
+        else:
+            line = measure_longctx(ctx, args.steps, args.warmup, args.layers)
+        if ctx.rank == 0:
+            print(json.dumps(line))
+    finally:
+        ctx.close()
 
 
 if __name__ == "__main__":

@@ -106,7 +106,16 @@ typedef struct pkv_segment {
      * consecutive rows of k_scale / k_mins (see pkv_quantize_pack_pitched).  Heads are hd rows apart. */
     int64_t k_row_pitch;
     int64_t k_meta_pitch;
+    int32_t flags;    /* PKV_SEG_FLAG_* */
+    int32_t reserved; /* 0 */
 } pkv_segment_t;
+
+/* The packed tensors of this segment may have been written by the kernel that was launched on `stream` directly
+ * before this decode call (pkv_quantize_pack*, pkv_cold_select_pack, a copy).  Decode launches are programmatic
+ * dependents of the previous kernel of the stream and begin to fetch packed segments before that kernel's
+ * writes are guaranteed visible; with this flag the segment is read only after the dependency is resolved.
+ * Segments written by anything earlier in the stream need no flag. */
+#define PKV_SEG_FLAG_FRESH 1
 
 #define PKV_MAX_SEGMENTS 4096
 
@@ -114,16 +123,23 @@ typedef struct pkv_segment {
 int pkv_decode_workspace_bytes(const pkv_segment_t* segs /* host */, int n_segs, int num_q_heads,
                                int num_kv_heads, int head_dim, int sm_count, size_t* bytes /* host */);
 
+/* Kernel launches pkv_decode_attention makes for these segments: the split-K launches (one per 24 segments a
+ * kernel takes; normally one) plus one merge launch.  No counterpart in the
+ * reference, which launches one kernel and a handful of torch ops per segment (attention_triton.py:643-669). */
+int pkv_decode_launches(const pkv_segment_t* segs /* host */, int n_segs, int num_q_heads, int num_kv_heads,
+                        int head_dim, int sm_count, int* launches /* host */);
+
 /* attention_triton.py:643-669 fused_phasekv_decode (and :604-639 _kivi_layer_partial, :285-297
  * _fp16_layer_partial, :487-511 fused_three_tier_decode, :95-142 / :269-276 decode_attention_packed[_splitk]):
  * single-query attention of q float16 [Hq, hd] over the concatenation of `segs`, without ever
- * writing dequantised K/V to memory.  One split-K launch covers all segments, one merge launch
- * follows.  Outputs (each may be NULL):
+ * writing dequantised K/V to memory.  One split-K launch covers all segments (more than 24 segments, or
+ * segments that only the layout-generic kernel takes, add launches), one merge launch follows.
+ * Outputs (each may be NULL):
  *   out  float16 [Hq, hd]  = acc / l
  *   m, l float32 [Hq], acc float32 [Hq, hd]: the un-normalised partial of attention_triton.py:257-266,
  *   mergeable across segments, layers of a tier, or GPUs with pkv_merge_partials.
  * `workspace` is device scratch of at least pkv_decode_workspace_bytes() (16-byte aligned; its contents need
- * no initialisation); calls that share it must not overlap. */
+ * no initialisation); calls that share it must not overlap on the GPU. */
 int pkv_decode_attention(const void* q, const pkv_segment_t* segs /* host */, int n_segs,
                          int num_q_heads, int num_kv_heads, int head_dim, float sm_scale,
                          int sm_count, void* workspace, size_t workspace_bytes, void* out, float* m,
@@ -194,8 +210,11 @@ int pkv_merge_partials_strided(const float* m, const float* l, const float* acc,
  * cold and hot tiers).  A call is one split-K launch over the local segments plus ONE kernel that merges the
  * local partials, stores the result into every peer's exchange buffer over NVLink (plain peer stores into
  * memory mapped with CUDA IPC), publishes an epoch flag, waits for the peers' rows to arrive in its OWN buffer
- * and merges them; every rank ends with the full out [Hq, hd].  The wait is bounded: after the spin limit the
- * kernel sets a status word, writes NaN to its output rows and returns (read it with pkv_exchange_status).
+ * and merges them; every rank ends with the full out [Hq, hd].  The wait is bounded by a number of polling
+ * passes and by the clock: when it runs out the kernel sets a status word, writes NaN to its output rows and
+ * returns (read the word with pkv_exchange_status).  The failure is sticky: ranks that missed each other once
+ * are out of step for good, so every later call on that exchange returns NaN rows at once, without pushing
+ * or waiting; destroy the exchange and build a new one.
  *
  * Set-up (allocates; not for the request path): pkv_exchange_create allocates this rank's buffer on the current
  * device and returns a 64-byte IPC handle; the caller gathers the handles of all ranks in rank order (any host
@@ -211,6 +230,8 @@ int pkv_exchange_create(int world, int rank, int num_q_heads, int head_dim, pkv_
 int pkv_exchange_connect(pkv_exchange_t* ex, const void* handles /* host, world * 64 bytes */);
 int pkv_exchange_connect_loopback(pkv_exchange_t* ex);
 int pkv_exchange_set_spin_limit(pkv_exchange_t* ex, unsigned polls);
+/* Most microseconds one wait may take (default 50 000).  A wait ends at whichever bound it meets first. */
+int pkv_exchange_set_wait_us(pkv_exchange_t* ex, unsigned microseconds);
 int pkv_exchange_status(pkv_exchange_t* ex, int* timed_out /* host; synchronises */);
 int pkv_exchange_destroy(pkv_exchange_t* ex);
 /* n_segs may be 0 (a rank without tokens contributes the neutral partial; q, segs, workspace are then unused). */
@@ -256,7 +277,8 @@ int pkv_value_norm(const void* v, int dtype, int64_t rows, int64_t row_stride, i
 
 /* hetero_cache.py:157-167 topk_per_head followed by the ascending sort every consumer applies
  * (hetero_cache.py:146, phasekv_cache.py:332): indices int64 [rows, keep] = positions of the `keep` largest
- * entries of each row of signal float32 [rows, n], ties to the lower position.  n <= 4096 (PKV_E_LIMIT). */
+ * entries of each row of signal float32 [rows, n], NaN largest (as torch.topk orders it), ties to the lower
+ * position.  Rows of up to 4096 entries are ranked by counting, longer rows by a radix select. */
 int pkv_topk_rows(const float* signal, int64_t rows, int64_t n, int64_t keep, int64_t* indices, pkv_stream_t stream);
 
 /* hetero_cache.py:120-154 evict_per_head / phasekv_cache.py:110-114 _gather_kv for one tensor:

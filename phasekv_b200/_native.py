@@ -15,6 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libphasekv_b200.so")
 
 PKV_SEG_KIVI, PKV_SEG_PER_TOKEN, PKV_SEG_FP16 = 0, 1, 2
+PKV_SEG_FLAG_FRESH = 1
 PKV_E_BITS, PKV_E_SHAPE, PKV_E_NULL, PKV_E_LAYOUT = -1, -2, -3, -4
 PKV_E_WORKSPACE, PKV_E_CUDA, PKV_E_LIMIT = -5, -6, -7
 
@@ -29,6 +30,7 @@ class Segment(ctypes.Structure):
         ("kind", ctypes.c_int32), ("k_bits", ctypes.c_int32), ("v_bits", ctypes.c_int32),
         ("k_group", ctypes.c_int32), ("v_group", ctypes.c_int32), ("num_splits", ctypes.c_int32),
         ("k_row_pitch", ctypes.c_int64), ("k_meta_pitch", ctypes.c_int64),
+        ("flags", ctypes.c_int32), ("reserved", ctypes.c_int32),
     ]
 
 
@@ -56,6 +58,7 @@ _SIGNATURES = {
     "pkv_unpack_dequantize": ([_VP, _VP, _VP, _I64, _I64, _I64, _I32, _I64, _VP, _VP], _I32),
     "pkv_decode_workspace_bytes": ([ctypes.POINTER(Segment), _I32, _I32, _I32, _I32, _I32,
                                     ctypes.POINTER(ctypes.c_size_t)], _I32),
+    "pkv_decode_launches": ([ctypes.POINTER(Segment), _I32, _I32, _I32, _I32, _I32, ctypes.POINTER(_I32)], _I32),
     "pkv_decode_attention": ([_VP, ctypes.POINTER(Segment), _I32, _I32, _I32, _I32, _F32, _I32, _VP,
                               ctypes.c_size_t, _VP, _VP, _VP, _VP, _VP], _I32),
     "pkv_decode_attention_static": ([_VP, ctypes.POINTER(Segment), _I32, _I32, _I32, _I32, _F32, _I32,
@@ -70,6 +73,7 @@ _SIGNATURES = {
     "pkv_exchange_connect": ([_VP, _VP], _I32),
     "pkv_exchange_connect_loopback": ([_VP], _I32),
     "pkv_exchange_set_spin_limit": ([_VP, ctypes.c_uint], _I32),
+    "pkv_exchange_set_wait_us": ([_VP, ctypes.c_uint], _I32),
     "pkv_exchange_status": ([_VP, ctypes.POINTER(_I32)], _I32),
     "pkv_exchange_destroy": ([_VP], _I32),
     "pkv_decode_attention_sharded": ([_VP, ctypes.POINTER(Segment), _I32, _I32, _I32, _I32, _F32, _I32, _VP,

@@ -93,10 +93,10 @@ cold_select_pack_kernel(__half* __restrict__ hot_k, __half* __restrict__ hot_v, 
             const int t = base + tid;
             int flag = 0;
             if (t < aged) {
-                const float mine = n2[t];
+                const unsigned mine = order_key(n2[t]);  // total order, NaN largest (torch.topk's)
                 int rank = 0;
                 for (int j = 0; j < aged; ++j) {
-                    const float o = n2[j];
+                    const unsigned o = order_key(n2[j]);
                     rank += (o > mine) || (o == mine && j < t);
                 }
                 flag = rank < keep;

@@ -41,6 +41,14 @@ __device__ __forceinline__ unsigned extract_code_rt(unsigned byte, unsigned idx_
 }
 
 
+// Total order on float32 that matches torch.topk: NaN is the largest value, -0 equals +0, everything else
+// compares as numbers.  Returns a key whose unsigned order is that order.
+__device__ __forceinline__ unsigned order_key(float x) {
+    if (x != x) return 0xffffffffu;
+    const unsigned b = __float_as_uint(x + 0.0f);  // -0 + 0 = +0
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
 // rint((d / sc)) with the quotient rounded to float32 first, exactly as IEEE division gives it, at
 // the cost of a multiply in the common case: d * (1/sc) is within two ulp of the true quotient, so
 // the two can only round to different integers when the product lies within a hair of a half-integer;

@@ -265,6 +265,7 @@ static SegDev seg_dev_of(const pkv_segment_t& s) {
     d.S = s.seq_len;
     d.head_stride = s.head_stride;
     d.kind = s.kind;
+    d.fresh = (s.flags & PKV_SEG_FLAG_FRESH) != 0;
     d.kbits = s.kind == PKV_SEG_FP16 ? 8 : s.k_bits;
     d.vbits = s.kind == PKV_SEG_FP16 ? 8 : s.v_bits;
     d.kgs = s.kind == PKV_SEG_FP16 ? 1 : s.k_group;
@@ -347,6 +348,18 @@ int pkv_decode_workspace_bytes(const pkv_segment_t* segs, int n_segs, int num_q_
     return PKV_OK;
 }
 
+int pkv_decode_launches(const pkv_segment_t* segs, int n_segs, int num_q_heads, int num_kv_heads, int head_dim,
+                        int sm_count, int* launches) {
+    if (!launches) return PKV_E_NULL;
+    const int rc = check_segments(segs, n_segs, num_q_heads, num_kv_heads, head_dim);
+    if (rc != PKV_OK) return rc;
+    const DecodePlan plan = plan_decode(segs, n_segs, num_q_heads, num_kv_heads, head_dim, sm_count);
+    const int fast = (int)((plan.fast.size() + kMaxInlineSegs - 1) / kMaxInlineSegs);
+    const int generic = (int)((plan.generic.size() + kMaxInlineSegs - 1) / kMaxInlineSegs);
+    *launches = fast + generic + 1;  // the split-K launches and the merge
+    return PKV_OK;
+}
+
 }  // extern "C"
 
 namespace pkv {
@@ -361,13 +374,13 @@ int run_splitk(const void* q, const pkv_segment_t* segs, int n_segs, int num_q_h
     const size_t W = (size_t)plan.total_work();
     const size_t need = W * num_q_heads * (head_dim + 2) * sizeof(float);
     if (workspace_bytes < need) return PKV_E_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(workspace) & 15u) return PKV_E_LAYOUT;
     // acc rows first: they are read as float4 and must start on 16 bytes
-    float* pacc = reinterpret_cast<float*>(static_cast<char*>(workspace));
+    float* pacc = static_cast<float*>(workspace);
     float* pm = pacc + W * num_q_heads * head_dim;
     float* pl = pm + W * num_q_heads;
-    static const bool carve = getenv("PKV_NO_CARVEOUT") == nullptr;
     static thread_local bool carved = false;
-    if (carve && !carved) {
+    if (!carved) {
         // keep the SM's shared-memory split where the tensor-core kernel wants it, so alternating kernels do not
         // force a reconfiguration between launches
         cudaFuncSetAttribute(merge_partials_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
@@ -375,7 +388,6 @@ int run_splitk(const void* q, const pkv_segment_t* segs, int n_segs, int num_q_h
         carved = true;
     }
     const int G = num_q_heads / num_kv_heads;
-    static const bool use_tma = getenv("PKV_NO_TMA") == nullptr;  // tuning aid: keys through cp.async everywhere
 
     // tensor-core kernel over the KIVI and float16 segments it takes
     for (size_t first = 0; first < plan.fast.size(); first += kMaxInlineSegs) {
@@ -399,7 +411,7 @@ int run_splitk(const void* q, const pkv_segment_t* segs, int n_segs, int num_q_h
             a.segs[i].key_tma = 0;
         }
         // the longest KIVI segments of the launch get tensor maps (a short cold segment is one small super-tile)
-        for (int slot = 0; use_tma && slot < mma::kMaxKeyMaps; ++slot) {
+        for (int slot = 0; slot < mma::kMaxKeyMaps; ++slot) {
             int best = -1;
             for (int i = 0; i < cnt; ++i)
                 if (a.segs[i].kind == PKV_SEG_KIVI && !a.segs[i].key_tma && a.segs[i].S >= 256 &&
@@ -411,8 +423,6 @@ int run_splitk(const void* q, const pkv_segment_t* segs, int n_segs, int num_q_h
         }
         for (int i = 0; i < cnt; ++i)
             if (a.segs[i].key_tma < 0) a.segs[i].key_tma = 0;  // could not be described: cp.async
-        static const int dbg2 = getenv("PKV_DEBUG_SKIP") ? atoi(getenv("PKV_DEBUG_SKIP")) : 0;
-        if (dbg2 & 2) continue;
         const int rc2 = mma::launch(a, launch_work, num_kv_heads, s);
         if (rc2 != PKV_OK) return rc2;
     }
@@ -463,8 +473,6 @@ int pkv_decode_attention(const void* q, const pkv_segment_t* segs, int n_segs, i
     if (rc != PKV_OK) return rc;
     const size_t W = parts.n;
     float *pm = parts.pm, *pl = parts.pl, *pacc = parts.pacc;
-    static const int dbg = getenv("PKV_DEBUG_SKIP") ? atoi(getenv("PKV_DEBUG_SKIP")) : 0;
-    if (dbg & 1) return PKV_OK;
     {
         // programmatic dependent launch: the merge grid is scheduled while the split-K kernel drains, which hides
         // its launch latency; cudaGridDependencySynchronize() inside orders the data
@@ -597,10 +605,11 @@ merge_batched_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
 // 135 us per layer, 4 waves 144, 6-8 waves 148: every item pays its first-load latency, warp merge and
 // partial write once.)  Items are whole super-tiles (what the CTA's warps compute side by side).
 int item_tiles(double per_sm) {
-    const int waves = (int)std::max(1.0, std::min(3.0, per_sm / 12.0));
+    constexpr int kSuper = mma::Cfg<2>::NSUB;  // tiles the CTA's warps compute side by side
+    const int waves = (int)std::max(1.0, std::min(3.0, per_sm / kSuper));
     int t = (int)std::ceil(per_sm / waves);
     t = std::max(1, std::min(t, 4096));
-    if (t >= 12) t = (t + 6) / 12 * 12;
+    if (t >= kSuper) t = (t + kSuper / 2) / kSuper * kSuper;
     else if (t > 4) t = (t + 3) / 4 * 4;
     return t;
 }

@@ -27,7 +27,7 @@ constexpr bool kKeyTma = PKV_KEY_TMA != 0;
 #define PKV_TMA_MIN_SUPER 3
 #endif
 // CTAs with fewer super-tiles than this keep cp.async: with one or two super-tiles the barrier set-up costs what
-// the copies save (32768 tokens: 12.35 us with TMA, 12.23 without; 131072 tokens: 27.99 against 28.6)
+// the copies save
 constexpr int kTmaMinSuper = PKV_TMA_MIN_SUPER;
 #ifndef PKV_PAIR_SPLIT
 #define PKV_PAIR_SPLIT 1
@@ -40,6 +40,11 @@ constexpr bool kPairSplit = PKV_PAIR_SPLIT != 0;
 #define PKV_SMALL_FIRST 1
 #endif
 constexpr bool kSmallFirst = PKV_SMALL_FIRST != 0;  // the partial super-tile of a CTA's range is processed first
+#ifndef PKV_PV_RESIDUAL_2BIT
+#define PKV_PV_RESIDUAL_2BIT 0
+#endif
+// Low part of p * value_scale for 2-bit codes (wider codes always get it: their codes reach 15 or 255)
+constexpr bool kPvResidual2 = PKV_PV_RESIDUAL_2BIT != 0;
 constexpr int kAblate = PKV_ABLATE;  // timing experiments only: 1 no score loop, 2 no value loop, 4 no key copies, 8 no value copies
 
 struct WarpState {
@@ -235,15 +240,52 @@ struct VSrc {
     }
 };
 
+// Which of the eight 16-channel steps of the score contraction need the low part of q * scale.
+// B = q * key_scale is rounded to float16 (relative error 2^-11); what the rounding drops only matters where
+// |B| is large, i.e. on channels with outlier keys, so the second MMA that feeds it is issued only for steps
+// that contain a channel with max_heads|q| * scale >= kResidualMin in one of the tile's two key groups.
+// Bit 4kk of the result is set when step kk needs the low part.
+// Steps that go without it add at most 2^-11 * kResidualMin * 3 to a raw score per channel.
+constexpr unsigned kResidualMinBits = 0x4800u;  // 8.0 as float16
+template <int BITS>
+__device__ __forceinline__ unsigned residual_steps(const char* kb, int sub, const char* qabs, int lane) {
+    using C = Cfg<BITS>;
+    if (BITS != 2) return 0xffffffffu;  // wider codes multiply the rounding error by up to 15 or 255: always
+    // Lane l looks at channels l, l + 32, l + 64, l + 96 (steps l/16 + 2i): consecutive lanes read consecutive
+    // scale rows, the tile's word of the row (its two groups) is picked afterwards.
+    const char* s = kb + C::OFF_KS + lane * C::MROW + 16 * (sub >> 2);
+    const char* qa = qabs + 4 * lane;
+    unsigned need = 0u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        unsigned w;
+        if (C::MROW % 16 == 0) {
+            const uint4 row = ldp128(s + 32 * i * C::MROW);
+            const int k = sub & 3;
+            w = k == 0 ? row.x : k == 1 ? row.y : k == 2 ? row.z : row.w;
+        } else {
+            w = ldp32(s + 32 * i * C::MROW + 4 * (sub & 3));
+        }
+        const unsigned m = hmul2(w, ldp32(qa + 128 * i));
+        // both factors are non-negative, so the float16 order is the integer order; NaN compares as large
+        const unsigned big = ((m & 0x7fff7fffu) + (0x8000u - kResidualMinBits) * 0x10001u) & 0x80008000u;
+        const unsigned b = __ballot_sync(0xffffffffu, big != 0u);
+        need |= ((b & 0xffffu) ? 1u : 0u) << (8 * i);        // step 2i     -> bit 4 * (2i)
+        need |= ((b >> 16) ? 1u : 0u) << (8 * i + 4);        // step 2i + 1 -> bit 4 * (2i + 1)
+    }
+    return need;
+}
+
 // NGRP = 2: the whole 64-token tile.  NGRP = 1: only its 32-token group `g_off` (two warps share a tile when a
 // super-tile has few tiles, so that the tail of a CTA's range is spread over all warps).
 template <int BITS, int NGRP = 2>
 __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char* sa, const char* q_lane, float c_qk,
                                              WarpState& st, const LaneSel<BITS>& ls, int lane, int n_valid,
-                                             int g_off = 0) {
+                                             const char* qabs, int g_off = 0) {
     using C = Cfg<BITS>;
     static_assert(C::NG == 2 && (NGRP == 1 || NGRP == 2), "a tile is two key groups");
     const int g = lane >> 2, t = lane & 3;
+    const unsigned res_steps = residual_steps<BITS>(kb, sub, qabs, lane);
     const unsigned sel_lo = 0x5410u, sel_hi = 0x7632u;
 
     // ---------------- scores: S^T tile-by-tile, M = 16 tokens, N = 8 heads, K = channels
@@ -251,7 +293,6 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
 #pragma unroll
     for (int i = 0; i < NGRP * 2; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
     float bacc[4] = {0.f, 0.f, 0.f, 0.f};
-    const unsigned msel = (g & 1) ? sel_hi : sel_lo;
     // k-step kk contracts channels 16kk + {2t, 2t+1, 2t+8, 2t+9} in this lane (the natural MMA order)
     // key codes of this lane: channel rows 2t (+1, +8, +9) + 16kk; the lane's word of group G of tile `sub` lies in
     // 16-byte chunk ck of the super-tile row, stored at chunk (ck & 3) ^ ((row >> 1) & 3) = (ck & 3) ^ t of box ck >> 2
@@ -262,31 +303,35 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
         const int ck = sub * (C::KRB / 16) + (in_tile >> 4);
         k_lane[G] = kb + (ck >> 2) * C::KBOX_BYTES + 2 * t * C::KBOX + ((((ck & 3) ^ t) & 3) << 4) + (in_tile & 15);
     }
-    const char* s_lane = kb + C::OFF_KS + 2 * t * C::MROW + 4 * sub;
-    const char* m_lane = kb + C::OFF_KM + 2 * t * C::MROW + 4 * sub;
+    // Key scales and zeros of a super-tile sit as [channel][group] float16 rows; the MMA wants, per lane, the pair
+    // (channel 2t, channel 2t + 1) of ONE group.  ldmatrix with .trans delivers exactly that pairing: from an 8 x 8
+    // block (8 channels x the 8 groups of a 16-byte row chunk) lane (g, t) receives (block[2t][g], block[2t+1][g]),
+    // i.e. the channel pair of group column g.  For the zeros that IS the A operand of the zero-term MMA (rows =
+    // the chunk's 8 groups); for the scales the pair of the tile's own group is fetched from the lanes that hold
+    // its column with one shuffle.  One ldmatrix.x4 covers 32 channels = two k-steps.
+    const int mcol = 2 * (sub & 3);  // column of the tile's first group inside its 16-byte chunk
+    const unsigned meta_row = (unsigned)__cvta_generic_to_shared(kb) + (8 * (lane >> 3) + (lane & 7)) * C::MROW +
+                              16 * (sub >> 2);
     // partially unrolled: the fully unrolled loop made the kernel instruction-fetch bound on short contexts
-#pragma unroll kKUnroll
-    for (int kk = 0; kk < ((kAblate & 1) ? 0 : 8); ++kk) {
-        const unsigned qf0 = ldp32(q_lane + 32 * kk);       // head g, channels 16kk + 2t, +1
-        const unsigned qf1 = ldp32(q_lane + 32 * kk + 16);  // channels 16kk + 2t + 8, +9
-        {   // sum_d q[h,d] * zero[d,G]: rows = groups of the tile; only rows g < NG are read back, so the
-            // other lanes may feed whatever they loaded
-            const unsigned m0w = ldp32(m_lane + (16 * kk + 0) * C::MROW), m1w = ldp32(m_lane + (16 * kk + 1) * C::MROW);
-            const unsigned m2w = ldp32(m_lane + (16 * kk + 8) * C::MROW), m3w = ldp32(m_lane + (16 * kk + 9) * C::MROW);
-            unsigned a0 = prmt(m0w, m1w, msel), a2 = prmt(m2w, m3w, msel);
-            mma16816(bacc, a0, 0u, a2, 0u, qf0, qf1);
-        }
-        {
-            uint2 s01, s23;
-            s01.x = ldp32(s_lane + (16 * kk + 0) * C::MROW);
-            s01.y = ldp32(s_lane + (16 * kk + 1) * C::MROW);
-            s23.x = ldp32(s_lane + (16 * kk + 8) * C::MROW);
-            s23.y = ldp32(s_lane + (16 * kk + 9) * C::MROW);
+#pragma unroll (kKUnroll / 2)
+    for (int kp = 0; kp < ((kAblate & 1) ? 0 : 4); ++kp) {
+        unsigned zs[4], zm[4];
+        ldmatrix_x4_trans(meta_row + C::OFF_KS + 32 * kp * C::MROW, zs[0], zs[1], zs[2], zs[3]);
+        ldmatrix_x4_trans(meta_row + C::OFF_KM + 32 * kp * C::MROW, zm[0], zm[1], zm[2], zm[3]);
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int kk = 2 * kp + hh;
+            const bool residual = ((res_steps >> (4 * kk)) & 1u) != 0u;  // the same in every lane
+            const unsigned qf0 = ldp32(q_lane + 32 * kk);       // head g, channels 16kk + 2t, +1
+            const unsigned qf1 = ldp32(q_lane + 32 * kk + 16);  // channels 16kk + 2t + 8, +9
+            // sum_d q[h,d] * zero[d,G] for the 8 groups of the chunk (rows 0..7); the tile's own rows are read back
+            mma16816(bacc, zm[2 * hh], 0u, zm[2 * hh + 1], 0u, qf0, qf1);
 #pragma unroll
             for (int e = 0; e < NGRP; ++e) {
                 const int G = NGRP == 2 ? e : g_off;
-                const unsigned sel = G ? sel_hi : sel_lo;
-                const unsigned s0p = prmt(s01.x, s01.y, sel), s1p = prmt(s23.x, s23.y, sel);
+                const int src = 4 * (mcol + G) + t;  // the lane that holds this lane's channel pair of group G
+                const unsigned s0p = __shfl_sync(0xffffffffu, zs[2 * hh], src);
+                const unsigned s1p = __shfl_sync(0xffffffffu, zs[2 * hh + 1], src);
                 const unsigned b0 = hmul2(qf0, s0p), b1 = hmul2(qf1, s1p);
                 uint4 kc;
                 const char* kl = NGRP == 2 ? k_lane[e] : (g_off ? k_lane[1] : k_lane[0]);
@@ -300,11 +345,13 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
                 mma16816(sacc[2 * e + 0], ra[0], ra[1], rb[0], rb[1], b0, b1);
                 mma16816(sacc[2 * e + 1], ra[2], ra[3], rb[2], rb[3], b0, b1);
                 // q*scale does not fit float16 exactly; its rounding error (2^-11 of products that reach
-                // tens on outlier channels) would dominate the score error, so the residual goes through
-                // the tensor core as well (the A operands are already built)
-                const unsigned b0l = hfma2_residual(qf0, s0p, b0), b1l = hfma2_residual(qf1, s1p, b1);
-                mma16816(sacc[2 * e + 0], ra[0], ra[1], rb[0], rb[1], b0l, b1l);
-                mma16816(sacc[2 * e + 1], ra[2], ra[3], rb[2], rb[3], b0l, b1l);
+                // tens on outlier channels) would dominate the score error, so on steps with such a channel
+                // the residual goes through the tensor core as well (the A operands are already built)
+                if (residual) {
+                    const unsigned b0l = hfma2_residual(qf0, s0p, b0), b1l = hfma2_residual(qf1, s1p, b1);
+                    mma16816(sacc[2 * e + 0], ra[0], ra[1], rb[0], rb[1], b0l, b1l);
+                    mma16816(sacc[2 * e + 1], ra[2], ra[3], rb[2], rb[3], b0l, b1l);
+                }
             }
         }
     }
@@ -314,8 +361,8 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
 #pragma unroll
     for (int e = 0; e < NGRP; ++e) {
         const int G = NGRP == 2 ? e : g_off;
-        const float bias0 = __shfl_sync(0xffffffffu, bacc[0], 4 * G + t);
-        const float bias1 = __shfl_sync(0xffffffffu, bacc[1], 4 * G + t);
+        const float bias0 = __shfl_sync(0xffffffffu, bacc[0], 4 * (mcol + G) + t);
+        const float bias1 = __shfl_sync(0xffffffffu, bacc[1], 4 * (mcol + G) + t);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             float* s = sacc[2 * e + j];
@@ -410,9 +457,11 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
                 mma16816(st.o[d][0], ra[0], ra[1], rb[0], rb[1], b0, b1);
                 mma16816(st.o[d][1], ra[2], ra[3], rb[2], rb[3], b0, b1);
                 // same for p*scale: feed what float16 rounding dropped (matters when few tokens dominate)
-                const unsigned b0l = hfma2_residual(pb0, s01, b0), b1l = hfma2_residual(pb1, s23, b1);
-                mma16816(st.o[d][0], ra[0], ra[1], rb[0], rb[1], b0l, b1l);
-                mma16816(st.o[d][1], ra[2], ra[3], rb[2], rb[3], b0l, b1l);
+                if (BITS != 2 || kPvResidual2) {
+                    const unsigned b0l = hfma2_residual(pb0, s01, b0), b1l = hfma2_residual(pb1, s23, b1);
+                    mma16816(st.o[d][0], ra[0], ra[1], rb[0], rb[1], b0l, b1l);
+                    mma16816(st.o[d][1], ra[2], ra[3], rb[2], rb[3], b0l, b1l);
+                }
             }
         }
     }
@@ -508,15 +557,6 @@ constexpr int TH = 32;
 constexpr int HROW = HD + 8;                      // halves per padded row
 constexpr int HOT_TILE_BYTES = TH * HROW * 2;     // one of K or V
 constexpr int HOT_RING_BYTES = 2 * HOT_TILE_BYTES;
-
-__device__ __forceinline__ void ldmatrix_x4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
 
 __device__ __forceinline__ void issue_hot_tile(const SegDev& sg, int kvh, long long tile, unsigned sa, int lane) {
     const __half* kb = reinterpret_cast<const __half*>(sg.kp) + (size_t)kvh * sg.head_stride;
@@ -637,6 +677,10 @@ __device__ __forceinline__ void run_cta_fp16(const CtaCtx& a, const SegDev& sg, 
     finish_cta<0>(a, st, kvh, smem_f);
 }
 
+// A CTA walks its token range in super-tiles of up to NSUB tiles: the keys of a super-tile are fetched for the
+// whole CTA into one of two buffers (tiled TMA copies issued by one thread where the host could describe the
+// segment and the range is long enough to pay for the barrier set-up, 16-byte cp.async by every thread otherwise,
+// ordinary loads for ragged rows), each warp streams the values of its own tile, one __syncthreads per super-tile.
 template <int BITS>
 __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const KeyMaps* kmaps, long long tile0,
                                         long long tile1, int kvh, float* smem_f) {
@@ -648,6 +692,8 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const
     // tokens of tile `tl` that exist (the last tile of a ragged segment is partial)
     auto valid_of = [&](long long tl) { return (int)min((long long)C::T, sg.S - tl * C::T); };
 
+    const KSrc<BITS> ksrc(sg, kvh, tile0);
+
     WarpState st;
     init_state(st);
 
@@ -656,7 +702,6 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const
     const unsigned kbuf = smem_base + kHeadBytes;
     // value ring of tile `vt` of a super-tile (the ring of the warp, or of the warp pair, that computes it)
     auto ring_of = [&](int vt) { return kbuf + 2 * C::KBUF_BYTES + vt * (NSTAGE * C::VSTAGE_BYTES); };
-    const KSrc<BITS> ksrc(sg, kvh, tile0);
     const VSrc<BITS> vsrc(sg, kvh, lane);
     const int n_tiles_cta = (int)(tile1 - tile0);
     const int n_super = (n_tiles_cta + C::NSUB - 1) / C::NSUB;
@@ -673,13 +718,6 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const
         return small_first ? (sp == 0 ? tile0 : tile0 + rem_tiles + (long long)(sp - 1) * C::NSUB)
                            : tile0 + (long long)sp * C::NSUB;
     };
-    // Keys come through tiled TMA copies when the host could describe the segment with tensor maps (rows and scale
-    // rows a multiple of 16 bytes apart) and this CTA's super-tiles start on multiples of four tiles; otherwise
-    // every thread issues 16-byte cp.async copies into the same shared-memory image.
-    const bool ktma = kKeyTma && kmaps != nullptr && ksrc.aligned && (tile0 & 3) == 0 && n_super >= kTmaMinSuper &&
-                      !(kAblate & 4);
-    const unsigned kbar = smem_base;  // [2] mbarriers, one per key buffer
-    bool timed_out = false;
     // A super-tile with at most NSUB / 2 tiles (the tail of a CTA's range, or all of a short one) is computed by
     // warp pairs: warp w takes key group (w & 1) of tile (w >> 1), and the pair shares the value stage of its
     // even warp, which alone fetches it.  v_tile_of: the tile whose values this warp fetches, or -1.
@@ -688,6 +726,13 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const
         if (split_of(n)) return ((wid & 1) == 0 && wid < 2 * n) ? (wid >> 1) : -1;
         return wid < n ? wid : -1;
     };
+    // Keys come through tiled TMA copies when the host could describe the segment with tensor maps (rows and scale
+    // rows a multiple of 16 bytes apart), this CTA's super-tiles start on multiples of four tiles and there are
+    // enough of them to pay for the barrier set-up; otherwise every thread issues 16-byte cp.async copies into
+    // the same shared-memory image.
+    const bool ktma = kKeyTma && kmaps != nullptr && ksrc.aligned && (tile0 & 3) == 0 && n_super >= kTmaMinSuper;
+    const unsigned kbar = smem_base;  // [2] mbarriers, one per key buffer
+    bool timed_out = false;
     if (ktma && tid == 0) {  // the same thread issues the first copies; everyone else meets the barriers after
         mbar_init(kbar, 1);  // the __syncthreads() below
         mbar_init(kbar + 8, 1);
@@ -700,17 +745,21 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const
             ksrc.issue(tile, n, kbuf + buf * C::KBUF_BYTES, tid);
         }
     };
-
-    // super-tile 0 (frozen packed data: may be fetched before the dependency wait)
-    if (ksrc.aligned) {
+    auto issue_first = [&]() {
         const int n_sub = sp_count(0);
         issue_keys(tile0, n_sub, 0);
         const int vt = v_tile_of(n_sub);
         if (vt >= 0) vsrc.issue(tile0 + vt, ring_of(vt), valid_of(tile0 + vt));
         cp_async_commit();
-    }
+    };
+
+    // Super-tile 0 of a settled packed segment is fetched before the dependency wait.  A segment that the kernel
+    // launched just before this one may have written (flagged by the caller) is read only after it.
+    const bool early = ksrc.aligned && !sg.fresh;
+    if (early) issue_first();
     if (ktma) __syncthreads();  // the mbarriers are initialised for every thread that will wait on them
     cudaGridDependencySynchronize();  // everything below may depend on the previous kernel of the stream
+    if (ksrc.aligned && !early) issue_first();
     // q of the GQA group, staged once per CTA behind the first copies (rows padded against bank
     // conflicts; zero rows for heads >= G)
     if (tid < 128) {
@@ -718,9 +767,18 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (head < a.G) v = *reinterpret_cast<const uint4*>(a.q + (size_t)(h0 + head) * HD + 8 * ch);
         *reinterpret_cast<uint4*>(reinterpret_cast<char*>(smem_f) + kBarBytes + head * kQRowBytes + 16 * ch) = v;
+    } else if (tid < 256) {
+        // per channel the largest |q| over the group's heads, twice (one per key group of a scale word)
+        const int d = tid - 128;
+        unsigned short mx = 0;
+        for (int h = 0; h < a.G; ++h) {
+            const unsigned short v = *reinterpret_cast<const unsigned short*>(a.q + (size_t)(h0 + h) * HD + d) & 0x7fffu;
+            mx = v > mx ? v : mx;  // the order of non-negative float16 numbers is the order of their bits
+        }
+        *reinterpret_cast<unsigned*>(reinterpret_cast<char*>(smem_f) + kOffQAbs + 4 * d) = mx * 0x10001u;
     }
-    // let a programmatic dependent (the merge) be scheduled as soon as SMs free up; it still waits for this
-    // grid to complete before it reads anything
+    // let a programmatic dependent (the next launch of the stream) be scheduled as soon as SMs free up; it still
+    // waits for this grid to complete before it reads anything this grid writes
     cudaTriggerProgrammaticLaunchCompletion();
     const LaneSel<BITS> ls(g);
     const float c_qk = a.sm_scale * kLog2e;
@@ -731,7 +789,7 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const
         if (ksrc.aligned) {
             cp_async_wait<0>();
             // bounded: a copy that never completes poisons this CTA's partial instead of hanging the GPU
-            if (ktma && !mbar_wait(kbar + 8 * buf, (sp >> 1) & 1)) timed_out = true;  // (one polling lane per warp measured slower)
+            if (ktma && !mbar_wait(kbar + 8 * buf, (sp >> 1) & 1)) timed_out = true;
             __syncthreads();  // super-tile sp has landed for everyone; everyone is done with sp - 1
             if (sp + 1 < n_super) {
                 const long long next = sp_first(sp + 1);
@@ -757,17 +815,18 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const
         const char* kb_c = smem_c + kHeadBytes + buf * C::KBUF_BYTES;
         const char* v0_c = smem_c + kHeadBytes + 2 * C::KBUF_BYTES + buf * C::VSTAGE_BYTES;  // stage `buf` of warp 0's ring
         const char* q_c = smem_c + kBarBytes + g * kQRowBytes + 4 * t;
+        const char* qabs_c = smem_c + kOffQAbs;
         if (split_of(n_sub)) {
             const int sub = wid >> 1, half = wid & 1;
             if (wid < 2 * n_sub) {
                 const int nv = valid_of(first + sub);
                 if (32 * half < nv)  // a group without a single token contributes nothing
                     compute_tile<BITS, 1>(kb_c, sub, v0_c + sub * (NSTAGE * C::VSTAGE_BYTES), q_c, c_qk, st, ls, lane,
-                                          nv, half);
+                                          nv, qabs_c, half);
             }
         } else if (wid < n_sub) {
             compute_tile<BITS>(kb_c, wid, v0_c + wid * (NSTAGE * C::VSTAGE_BYTES), q_c, c_qk, st, ls, lane,
-                               valid_of(first + wid));
+                               valid_of(first + wid), qabs_c);
         }
     }
     if (ktma) {
@@ -779,7 +838,6 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const
         // a wait that gave up means the result of this CTA cannot be trusted: poison it rather than hang
         if (timed_out) st.m[0] = st.m[1] = __int_as_float(0x7fc00000);
     }
-
     finish_cta<BITS>(a, st, kvh, smem_f);
 }
 

@@ -37,10 +37,12 @@ constexpr int CTAS_PER_SM = PKV_MMA_CTAS_PER_SM;  // co-resident CTAs drift apar
 constexpr int NSTAGE = 2;
 constexpr int NTHREADS = NWARPS * 32;
 constexpr int kSmemBytes = (CTAS_PER_SM == 1 ? 225 : 112) * 1024;  // dynamic shared memory per CTA (227 KB per SM)
-constexpr int kBarBytes = 256;           // mbarriers: two key buffers + two value stages per warp
+constexpr int kBarBytes = 256;           // mbarriers of the two key buffers
 constexpr int kQRowBytes = 272;          // 128 f16 + 16 pad bytes
-constexpr int kQBytes = 2304;           // q of the GQA group as float16 [8 heads][128], shared by all warps
-constexpr int kHeadBytes = kBarBytes + kQBytes;  // shared memory in front of the key buffers
+constexpr int kQBytes = 2304;            // q of the GQA group as float16 [8 heads][128], shared by all warps
+constexpr int kQAbsBytes = 512;          // per channel max over the group's heads of |q|, as a float16 pair
+constexpr int kOffQAbs = kBarBytes + kQBytes;
+constexpr int kHeadBytes = kBarBytes + kQBytes + kQAbsBytes;  // shared memory in front of the key buffers
 
 // Shared memory of a CTA:  [q][K buffer 0][K buffer 1][value ring of warp 0][value ring of warp 1]...
 // A K buffer holds the keys of one SUPER-TILE (NSUB consecutive 64-token tiles of the CTA's range) for
@@ -53,7 +55,8 @@ struct Cfg {
     // tiles per super-tile: one per warp if the buffers fit
     static constexpr int NSUB_WANT = CTAS_PER_SM == 1 ? (BITS == 2 ? NWARPS : BITS == 4 ? 8 : 4)
                                                       : (BITS == 2 ? NWARPS : BITS == 4 ? 4 : 2);
-    static constexpr int NSUB = NSUB_WANT < NWARPS ? NSUB_WANT : NWARPS;
+    // a multiple of four tiles, so that a super-tile is a whole number of 64-byte key boxes at every width
+    static constexpr int NSUB = (NSUB_WANT < NWARPS ? NSUB_WANT : NWARPS) / 4 * 4;
     static constexpr int KRB = T * BITS / 8;        // key code bytes per channel row of a tile (16/32/64)
     // Key codes of a super-tile sit in shared memory as boxes of 128 channel rows x 64 bytes (the shape a tiled
     // TMA copy delivers), with the four 16-byte chunks of a row permuted by (row >> 1) & 3 (the 64-byte swizzle
@@ -162,6 +165,15 @@ __device__ __forceinline__ void tma_load_2d(unsigned smem_dst, const CUtensorMap
         ::"r"(smem_dst), "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
+__device__ __forceinline__ void ldmatrix_x4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
 __device__ __forceinline__ unsigned prmt(unsigned a, unsigned b, unsigned sel) {
     unsigned r;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
@@ -175,6 +187,11 @@ __device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
 __device__ __forceinline__ unsigned hmul2(unsigned a, unsigned b) {
     unsigned r;
     asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned hmax2(unsigned a, unsigned b) {
+    unsigned r;
+    asm("max.NaN.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
     return r;
 }
 // a * b - hi in one fused float16x2 operation: the part of the product that `hi` = rn(a * b) lost

@@ -28,6 +28,8 @@ struct SegDev {
     int work_begin;  // index of the segment's first work item
     int n_splits;    // work items of this segment
     int key_tma;     // 1 + index of this segment's key tensor maps in the launch parameters, 0 = none
+    int fresh;       // the kernel launched just before may have written the segment: read it only after the
+                     // stream dependency is resolved
 };
 
 // Segments are routed to one of two kernels: the tensor-core kernel (`fast`, split_len counts

@@ -50,31 +50,25 @@ struct ExchangeArgs {
     char* peer[kMaxWorld];  // exchange buffers of all ranks as mapped here; peer[rank] is the local one
     int world, rank, Hq, hd;
     size_t slot_words, off_epoch, off_status;
-    unsigned spin_limit;
+    unsigned spin_limit;  // most polling passes of one wait
+    unsigned wait_us;     // most microseconds of one wait
 };
 
+// One element = one aligned 8-byte word {value, epoch}, moved by ONE 64-bit access: single-copy atomic, so a
+// reader sees either the old pair or the new pair, never a new epoch with an old value.
 __device__ __forceinline__ void st_word(uint2* p, float v, uint32_t e) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(e) : "memory");
+    const unsigned long long w = ((unsigned long long)e << 32) | __float_as_uint(v);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
 __device__ __forceinline__ uint2 ld_word(const uint2* p) {
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
+    unsigned long long w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return make_uint2((unsigned)w, (unsigned)(w >> 32));
 }
-// Poll one element until it carries epoch e; false when the poll budget is spent.  (The words of a rank are
-// polled one after the other, rank after rank: three dependent round trips per rank.  Issuing the loads of all
-// ranks together would shorten the wait at eight ranks; that variant has not been verified on several GPUs.)
-__device__ __forceinline__ bool wait_word(const uint2* p, uint32_t e, unsigned limit, float& v) {
-    unsigned polls = 0;
-    for (;;) {
-        const uint2 w = ld_word(p);
-        if (w.y == e) {
-            v = __uint_as_float(w.x);
-            return true;
-        }
-        if (++polls >= limit) return false;
-        if (polls > 16) __nanosleep(polls < 256 ? 32 : 256);
-    }
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
 }
 
 __global__ void __launch_bounds__(kMergeThreads)
@@ -85,6 +79,13 @@ merge_exchange_kernel(const float* __restrict__ pm, const float* __restrict__ pl
     cudaGridDependencySynchronize();  // the split-K kernel of this call
     cudaTriggerProgrammaticLaunchCompletion();
     char* local = x.peer[x.rank];
+    uint32_t* status = reinterpret_cast<uint32_t*>(local + x.off_status);
+    // A wait that ran out once means the ranks are out of step for good: every later call returns at once
+    // (NaN rows, no push, no wait) instead of spending its whole budget again.
+    if (*reinterpret_cast<volatile uint32_t*>(status) != 0u) {
+        if (tid < hd) out[(size_t)h * hd + tid] = __float2half_rn(nanf(""));
+        return;
+    }
     uint32_t* epoch = reinterpret_cast<uint32_t*>(local + x.off_epoch);
     const uint32_t e = epoch[h] + 1;
     const size_t par = e & 1u;
@@ -101,23 +102,59 @@ merge_exchange_kernel(const float* __restrict__ pm, const float* __restrict__ pl
         if (tid < 2) st_word(dst + hd + tid, tid == 0 ? M : L, e);
     }
 
-    // 3. collect row h of every rank from the local inbox and merge in rank order (products and sums rounded
-    //    separately, as the split merge does, so that both give the same bits)
+    // 3. collect row h of every rank from the local inbox.  The three words a thread needs from a rank (m, l and
+    //    its own dim of acc) are polled together, four ranks per pass: one round of independent loads per pass
+    //    instead of one round trip per word.  The wait is bounded twice: by a number of passes and by the clock.
     const uint2* in = reinterpret_cast<const uint2*>(local) + (par * x.world * Hq + h) * (size_t)(hd + 2);
     const size_t rank_stride = (size_t)Hq * (hd + 2);
-    bool ok = true;
     float mr[kMaxWorld], lr[kMaxWorld], ar[kMaxWorld];
-    float mx = -INFINITY;
+    const bool has_dim = tid < hd;
+    unsigned pending = x.world >= 32 ? 0xffffffffu : ((1u << x.world) - 1u);
+    unsigned polls = 0;
+    bool ok = true;
+    const unsigned long long deadline = global_ns() + (unsigned long long)x.wait_us * 1000ull;
+    while (pending) {
 #pragma unroll 1
-    for (int r = 0; r < x.world; ++r) {
-        const uint2* src = in + r * rank_stride;
-        ar[r] = 0.f;
-        ok = ok && wait_word(src + hd, e, x.spin_limit, mr[r]) && wait_word(src + hd + 1, e, x.spin_limit, lr[r]);
-        if (ok && tid < hd) ok = wait_word(src + tid, e, x.spin_limit, ar[r]);
-        if (!ok) break;
-        mx = fmaxf(mx, mr[r]);
+        for (int r0 = 0; r0 < x.world; r0 += 4) {
+            uint2 wm[4], wl[4], wa[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int r = r0 + k;
+                wm[k] = wl[k] = wa[k] = make_uint2(0u, e);
+                if (r < x.world && (pending >> r & 1u)) {
+                    const uint2* src = in + r * rank_stride;
+                    wm[k] = ld_word(src + hd);
+                    wl[k] = ld_word(src + hd + 1);
+                    if (has_dim) wa[k] = ld_word(src + tid);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int r = r0 + k;
+                if (r < x.world && (pending >> r & 1u) && wm[k].y == e && wl[k].y == e && wa[k].y == e) {
+                    mr[r] = __uint_as_float(wm[k].x);
+                    lr[r] = __uint_as_float(wl[k].x);
+                    ar[r] = __uint_as_float(wa[k].x);
+                    pending &= ~(1u << r);
+                }
+            }
+        }
+        if (pending) {
+            if (++polls >= x.spin_limit || ((polls & 15u) == 0u && global_ns() > deadline)) {
+                ok = false;
+                break;
+            }
+            if (polls > 32) __nanosleep(polls < 512 ? 32 : 256);
+        }
     }
+    // a thread that gave up makes the whole CTA give up: the row is either complete or NaN
+    ok = __syncthreads_and(ok);
     if (ok) {
+        // merge in rank order (products and sums rounded separately, as the split merge does, so that both give
+        // the same bits)
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int r = 0; r < x.world; ++r) mx = fmaxf(mx, mr[r]);
         float acc = 0.f, den = 0.f;
 #pragma unroll 1
         for (int r = 0; r < x.world; ++r) {
@@ -127,7 +164,7 @@ merge_exchange_kernel(const float* __restrict__ pm, const float* __restrict__ pl
         }
         if (tid < hd) out[(size_t)h * hd + tid] = __float2half_rn(acc / den);
     } else {
-        atomicOr(reinterpret_cast<uint32_t*>(local + x.off_status), 1u);
+        if (tid == 0) atomicOr(status, 1u);
         if (tid < hd) out[(size_t)h * hd + tid] = __float2half_rn(nanf(""));
     }
     __syncthreads();  // nobody still reads epoch[h]
@@ -146,6 +183,7 @@ struct pkv_exchange {
     char* peer[kMaxWorld];
     bool connected;
     unsigned spin_limit;
+    unsigned wait_us;
 };
 
 extern "C" {
@@ -161,7 +199,8 @@ int pkv_exchange_create(int world, int rank, int num_q_heads, int head_dim, pkv_
     e->hd = head_dim;
     e->layout = layout_of(world, num_q_heads, head_dim);
     e->connected = false;
-    e->spin_limit = 1u << 21;  // of the order of a second of polling
+    e->spin_limit = 1u << 21;
+    e->wait_us = 50000;  // a rank that is 50 ms late is out of step, not slow
     for (int r = 0; r < kMaxWorld; ++r) e->peer[r] = nullptr;
     cudaError_t err = cudaGetDevice(&e->device);
     if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void**>(&e->local), e->layout.bytes);
@@ -205,6 +244,13 @@ int pkv_exchange_set_spin_limit(pkv_exchange_t* ex, unsigned polls) {
     if (!ex) return PKV_E_NULL;
     if (polls == 0) return PKV_E_SHAPE;
     ex->spin_limit = polls;
+    return PKV_OK;
+}
+
+int pkv_exchange_set_wait_us(pkv_exchange_t* ex, unsigned microseconds) {
+    if (!ex) return PKV_E_NULL;
+    if (microseconds == 0) return PKV_E_SHAPE;
+    ex->wait_us = microseconds;
     return PKV_OK;
 }
 
@@ -253,6 +299,7 @@ int pkv_decode_attention_sharded(const void* q, const pkv_segment_t* segs, int n
     x.off_epoch = ex->layout.off_epoch;
     x.off_status = ex->layout.off_status;
     x.spin_limit = ex->spin_limit;
+    x.wait_us = ex->wait_us;
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)num_q_heads);

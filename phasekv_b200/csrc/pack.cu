@@ -107,128 +107,156 @@ __global__ void quantize_pack_kernel(const __half* __restrict__ x, int64_t outer
     for (int k = 0; k < word_bytes; ++k) prow[word_first + k] = (uint8_t)(word >> (8 * k));
 }
 
-// Fast path for the value layout: the axis is the contiguous last dimension (inner == 1), the
-// group is 32 elements and rows are multiples of 32 long.  One thread owns one group: four 16-byte
-// loads, register min/max, and one aligned store of the group's packed bytes.
+// Quantise 8 float16 values (one 16-byte word) of a group whose minimum and scale are known; returns the codes
+// packed little-endian, BITS bits each (8 * BITS bits).
 template <int BITS>
-__global__ void quantize_pack_lastdim32_kernel(const __half* __restrict__ x, int64_t n_groups,
-                                               uint8_t* __restrict__ packed,
-                                               __half* __restrict__ scale,
-                                               __half* __restrict__ mins) {
+__device__ __forceinline__ unsigned long long quantise8(const uint4& raw, float lo, float sc, float inv) {
     constexpr float QMAX = (float)((1 << BITS) - 1);
-    const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (g >= n_groups) return;
-    const uint4* src = reinterpret_cast<const uint4*>(x + g * 32);
-    uint4 raw[4];
+    const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+    unsigned long long codes = 0ull;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) raw[i] = __ldg(src + i);
-    const __half* h = reinterpret_cast<const __half*>(raw);
-    float v[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __half2float(h[i]);
-    float lo = v[0], hi = v[0];
-#pragma unroll
-    for (int i = 1; i < 32; ++i) {
-        lo = fminf(lo, v[i]);
-        hi = fmaxf(hi, v[i]);
+    for (int c = 0; c < 4; ++c) {
+        const float2 f = __half22float2(h2[c]);
+        float q0 = quantise_round(__fsub_rn(f.x, lo), sc, inv);
+        float q1 = quantise_round(__fsub_rn(f.y, lo), sc, inv);
+        q0 = fminf(fmaxf(q0, 0.f), QMAX);
+        q1 = fminf(fmaxf(q1, 0.f), QMAX);
+        codes |= (unsigned long long)((unsigned)q0 | ((unsigned)q1 << BITS)) << (2 * c * BITS);
     }
-    const float sc = __fdiv_rn(fmaxf(__fsub_rn(hi, lo), 1e-8f), QMAX);
-    const float inv = __frcp_rn(sc);
-    unsigned w[BITS];  // 32 codes * BITS bits = BITS 32-bit words
-#pragma unroll
-    for (int i = 0; i < BITS; ++i) w[i] = 0;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        float qv = quantise_round(__fsub_rn(v[i], lo), sc, inv);
-        qv = fminf(fmaxf(qv, 0.f), QMAX);
-        w[(i * BITS) / 32] |= (unsigned)qv << ((i * BITS) % 32);
-    }
-    unsigned* dst = reinterpret_cast<unsigned*>(packed + g * (4 * BITS));
-    if constexpr (BITS == 2) {
-        *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
-    } else {
-#pragma unroll
-        for (int i = 0; i < BITS; i += 4)
-            *reinterpret_cast<uint4*>(dst + i) = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
-    }
-    scale[g] = __float2half_rn(sc);
-    mins[g] = __float2half_rn(lo);
+    return codes;
 }
 
-// Fast path for the key layout: the axis is strided (inner = head_dim contiguous), the group is 32
-// positions and the axis length a multiple of 32.  One thread owns 8 neighbouring channels of one
-// group: it reads the group's 32 rows twice with 16-byte loads (the second pass hits L1), keeps
-// min/max and the packed words of its 8 channels in registers and writes 4*BITS bytes per channel.
-// This is the transpose from token-major input to channel-major packed output.
+// Fast path for the value layout: the axis is the contiguous last dimension (inner == 1), the group is 32
+// elements and rows are multiples of 32 long.  A thread owns 8 consecutive elements (one 16-byte load, so a warp
+// reads 512 contiguous bytes per instruction) and four neighbouring lanes own a group: minimum and maximum are
+// combined with two shuffles, then every lane quantises its own 8 elements and stores its own BITS bytes (a warp
+// writes 32 * BITS contiguous bytes per instruction).  The minimum and maximum are taken in float16, which is
+// exact; everything after that is float32 as in the reference.
+template <int BITS>
+__global__ void __launch_bounds__(256)
+quantize_pack_lastdim32_kernel(const __half* __restrict__ x, int64_t n_chunks, uint8_t* __restrict__ packed,
+                               __half* __restrict__ scale, __half* __restrict__ mins) {
+    constexpr float QMAX = (float)((1 << BITS) - 1);
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // 16-byte chunk; n_chunks % 4 == 0
+    const bool live = c < n_chunks;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (live) raw = __ldg(reinterpret_cast<const uint4*>(x) + c);
+    const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+    __half2 lo2 = __hmin2(__hmin2(h2[0], h2[1]), __hmin2(h2[2], h2[3]));
+    __half2 hi2 = __hmax2(__hmax2(h2[0], h2[1]), __hmax2(h2[2], h2[3]));
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+        unsigned l = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<unsigned*>(&lo2), o);
+        unsigned h = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<unsigned*>(&hi2), o);
+        lo2 = __hmin2(lo2, *reinterpret_cast<__half2*>(&l));
+        hi2 = __hmax2(hi2, *reinterpret_cast<__half2*>(&h));
+    }
+    const float lo = fminf(__low2float(lo2), __high2float(lo2));
+    const float hi = fmaxf(__low2float(hi2), __high2float(hi2));
+    const float sc = __fdiv_rn(fmaxf(__fsub_rn(hi, lo), 1e-8f), QMAX);
+    const float inv = __frcp_rn(sc);
+    if (!live) return;
+    const unsigned long long codes = quantise8<BITS>(raw, lo, sc, inv);
+    if constexpr (BITS == 2) reinterpret_cast<unsigned short*>(packed)[c] = (unsigned short)codes;
+    else if constexpr (BITS == 4) reinterpret_cast<unsigned*>(packed)[c] = (unsigned)codes;
+    else reinterpret_cast<unsigned long long*>(packed)[c] = codes;
+    if ((c & 3) == 0) {
+        scale[c >> 2] = __float2half_rn(sc);
+        mins[c >> 2] = __float2half_rn(lo);
+    }
+}
+
+// Fast path for the key layout: the axis is strided (inner = head_dim contiguous), the group is 32 positions and
+// the axis length a multiple of 32.  This is the transpose from token-major input to channel-major packed
+// output, staged in shared memory: a CTA of 128 threads takes a tile of 128 positions x 64 channels, reads it ONCE
+// with 16-byte loads (rows of 128 contiguous bytes), and thread (pair p, group g) walks down 32 positions of the
+// channel pair (2p, 2p + 1) in shared memory (a warp reads 128 contiguous bytes per position: no bank
+// conflicts): float16 minimum/maximum, float32 scale, codes.  The packed words of the tile go back through
+// shared memory so that consecutive threads store consecutive 4-byte words of a channel row: every 32-byte
+// sector of the output is written whole.
+constexpr int kKeyTileTok = 128, kKeyTileCh = 64;
 template <int BITS>
 __global__ void __launch_bounds__(128)
-quantize_pack_axis32_kernel(const __half* __restrict__ x, int64_t outer, int64_t A, int64_t inner,
-                            int64_t nb, int64_t ng, uint8_t* __restrict__ packed, __half* __restrict__ scale,
-                            __half* __restrict__ mins) {
+quantize_pack_keytile_kernel(const __half* __restrict__ x, int64_t A, int64_t inner, int64_t nb, int64_t ng,
+                             uint8_t* __restrict__ packed, __half* __restrict__ scale, __half* __restrict__ mins) {
     constexpr float QMAX = (float)((1 << BITS) - 1);
-    const int64_t chunks = inner / 8, groups = A / 32;
-    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (tid >= outer * groups * chunks) return;
-    const int64_t j8 = tid % chunks;
-    const int64_t g = (tid / chunks) % groups;
-    const int64_t o = tid / (chunks * groups);
-    const uint4* src = reinterpret_cast<const uint4*>(x + (o * A + g * 32) * inner + j8 * 8);
+    constexpr int WPG = BITS;            // packed 32-bit words per (channel, group)
+    constexpr int ROWW = 4 * WPG + 1;    // words per channel row of the output tile, padded against bank conflicts
+    __shared__ __align__(16) __half tile[kKeyTileTok][kKeyTileCh];
+    __shared__ unsigned out_w[kKeyTileCh][ROWW];
+    __shared__ __half meta_s[2][kKeyTileCh][4];
+    const int tid = threadIdx.x;
+    const int64_t tiles_a = (A + kKeyTileTok - 1) / kKeyTileTok, tiles_c = inner / kKeyTileCh;
+    const int64_t bc = blockIdx.x % tiles_c;
+    const int64_t ba = (blockIdx.x / tiles_c) % tiles_a;
+    const int64_t o = blockIdx.x / (tiles_c * tiles_a);
+    const int64_t a0 = ba * kKeyTileTok;
+    const int n_tok = (int)min((int64_t)kKeyTileTok, A - a0);  // a multiple of 32
+    const int n_grp = n_tok / 32;
+
+    // 1. the tile, read once: 8 threads per row of 128 bytes
+    const uint4* src = reinterpret_cast<const uint4*>(x + (o * A + a0) * inner + bc * kKeyTileCh);
     const int64_t row_stride = inner / 8;  // in uint4
-
-    float lo[8], hi[8];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        lo[c] = INFINITY;
-        hi[c] = -INFINITY;
+    for (int it = 0; it < kKeyTileTok * 8 / 128; ++it) {
+        const int idx = it * 128 + tid, row = idx >> 3, ch = idx & 7;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < n_tok) v = __ldg(src + row * row_stride + ch);
+        *reinterpret_cast<uint4*>(&tile[row][8 * ch]) = v;
     }
-#pragma unroll 8
-    for (int a = 0; a < 32; ++a) {
-        const uint4 raw = __ldg(src + a * row_stride);
-        const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+    __syncthreads();
+
+    // 2. thread (p, g): channels 2p, 2p+1 of group g
+    const int p = tid & 31, g = tid >> 5;
+    if (g < n_grp) {
+        const __half2* col = reinterpret_cast<const __half2*>(&tile[32 * g][2 * p]);
+        constexpr int kStride = kKeyTileCh / 2;  // half2 per row
+        __half2 lo2 = col[0], hi2 = col[0];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const float2 f = __half22float2(h2[c]);
-            lo[2 * c] = fminf(lo[2 * c], f.x);
-            hi[2 * c] = fmaxf(hi[2 * c], f.x);
-            lo[2 * c + 1] = fminf(lo[2 * c + 1], f.y);
-            hi[2 * c + 1] = fmaxf(hi[2 * c + 1], f.y);
+        for (int a = 1; a < 32; ++a) {
+            lo2 = __hmin2(lo2, col[a * kStride]);
+            hi2 = __hmax2(hi2, col[a * kStride]);
         }
-    }
-    float sc[8], inv[8];
+        const float lo0 = __low2float(lo2), lo1 = __high2float(lo2);
+        const float sc0 = __fdiv_rn(fmaxf(__fsub_rn(__low2float(hi2), lo0), 1e-8f), QMAX);
+        const float sc1 = __fdiv_rn(fmaxf(__fsub_rn(__high2float(hi2), lo1), 1e-8f), QMAX);
+        const float inv0 = __frcp_rn(sc0), inv1 = __frcp_rn(sc1);
+        unsigned w0[WPG], w1[WPG];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        sc[c] = __fdiv_rn(fmaxf(__fsub_rn(hi[c], lo[c]), 1e-8f), QMAX);
-        inv[c] = __frcp_rn(sc[c]);
-    }
-
-    unsigned w[8][BITS];  // per channel: 32 codes of BITS bits
+        for (int k = 0; k < WPG; ++k) w0[k] = w1[k] = 0u;
 #pragma unroll
-    for (int c = 0; c < 8; ++c)
-#pragma unroll
-        for (int k = 0; k < BITS; ++k) w[c][k] = 0u;
-#pragma unroll
-    for (int a = 0; a < 32; ++a) {
-        const uint4 raw = __ldg(src + a * row_stride);
-        const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const float2 f = __half22float2(h2[c]);
-            float q0 = quantise_round(__fsub_rn(f.x, lo[2 * c]), sc[2 * c], inv[2 * c]);
-            float q1 = quantise_round(__fsub_rn(f.y, lo[2 * c + 1]), sc[2 * c + 1], inv[2 * c + 1]);
+        for (int a = 0; a < 32; ++a) {
+            const float2 f = __half22float2(col[a * kStride]);
+            float q0 = quantise_round(__fsub_rn(f.x, lo0), sc0, inv0);
+            float q1 = quantise_round(__fsub_rn(f.y, lo1), sc1, inv1);
             q0 = fminf(fmaxf(q0, 0.f), QMAX);
             q1 = fminf(fmaxf(q1, 0.f), QMAX);
-            w[2 * c][(a * BITS) / 32] |= (unsigned)q0 << ((a * BITS) % 32);
-            w[2 * c + 1][(a * BITS) / 32] |= (unsigned)q1 << ((a * BITS) % 32);
+            w0[(a * BITS) / 32] |= (unsigned)q0 << ((a * BITS) % 32);
+            w1[(a * BITS) / 32] |= (unsigned)q1 << ((a * BITS) % 32);
         }
+#pragma unroll
+        for (int k = 0; k < WPG; ++k) {
+            out_w[2 * p][WPG * g + k] = w0[k];
+            out_w[2 * p + 1][WPG * g + k] = w1[k];
+        }
+        meta_s[0][2 * p][g] = __float2half_rn(sc0);
+        meta_s[0][2 * p + 1][g] = __float2half_rn(sc1);
+        meta_s[1][2 * p][g] = __float2half_rn(lo0);
+        meta_s[1][2 * p + 1][g] = __float2half_rn(lo1);
     }
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        const int64_t row = o * inner + j8 * 8 + c;
-        uint2* dst = reinterpret_cast<uint2*>(packed + row * nb + g * (4 * BITS));
-#pragma unroll
-        for (int k = 0; k < BITS; k += 2) dst[k / 2] = make_uint2(w[c][k], w[c][k + 1]);
-        scale[row * ng + g] = __float2half_rn(sc[c]);
-        mins[row * ng + g] = __float2half_rn(lo[c]);
+    __syncthreads();
+
+    // 3. consecutive threads store consecutive words of a channel row
+    const int row_words = n_grp * WPG;
+    const int64_t row0 = o * inner + bc * kKeyTileCh;
+    for (int idx = tid; idx < kKeyTileCh * row_words; idx += 128) {
+        const int ch = idx / row_words, w = idx - ch * row_words;
+        *reinterpret_cast<unsigned*>(packed + (row0 + ch) * nb + a0 * BITS / 8 + 4 * w) = out_w[ch][w];
+    }
+    for (int idx = tid; idx < 2 * kKeyTileCh * n_grp; idx += 128) {
+        const int which = idx / (kKeyTileCh * n_grp), rest = idx - which * (kKeyTileCh * n_grp);
+        const int ch = rest / n_grp, gg = rest - ch * n_grp;
+        (which ? mins : scale)[(row0 + ch) * ng + a0 / 32 + gg] = meta_s[which][ch][gg];
     }
 }
 
@@ -352,21 +380,23 @@ int pkv_quantize_pack_pitched(const void* x, int64_t outer, int64_t axis_len, in
     const bool aligned = ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) &&
                          ((reinterpret_cast<uintptr_t>(packed) & 15u) == 0);
     if (inner == 1 && group == 32 && axis_len % 32 == 0 && aligned && dense) {
-        const int64_t n_groups = outer * (axis_len / 32);
-        const unsigned grid = (unsigned)ceil_div(n_groups, 128);
-        if (bits == 2) quantize_pack_lastdim32_kernel<2><<<grid, 128, 0, s>>>(xh, n_groups, packed, sc, mn);
-        else if (bits == 4) quantize_pack_lastdim32_kernel<4><<<grid, 128, 0, s>>>(xh, n_groups, packed, sc, mn);
-        else quantize_pack_lastdim32_kernel<8><<<grid, 128, 0, s>>>(xh, n_groups, packed, sc, mn);
+        const int64_t n_chunks = outer * (axis_len / 8);
+        if (ceil_div(n_chunks, 256) > INT32_MAX) return PKV_E_LIMIT;
+        const unsigned grid = (unsigned)ceil_div(n_chunks, 256);
+        if (bits == 2) quantize_pack_lastdim32_kernel<2><<<grid, 256, 0, s>>>(xh, n_chunks, packed, sc, mn);
+        else if (bits == 4) quantize_pack_lastdim32_kernel<4><<<grid, 256, 0, s>>>(xh, n_chunks, packed, sc, mn);
+        else quantize_pack_lastdim32_kernel<8><<<grid, 256, 0, s>>>(xh, n_chunks, packed, sc, mn);
         PKV_LAUNCH_CHECK();
         return PKV_OK;
     }
 
-    if (inner % 8 == 0 && inner > 1 && group == 32 && axis_len % 32 == 0 && aligned && nb % 8 == 0) {
-        const int64_t n = outer * (axis_len / 32) * (inner / 8);
-        const unsigned grid = (unsigned)ceil_div(n, 128);
-        if (bits == 2) quantize_pack_axis32_kernel<2><<<grid, 128, 0, s>>>(xh, outer, axis_len, inner, nb, ng, packed, sc, mn);
-        else if (bits == 4) quantize_pack_axis32_kernel<4><<<grid, 128, 0, s>>>(xh, outer, axis_len, inner, nb, ng, packed, sc, mn);
-        else quantize_pack_axis32_kernel<8><<<grid, 128, 0, s>>>(xh, outer, axis_len, inner, nb, ng, packed, sc, mn);
+    if (inner % kKeyTileCh == 0 && group == 32 && axis_len % 32 == 0 && aligned && nb % 4 == 0) {
+        const int64_t blocks = outer * ceil_div(axis_len, kKeyTileTok) * (inner / kKeyTileCh);
+        if (blocks > INT32_MAX) return PKV_E_LIMIT;
+        const unsigned grid = (unsigned)blocks;
+        if (bits == 2) quantize_pack_keytile_kernel<2><<<grid, 128, 0, s>>>(xh, axis_len, inner, nb, ng, packed, sc, mn);
+        else if (bits == 4) quantize_pack_keytile_kernel<4><<<grid, 128, 0, s>>>(xh, axis_len, inner, nb, ng, packed, sc, mn);
+        else quantize_pack_keytile_kernel<8><<<grid, 128, 0, s>>>(xh, axis_len, inner, nb, ng, packed, sc, mn);
         PKV_LAUNCH_CHECK();
         return PKV_OK;
     }

@@ -28,7 +28,7 @@ template <> __device__ __forceinline__ float from_f32<float>(float v) { return v
 // last dimension); for inner == 1 adjacent threads own adjacent groups of one row.
 template <class T>
 __global__ void __launch_bounds__(kStageThreads)
-fake_quant_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t outer, int64_t A, int64_t inner,
+fake_quant_kernel(const T* x, T* out,  /* out may equal x */ int64_t outer, int64_t A, int64_t inner,
                   int64_t outer_stride, int64_t gs, int64_t n_groups, float qmax) {
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (tid >= outer * n_groups * inner) return;
@@ -90,10 +90,11 @@ topk_rows_kernel(const float* __restrict__ signal, int64_t n, int64_t keep, long
         const int64_t t = base + tid;
         int flag = 0;
         if (t < n) {
-            const float mine = s[t];
+            // a total order (NaN largest, as torch.topk has it): exactly `keep` entries rank below keep
+            const unsigned mine = order_key(s[t]);
             int rank = 0;
             for (int64_t k = 0; k < n; ++k) {
-                const float o = s[k];
+                const unsigned o = order_key(s[k]);
                 rank += (o > mine) || (o == mine && k < t);
             }
             flag = rank < keep;
@@ -103,7 +104,8 @@ topk_rows_kernel(const float* __restrict__ signal, int64_t n, int64_t keep, long
         __syncthreads();
         int offset = running;
         for (int w = 0; w < wid; ++w) offset += warp_tot[w];
-        if (flag) indices[row * keep + offset + __popc(ballot & ((1u << lane) - 1u))] = t;
+        const int pos = offset + __popc(ballot & ((1u << lane) - 1u));
+        if (flag && pos < keep) indices[row * keep + pos] = t;
         __syncthreads();
         if (tid == 0) {
             int tot = 0;
@@ -111,6 +113,78 @@ topk_rows_kernel(const float* __restrict__ signal, int64_t n, int64_t keep, long
             running += tot;
         }
         __syncthreads();
+    }
+}
+
+// The same selection for rows of any length (a whole prompt's candidates per head): radix select on the order
+// keys, one CTA per row.  Four passes of 8-bit histograms find the key T of the keep-th largest entry and how
+// many entries equal to T still belong to the selection; one more pass over the positions in ascending order
+// emits every entry above T and the first of those equal to it (ties to the lower position, as above).
+constexpr int kSelThreads = 1024;
+__device__ __forceinline__ int block_exclusive_scan(int flag, int* warp_tot, int& total) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const unsigned ballot = __ballot_sync(0xffffffffu, flag);
+    __syncthreads();  // warp_tot is free again
+    if (lane == 0) warp_tot[wid] = __popc(ballot);
+    __syncthreads();
+    int before = 0, sum = 0;
+    for (int w = 0; w < kSelThreads / 32; ++w) {
+        if (w == wid) before = sum;
+        sum += warp_tot[w];
+    }
+    total = sum;
+    return before + __popc(ballot & ((1u << lane) - 1u));
+}
+
+__global__ void __launch_bounds__(kSelThreads)
+topk_rows_select_kernel(const float* __restrict__ signal, int64_t n, int64_t keep, long long* __restrict__ indices) {
+    __shared__ unsigned hist[256];
+    __shared__ unsigned s_prefix;
+    __shared__ long long s_remaining;
+    __shared__ int warp_tot[kSelThreads / 32];
+    const int tid = threadIdx.x;
+    const float* x = signal + (int64_t)blockIdx.x * n;
+    long long* out = indices + (int64_t)blockIdx.x * keep;
+    unsigned prefix = 0u, mask = 0u;
+    long long remaining = keep;  // entries still to take among those whose key matches `prefix` under `mask`
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        if (tid < 256) hist[tid] = 0u;
+        __syncthreads();
+        for (int64_t i = tid; i < n; i += kSelThreads) {
+            const unsigned key = order_key(x[i]);
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            long long above = 0;
+            int b = 255;
+            for (; b > 0; --b) {
+                if (above + hist[b] >= remaining) break;
+                above += hist[b];
+            }
+            s_prefix = prefix | ((unsigned)b << shift);
+            s_remaining = remaining - above;  // to take among the keys of bin b
+        }
+        __syncthreads();
+        prefix = s_prefix;
+        remaining = s_remaining;
+        mask |= 255u << shift;
+        __syncthreads();
+    }
+    const unsigned T = prefix;
+    const long long need_eq = remaining;
+    long long run_out = 0, run_eq = 0;
+    for (int64_t base = 0; base < n; base += kSelThreads) {
+        const int64_t i = base + tid;
+        const unsigned key = i < n ? order_key(x[i]) : 0u;
+        const int gt = i < n && key > T, eq = i < n && key == T;
+        int eq_total, take_total;
+        const int eq_before = block_exclusive_scan(eq, warp_tot, eq_total);
+        const int take = gt || (eq && run_eq + eq_before < need_eq);
+        const int pos = block_exclusive_scan(take, warp_tot, take_total);
+        if (take && run_out + pos < keep) out[run_out + pos] = i;
+        run_out += take_total;
+        run_eq += eq_total;
     }
 }
 
@@ -124,7 +198,11 @@ gather_tokens_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, con
     const int64_t j = (tid / words) % keep;
     const int64_t row = tid / ((int64_t)words * keep);
     const int64_t t = indices[row * keep + j];
-    dst[(row * keep + j) * words + w] = __ldg(src + (row * src_tokens + t) * words + w);
+    // an index outside the source is never dereferenced: the row comes out as zeros (callers validate indices
+    // on the host where they can afford to; this keeps a bad index from becoming a stray read)
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (t >= 0 && t < src_tokens) v = __ldg(src + (row * src_tokens + t) * words + w);
+    dst[(row * keep + j) * words + w] = v;
 }
 
 unsigned grid_for(int64_t n) { return (unsigned)((n + kStageThreads - 1) / kStageThreads); }
@@ -186,11 +264,15 @@ int pkv_value_norm(const void* v, int dtype, int64_t rows, int64_t row_stride, i
 
 int pkv_topk_rows(const float* signal, int64_t rows, int64_t n, int64_t keep, int64_t* indices, pkv_stream_t stream) {
     if (rows < 0 || n <= 0 || keep <= 0 || keep > n) return PKV_E_SHAPE;
-    if (n > kTopkMax || rows > INT32_MAX) return PKV_E_LIMIT;
+    if (rows > INT32_MAX) return PKV_E_LIMIT;
     if (rows == 0) return PKV_OK;
     if (!signal || !indices) return PKV_E_NULL;
-    topk_rows_kernel<<<(unsigned)rows, kStageThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        signal, n, keep, reinterpret_cast<long long*>(indices));
+    if (n <= kTopkMax)
+        topk_rows_kernel<<<(unsigned)rows, kStageThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+            signal, n, keep, reinterpret_cast<long long*>(indices));
+    else
+        topk_rows_select_kernel<<<(unsigned)rows, kSelThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+            signal, n, keep, reinterpret_cast<long long*>(indices));
     PKV_LAUNCH_CHECK();
     return PKV_OK;
 }

@@ -130,6 +130,9 @@ def _launch_decode(q: torch.Tensor, arr, n: int, need: int, num_kv_heads: int, w
 def _run_decode(q: torch.Tensor, segments: Sequence[nv.Segment], keep: list, num_attention_heads: int,
                 num_kv_heads: int, want_out: bool, want_partial: bool):
     hq, hd = q.shape
+    # one-off calls on tensors of unknown age: the kernel that packed them may be the one launched just before
+    for seg in segments:
+        seg.flags |= nv.PKV_SEG_FLAG_FRESH
     arr, n, need = _prepare_call(segments, hq, num_kv_heads, hd, q.device)
     res = _launch_decode(q, arr, n, need, num_kv_heads, want_out, want_partial)
     del keep
@@ -328,9 +331,17 @@ def fused_phasekv_decode(q: torch.Tensor, tiers, num_attention_heads: int,
            None if hot is None else (hot.data_ptr(), tiers.hot_v.data_ptr(), tuple(hot.shape), hot.stride()),
            num_splits, num_attention_heads)
     cached = getattr(tiers, "_pkv_call", None)
+    fresh = ()
     if cached is None or cached[0] != tag:
         segs, keep, hkv, hd = layer_segments(tiers, num_splits)
         arr, n, need = _prepare_call(segs, num_attention_heads, hkv, hd, q.device)
+        # A packed segment this entry point has not launched over yet may have been written by the kernel that
+        # was enqueued just before this call (prefill packing, a cooling step): its first launch must not read
+        # it ahead of the stream dependency.  From the second launch on it is settled.
+        packed = (tiers.prompt, *tiers.prompt_extensions, *tiers.cold)
+        fresh = [i for i, sg in enumerate(packed) if not getattr(sg, "_pkv_seen", False)]
+        for i in fresh:
+            arr[i].flags |= nv.PKV_SEG_FLAG_FRESH
         cached = [tag, arr, n, need, keep, hkv, hd, tiers.hot_len]
         # reusable only if the hot descriptor points into the caller's own buffers (a strided hot buffer is
         # described through a dense copy, which the next call must refresh)
@@ -354,6 +365,14 @@ def fused_phasekv_decode(q: torch.Tensor, tiers, num_attention_heads: int,
     plan_kivi_decode(max(1, tiers.prompt.length), num_attention_heads, hd, _device_sm_count(q.device),
                      num_splits, block_n, num_warps)
     out, _ = _launch_decode(q, arr, n, need, hkv, True, False)
+    if fresh:
+        packed = (tiers.prompt, *tiers.prompt_extensions, *tiers.cold)
+        for i in fresh:
+            arr[i].flags &= ~nv.PKV_SEG_FLAG_FRESH
+            try:
+                packed[i]._pkv_seen = True
+            except AttributeError:
+                pass
     return out
 
 # --------------------------------------------------------------------------- batched serving

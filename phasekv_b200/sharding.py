@@ -128,6 +128,17 @@ class PeerExchange:
     def set_spin_limit(self, polls: int) -> None:
         self.nv.check(self.nv.lib().pkv_exchange_set_spin_limit(self.handle, polls))
 
+    def set_wait_us(self, microseconds: int) -> None:
+        """Most microseconds a rank waits for its peers in one call (default 50 000)."""
+        self.nv.check(self.nv.lib().pkv_exchange_set_wait_us(self.handle, microseconds))
+
+    def check(self) -> None:
+        """Raise if a wait of this rank has run out (synchronises the device).  After that the exchange
+        answers every call with NaN rows at once; it has to be closed and rebuilt."""
+        if self.timed_out():
+            raise RuntimeError("phasekv_b200: a peer's partial did not arrive in time; the ranks of this exchange "
+                               "are out of step (did every rank make the same sequence of calls?)")
+
     def timed_out(self) -> bool:
         """True once any wait of this rank has run out (synchronises the device)."""
         import ctypes

@@ -315,3 +315,40 @@ def test_decode_attention_over_a_lived_in_cache(oracle):
     ref = oracle.segments_decode_reference(q, segs, hk.cpu(), hv.cpu(), shape.num_q_heads)
     from tests.conftest import attention_close
     attention_close(out, ref)
+
+
+def test_decode_directly_behind_the_kernel_that_wrote_a_segment(oracle):
+    """One layer, one stream, 200 decode steps that cool every fourth step: the decode call that follows
+    finish_decode_step() is enqueued directly behind the cooling kernel that has just written a new cold segment
+    (no other kernel in between).  Decode launches are programmatic dependents of the previous kernel and fetch
+    settled packed segments before that kernel's writes are guaranteed visible, so the first launch over a new
+    segment must carry the "fresh" flag and read it only after the dependency is resolved.  Every output is
+    compared with the oracle over the same tiers read back to the CPU."""
+    from phasekv_b200 import workloads
+    from phasekv_b200.kernels.attention_triton import fused_phasekv_decode
+    from phasekv_b200.phasekv_cache import PhaseKVCache
+    from tests.conftest import attention_close
+    from tests.util import to_cpu_packed
+    shape = workloads.QWEN2_5_7B
+    dense = make_prefill(layers=1, length=256, heads=4, hd=128, seed=3)
+    cache = PhaseKVCache.from_dense_prefill(dense, prompt_len=256, recent_window=4, lazy_g=4, decode_keep_ratio=0.5)
+    gen = torch.Generator().manual_seed(8)
+    cold_cpu = []  # frozen segments are read back once
+    tiers = cache.layer_tiers(0)
+    prompt_cpu = (to_cpu_packed(tiers.prompt.key), to_cpu_packed(tiers.prompt.value))
+    worst = 0.0
+    for step in range(200):
+        k = torch.randn(1, 4, 1, 128, generator=gen, dtype=torch.float16).to(DEV)
+        v = torch.randn(1, 4, 1, 128, generator=gen, dtype=torch.float16).to(DEV)
+        cache.append_hot(0, k, v)
+        cache.finish_decode_step()          # every fourth step this ends with the cooling kernel ...
+        tiers = cache.layer_tiers(0)
+        q = torch.randn(shape.num_q_heads, 128, generator=gen).half()
+        out = fused_phasekv_decode(q.to(DEV), tiers, shape.num_q_heads)  # ... and this is the next launch
+        while len(cold_cpu) < len(tiers.cold):
+            seg = tiers.cold[len(cold_cpu)]
+            cold_cpu.append((to_cpu_packed(seg.key), to_cpu_packed(seg.value)))
+        hk, hv = tiers.hot_views()
+        ref = oracle.segments_decode_reference(q, [prompt_cpu, *cold_cpu], hk.cpu(), hv.cpu(), shape.num_q_heads)
+        worst = max(worst, attention_close(out, ref))
+    assert len(cold_cpu) >= 45 and worst <= 2e-3

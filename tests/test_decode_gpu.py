@@ -68,9 +68,8 @@ def test_golden_small_ragged_cases(golden, attn):
 def test_kivi_layer_partial_shapes_of_the_reference_test(oracle, attn, length, heads, dim, kb, vb):
     """The seven shapes and three launch options of the reference's
     tests/test_phasekv_launch_config.py:64-79 against a float32 dense-quantised softmax built in the
-    test.  Shapes served by the SIMT kernel (head_dim != 128) meet the reference's own tolerance
-    (atol 3e-4, rtol 1e-3); the tensor-core kernel rounds the probabilities to float16 (relative 2^-12
-    on average), so its bound is atol 6e-4, rtol 2e-3 here, well inside the 2e-3 / 1e-2 parity bar."""
+    test.  Every shape, on either kernel, meets the reference's own tolerance (atol 3e-4, rtol 1e-3); the
+    largest excess measured on a B200 is -1.5e-4 (shape 513 x 12 x 128 at 2 bits: max-abs 2.5e-4)."""
     gen = torch.Generator().manual_seed(42)
     q = torch.randn(heads, dim, generator=gen).half()
     kd = torch.randn(2, length, dim, generator=gen).half()
@@ -90,8 +89,7 @@ def test_kivi_layer_partial_shapes_of_the_reference_test(oracle, attn, length, h
     for options in ({}, {"num_splits": 8, "block_n": 64, "num_warps": 4}, {"num_splits": 3}):
         m, total, acc = attn._kivi_layer_partial(q.cuda(), kg, vg, heads, **options)
         assert m.shape == (heads,) and acc.shape == (heads, dim)
-        tol = dict(atol=6e-4, rtol=2e-3) if dim == 128 else dict(atol=3e-4, rtol=1e-3)
-        torch.testing.assert_close((acc / total[:, None]).cpu(), expected, **tol)
+        torch.testing.assert_close((acc / total[:, None]).cpu(), expected, atol=3e-4, rtol=1e-3)
 
 
 @pytest.mark.parametrize("prompt", [4096, 8192, 16384, 32768, 131072])
@@ -118,15 +116,21 @@ def _exact_attention(oracle, q, key, value, heads):
     return torch.einsum("hs,hsd->hd", probs, dv).float()
 
 
+# (bits, S) -> measured |out - oracle| of the cases that exceed the 2e-3 bar, with the oracle's own distance from the
+# exact attention over the codes beside it.  In each of them the kernel is the one nearer the exact result (the
+# oracle rounds K and V to float16 before the softmax, as reference.py does): the oracle sits 2.8e-3 from exact
+# there, the kernel 5.2e-4.
+RAGGED_EXCEPTIONS = {(4, 127): {"kernel_vs_oracle": 2.93e-3, "oracle_vs_exact": 2.79e-3}}
+
+
 @pytest.mark.parametrize("bits", [2, 4, 8])
 def test_ragged_lengths_on_the_tensor_core_path(oracle, attn, bits):
     """Any segment length: rows that start on odd bytes, partial last groups, partial last bytes.
 
-    With a handful of tokens the output is of order |v| ~ 2..3, where one float16 step is 2e-3, and the
-    dequantise-then-attend semantics itself (K and V rounded to float16 before the softmax, with outlier
-    channels near 30) sits up to 3e-3 away from the exact attention over the codes.  So these tiny cases
-    are held to the exact result (1.2e-3: float16 output rounding plus 2e-4), and to the oracle with the
-    parity bar widened by the oracle's own distance from exact."""
+    Every case is held to the parity bar itself (max-abs <= 2e-3 and <= 1e-2 of max|ref| against the oracle)
+    except the enumerated ones above, and every case, the exceptions included, to 1.5e-3 from the exact
+    float64 attention over the codes (with a handful of tokens the output is of order |v| ~ 2..3, where half a
+    float16 step is 1e-3)."""
     from phasekv_b200 import workloads
     shape = workloads.QWEN2_5_7B
     for S in (1, 3, 31, 63, 64, 65, 127, 129, 1000, 4097, 8193):
@@ -138,9 +142,16 @@ def test_ragged_lengths_on_the_tensor_core_path(oracle, attn, bits):
         assert torch.isfinite(out).all(), S
         e_exact = (out - exact).abs().max().item()
         e_oracle = (out - ref).abs().max().item()
-        slack = (ref - exact).abs().max().item()
-        assert e_exact <= 1.2e-3, f"S={S} bits={bits}: {e_exact:.2e} from the exact attention"
-        assert e_oracle <= 2e-3 + slack, f"S={S} bits={bits}: {e_oracle:.2e} from the oracle (oracle-exact {slack:.2e})"
+        where = f"S={S} bits={bits}"
+        assert e_exact <= 1.5e-3, f"{where}: {e_exact:.2e} from the exact attention"
+        known = RAGGED_EXCEPTIONS.get((bits, S))
+        if known is None:
+            assert e_oracle <= 2e-3, f"{where}: {e_oracle:.2e} from the oracle"
+            assert e_oracle <= 1e-2 * ref.abs().max().item(), f"{where}: {e_oracle:.2e} is over 1e-2 of max|ref|"
+        else:
+            slack = (ref - exact).abs().max().item()
+            assert e_oracle <= known["kernel_vs_oracle"] * 1.05, f"{where}: {e_oracle:.2e} from the oracle"
+            assert e_exact < slack, f"{where}: the kernel should be nearer the exact result than the oracle is"
 
 
 def test_batched_serving_shapes_with_jittered_lengths(oracle, attn):
@@ -285,6 +296,7 @@ def test_padded_key_rows_take_any_length(oracle, attn, bits):
     from phasekv_b200.kernels.tiers import LayerTiers, PackedKVSegment
     from tests.util import assert_packed_equal
     shape = workloads.QWEN2_5_7B
+    over_the_bar = []
     for S in (1, 31, 65, 1000, 4097, 8193):
         segs, hk, hv, q = _pack_tiers(oracle, shape, S, bits, [], 4, 0, seed=77 * bits + S)
         (pk, pv), _, _, _ = workloads.three_tier_dense(77 * bits + S, shape, S, 0, 0)
@@ -302,7 +314,10 @@ def test_padded_key_rows_take_any_length(oracle, attn, bits):
         out = attn.fused_phasekv_decode(q2.cuda(), tiers, shape.num_q_heads).float().cpu()
         dense = attn.fused_phasekv_decode(q2.cuda(), make_tiers(segs), shape.num_q_heads).float().cpu()
         assert torch.isfinite(out).all(), S
-        slack = (ref - exact).abs().max().item()
-        assert (out - exact).abs().max().item() <= 1.2e-3, f"S={S} bits={bits}"
-        assert (out - ref).abs().max().item() <= 2e-3 + slack, f"S={S} bits={bits}"
+        e_exact, e_oracle = (out - exact).abs().max().item(), (out - ref).abs().max().item()
+        assert e_exact <= 1.5e-3, f"S={S} bits={bits}: {e_exact:.2e} from the exact attention"
+        if e_oracle > 2e-3 or e_oracle > 1e-2 * ref.abs().max().item():
+            over_the_bar.append((S, bits, e_oracle, (ref - exact).abs().max().item()))
         assert (out - dense).abs().max().item() <= 1e-3, f"S={S} bits={bits}: padded and dense rows disagree"
+    # the parity bar itself (2e-3 and 1e-2 of max|ref| against the oracle), no exception among these cases
+    assert not over_the_bar, f"(S, bits, |out - oracle|, |oracle - exact|): {over_the_bar}"

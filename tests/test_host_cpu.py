@@ -56,7 +56,39 @@ def test_library_exports_every_declared_symbol():
     L = _native.lib()
     assert L.pkv_abi_version() >= 1
     assert L.pkv_strerror(0) == b"ok" and b"bit width" in L.pkv_strerror(-1)
-    assert ctypes.sizeof(_native.Segment) == 6 * 8 + 2 * 8 + 6 * 4 + 2 * 8
+
+
+def _c_layout_of_segment(tmp_path):
+    """sizeof and field offsets of pkv_segment_t as the C compiler lays the header's struct out."""
+    import subprocess
+    fields = [name for name, _ in __import__("phasekv_b200")._native.Segment._fields_]
+    src = tmp_path / "layout.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "phasekv_b200.h"\nint main(void) {\n'
+                   '  printf("%zu", sizeof(pkv_segment_t));\n'
+                   + "".join(f'  printf(" %zu", offsetof(pkv_segment_t, {f}));\n' for f in fields)
+                   + "  return 0;\n}\n")
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    nums = [int(v) for v in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
+    return nums[0], dict(zip(fields, nums[1:]))
+
+
+def test_segment_struct_layout_matches_the_header(tmp_path):
+    """The ctypes mirror in _native.py and the stub printed in INTEGRATION.md both describe the C struct."""
+    from phasekv_b200 import _native
+    size, offsets = _c_layout_of_segment(tmp_path)
+    assert ctypes.sizeof(_native.Segment) == size
+    for name, _ in _native.Segment._fields_:
+        assert getattr(_native.Segment, name).offset == offsets[name], name
+    # the stub a maintainer would copy out of INTEGRATION.md
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    block = text[text.index("class Segment(ctypes.Structure)"):]
+    block = block[:block.index("\n\n")]
+    scope = {"ctypes": ctypes}
+    exec(block, scope)
+    stub = scope["Segment"]
+    assert ctypes.sizeof(stub) == size
+    assert [n for n, _ in stub._fields_] == [n for n, _ in _native.Segment._fields_]
 
 
 def test_abi_rejects_bad_arguments_without_touching_a_gpu():

@@ -47,7 +47,7 @@ def _rank_main(rank, world, port, tmp):
             for _ in range(4):  # slots alternate with the call parity
                 got = layer.run(q.to(dev)).float().cpu()
                 err_p2p = max(err_p2p, (got - full).abs().max().item())
-            same = bool(torch.equal(layer.out, out))
+            same = (layer.out.float() - out.float()).abs().max().item() <= 5e-4  # two merge orders of the same partials
             timed_out = ex.timed_out()
         finally:
             dist.barrier()
