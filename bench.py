@@ -191,7 +191,7 @@ def time_graph(torch, fn, steps, warmup, barrier=None, sampler=None, agree_max=N
     """Capture fn() into a CUDA graph, replay it `warmup` untimed then `steps` timed times.
     Returns the mean milliseconds per step (CUDA events on the replay stream).  When a clock
     sampler is given it runs during the timed replays and during a top-up of further untimed
-    replays (about 0.7 s of the same load), so that it reads the clocks under the load that was
+    replays (about 1.5 s of the same load), so that it reads the clocks under the load that was
     timed.  The number of top-up replays is computed from the measured step time and, when the
     step contains an exchange between ranks, agreed on across the ranks first (`agree_max`, a
     function that returns the maximum of an int over all ranks): every rank must replay a graph
@@ -220,7 +220,7 @@ def time_graph(torch, fn, steps, warmup, barrier=None, sampler=None, agree_max=N
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / steps
         if sampler is not None:
-            extra = max(0, min(20000, int(700.0 / max(ms, 1e-3)) - steps))
+            extra = max(0, min(40000, int(1500.0 / max(ms, 1e-3)) - steps))
             if agree_max is not None:
                 extra = agree_max(extra)
             for _ in range(extra):
@@ -710,9 +710,15 @@ def measure_longctx(ctx, steps, warmup, layers):
             for lay, q in zip(nccl, qs):
                 lay.run(q)
         # every rank makes the same sequence of exchange calls; a rank that fell out of step shows up here
+        def check_all_ranks(where):
+            # the verdict is shared, so that every rank leaves (or stays) together
+            if ctx.max_over_ranks([1.0 if exchange.timed_out() else 0.0])[0]:
+                raise RuntimeError(f"a peer's partial did not arrive in time ({where}); the ranks are out of step")
+        if ctx.barrier:
+            ctx.barrier()  # building the layers takes the ranks different times; the exchange waits 250 ms at most
         step(), step_nccl()
         torch.cuda.synchronize()
-        exchange.check()
+        check_all_ranks("first eager step")
         diff = max(float((a.out.float() - b.out.float()).abs().max()) for a, b in zip(p2p, nccl))
         err, ref_max = 0.0, 0.0
         if rank == 0:
@@ -721,7 +727,7 @@ def measure_longctx(ctx, steps, warmup, layers):
         clocks = ClockSampler(ctx.local_rank)
         ms = time_graph(torch, step, steps, max(warmup, 3), ctx.barrier, sampler=clocks, agree_max=ctx.agree_max)
         torch.cuda.synchronize()
-        exchange.check()
+        check_all_ranks("graph replays")
         how = "cuda graph"
         try:
             ms_nccl = time_graph(torch, step_nccl, steps, max(warmup, 3), ctx.barrier)

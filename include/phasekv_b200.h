@@ -230,7 +230,8 @@ int pkv_exchange_create(int world, int rank, int num_q_heads, int head_dim, pkv_
 int pkv_exchange_connect(pkv_exchange_t* ex, const void* handles /* host, world * 64 bytes */);
 int pkv_exchange_connect_loopback(pkv_exchange_t* ex);
 int pkv_exchange_set_spin_limit(pkv_exchange_t* ex, unsigned polls);
-/* Most microseconds one wait may take (default 50 000).  A wait ends at whichever bound it meets first. */
+/* Most microseconds one wait may take (default 250 000).  A wait ends at whichever bound it meets first.  Ranks
+ * whose set-up takes different times meet at a host barrier before their first call. */
 int pkv_exchange_set_wait_us(pkv_exchange_t* ex, unsigned microseconds);
 int pkv_exchange_status(pkv_exchange_t* ex, int* timed_out /* host; synchronises */);
 int pkv_exchange_destroy(pkv_exchange_t* ex);

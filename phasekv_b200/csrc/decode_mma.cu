@@ -137,10 +137,14 @@ struct KSrc {
     __device__ __forceinline__ void issue_impl(long long tile, int n_sub_rt, unsigned kb, int tid) const {
         const int n_sub = FULL ? C::NSUB : n_sub_rt;
         const int cpr = n_sub * (C::KRB / 16);
-        const uint8_t* src = kp + tile * C::KRB;
-        for (int idx = tid; idx < HD * cpr; idx += NTHREADS) {
-            const int row = idx / cpr, ch = idx - row * cpr;
-            cp_async16(kb + key_chunk_offset(row, ch), src + (size_t)row * nbK + 16 * ch);
+        if (FULL && kHoisted) {
+            issue_full_codes(tile, kb, tid);
+        } else {
+            const uint8_t* src = kp + tile * C::KRB;
+            for (int idx = tid; idx < HD * cpr; idx += NTHREADS) {
+                const int row = idx / cpr, ch = idx - row * cpr;
+                cp_async16(kb + key_chunk_offset(row, ch), src + (size_t)row * nbK + 16 * ch);
+            }
         }
         const long long moff = tile * (C::NG * 2);
         if (meta16) {
@@ -174,6 +178,22 @@ struct KSrc {
             tma_load_2d(kb + b * C::KBOX_BYTES, &maps->codes, (int)(tile * C::KRB) + b * C::KBOX, y, bar);
         tma_load_2d(kb + C::OFF_KS, &maps->scale, (int)(tile * C::NG), y, bar);
         tma_load_2d(kb + C::OFF_KM, &maps->mins, (int)(tile * C::NG), y, bar);
+    }
+
+    // The codes of a FULL super-tile with the addressing hoisted: the thread count is a multiple of the 16-byte chunks
+    // per row, so a thread copies the same chunk column of rows row0, row0 + RPI, ... and both addresses advance by a
+    // constant per pass (the swizzle of a chunk depends on (row >> 1) & 3, which RPI, a multiple of 8, leaves alone).
+    static constexpr int CPR = C::NSUB * (C::KRB / 16);
+    static constexpr int RPI = NTHREADS / CPR;
+    static constexpr bool kHoisted = NTHREADS % CPR == 0 && RPI % 8 == 0;
+    __device__ __forceinline__ void issue_full_codes(long long tile, unsigned kb, int tid) const {
+        const int row0 = tid / CPR, ch = tid - row0 * CPR;
+        const uint8_t* src = kp + tile * C::KRB + (size_t)row0 * nbK + 16 * ch;
+        const unsigned dst = kb + key_chunk_offset(row0, ch);
+        const size_t step = (size_t)RPI * nbK;
+#pragma unroll
+        for (int i = 0; i < (HD + RPI - 1) / RPI; ++i)
+            if (HD % RPI == 0 || row0 + RPI * i < HD) cp_async16(dst + RPI * C::KBOX * i, src + step * i);
     }
 
     __device__ __forceinline__ void issue(long long tile, int n_sub, unsigned kb, int tid) const {
@@ -517,26 +537,40 @@ __device__ __forceinline__ void finish_cta(const CtaCtx& a, WarpState& st, int k
     __syncthreads();
 
     // ---------------- merge the warps' states into one partial per CTA
+    // one thread per head: maximum, the warps' weights (kept in shared memory for the next step), denominator
     const size_t widx = a.widx;
-    for (int idx = tid; idx < 8 * HD; idx += NTHREADS) {
-        const int h = idx >> 7, dim = idx & (HD - 1);
-        if (h >= a.G) break;
+    float* s_wgt = smem_f + NWARPS * (8 * HD + 16);  // [warp][8 heads]
+    if (tid < a.G) {
+        const int h = tid;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, smem_f[w * (8 * HD + 16) + 8 * HD + h]);
-        float acc = 0.f, l = 0.f;
+        float l = 0.f;
 #pragma unroll
         for (int w = 0; w < NWARPS; ++w) {
             const float* ws = smem_f + w * (8 * HD + 16);
             const float wgt = ex2(ws[8 * HD + h] - M);
-            acc = fmaf(wgt, ws[h * HD + dim], acc);
+            s_wgt[8 * w + h] = wgt;
             l = fmaf(wgt, ws[8 * HD + 8 + h], l);
         }
-        a.pacc[(widx * a.Hq + h0 + h) * HD + dim] = acc;
-        if (dim == 0) {
-            a.pm[widx * a.Hq + h0 + h] = M * (1.0f / kLog2e);  // back to the natural-log domain
-            a.pl[widx * a.Hq + h0 + h] = l;
+        a.pm[widx * a.Hq + h0 + h] = M * (1.0f / kLog2e);  // back to the natural-log domain
+        a.pl[widx * a.Hq + h0 + h] = l;
+    }
+    __syncthreads();
+    // one thread per four dims of a head
+    for (int idx = tid; idx < a.G * (HD / 4); idx += NTHREADS) {
+        const int h = idx >> 5, d4 = idx & 31;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) {
+            const float wgt = s_wgt[8 * w + h];
+            const float4 v = *reinterpret_cast<const float4*>(smem_f + w * (8 * HD + 16) + h * HD + 4 * d4);
+            acc.x = fmaf(wgt, v.x, acc.x);
+            acc.y = fmaf(wgt, v.y, acc.y);
+            acc.z = fmaf(wgt, v.z, acc.z);
+            acc.w = fmaf(wgt, v.w, acc.w);
         }
+        *reinterpret_cast<float4*>(a.pacc + (widx * a.Hq + h0 + h) * HD + 4 * d4) = acc;
     }
 }
 
@@ -755,11 +789,11 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const
 
     // Super-tile 0 of a settled packed segment is fetched before the dependency wait.  A segment that the kernel
     // launched just before this one may have written (flagged by the caller) is read only after it.
-    const bool early = ksrc.aligned && !sg.fresh;
-    if (early) issue_first();
+    const bool early = !sg.fresh;
+    if (!early) cudaGridDependencySynchronize();
+    if (ksrc.aligned) issue_first();
     if (ktma) __syncthreads();  // the mbarriers are initialised for every thread that will wait on them
-    cudaGridDependencySynchronize();  // everything below may depend on the previous kernel of the stream
-    if (ksrc.aligned && !early) issue_first();
+    if (early) cudaGridDependencySynchronize();  // everything below may depend on the previous kernel of the stream
     // q of the GQA group, staged once per CTA behind the first copies (rows padded against bank
     // conflicts; zero rows for heads >= G)
     if (tid < 128) {

@@ -78,7 +78,7 @@ struct Cfg {
     static constexpr int SMEM_BYTES = kHeadBytes + 2 * KBUF_BYTES + NSUB * NSTAGE * VSTAGE_BYTES;
 };
 
-constexpr int kMergeBytes = NWARPS * (8 * HD + 16) * 4;  // per-warp O[8][128] + m[8] + l[8]
+constexpr int kMergeBytes = NWARPS * (8 * HD + 16) * 4 + NWARPS * 8 * 4;  // per-warp O[8][128] + m[8] + l[8], then the warps' weights
 static_assert(kMergeBytes + kHeadBytes <= kSmemBytes && Cfg<2>::SMEM_BYTES <= kSmemBytes &&
               Cfg<4>::SMEM_BYTES <= kSmemBytes && Cfg<8>::SMEM_BYTES <= kSmemBytes, "shared memory budget");
 static_assert(Cfg<2>::NG == 2 && Cfg<2>::VSTAGE_BYTES % 16 == 0, "tile geometry");

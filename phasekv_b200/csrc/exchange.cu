@@ -200,7 +200,7 @@ int pkv_exchange_create(int world, int rank, int num_q_heads, int head_dim, pkv_
     e->layout = layout_of(world, num_q_heads, head_dim);
     e->connected = false;
     e->spin_limit = 1u << 21;
-    e->wait_us = 50000;  // a rank that is 50 ms late is out of step, not slow
+    e->wait_us = 250000;  // a rank that is a quarter of a second late is out of step, not slow
     for (int r = 0; r < kMaxWorld; ++r) e->peer[r] = nullptr;
     cudaError_t err = cudaGetDevice(&e->device);
     if (err == cudaSuccess) err = cudaMalloc(reinterpret_cast<void**>(&e->local), e->layout.bytes);

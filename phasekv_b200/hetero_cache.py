@@ -20,7 +20,6 @@ from . import quant
 
 
 #: rows longer than this exceed the shared memory of the rank-counting top-k kernel
-_TOPK_KERNEL_MAX = 4096
 
 
 def cache_num_layers(cache) -> int:
@@ -96,14 +95,12 @@ def value_norm_signal(value_layer: torch.Tensor, token_slice: slice) -> torch.Te
 def topk_per_head(signal: torch.Tensor, select_k: int) -> torch.Tensor:
     """Positions (relative to the slice) of the ``select_k`` largest entries of ``signal [B, Hkv, n]`` per head,
     int64 ``[B, Hkv, min(select_k, n)]``.  They come back in ascending position order (the reference returns
-    them in score order and every consumer sorts them); ties go to the lower position."""
+    them in score order and every consumer sorts them); NaN counts as the largest value, as ``torch.topk`` has
+    it, and ties go to the lower position.  Rows of any length: short rows are ranked by counting, a whole
+    prompt's candidates per head by a radix select, both on the GPU."""
+    nv.require_cuda(signal, "signal")
     b, h, n = signal.shape
     k = max(0, min(int(select_k), n))
-    if k and (not signal.is_cuda or n > _TOPK_KERNEL_MAX):
-        # a whole prompt's candidates (tens of thousands per head) or host-resident scores: a library selection
-        # (same positions; equal scores may be ordered differently than the kernel's lower-position rule)
-        return torch.topk(signal, k=k, dim=-1).indices.long().sort(dim=-1).values
-    nv.require_cuda(signal, "signal")
     out = torch.empty((b, h, k), dtype=torch.long, device=signal.device)
     if k == 0:
         return out
@@ -114,7 +111,9 @@ def topk_per_head(signal: torch.Tensor, select_k: int) -> torch.Tensor:
 
 
 def gather_tokens(tensor: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
-    """``tensor [B, Hkv, S, hd]`` gathered along tokens at ``indices [B, Hkv, K]`` (int64) -> ``[B, Hkv, K, hd]``."""
+    """``tensor [B, Hkv, S, hd]`` gathered along tokens at ``indices [B, Hkv, K]`` (int64) -> ``[B, Hkv, K, hd]``.
+    The kernel never dereferences an index outside ``[0, S)`` (such a row comes out as zeros); callers that take
+    indices from outside validate them first (``evict_per_head``, ``PhaseKVCache.from_dense_prefill``)."""
     nv.require_cuda(tensor, "tensor")
     b, h, seq, hd = tensor.shape
     idx = indices.to(device=tensor.device, dtype=torch.long).contiguous()
@@ -139,6 +138,8 @@ def evict_per_head(cache, keep_indices: Sequence[Optional[torch.Tensor]]):
             continue
         k = cache.key_cache[layer]
         idx = torch.sort(idx.to(device=k.device, dtype=torch.long), dim=-1).values
+        if idx.numel() and (int(idx.min()) < 0 or int(idx.max()) >= k.shape[2]):
+            raise ValueError(f"layer {layer}: keep_indices must lie in [0, {k.shape[2]})")
         cache.key_cache[layer] = gather_tokens(k, idx)
         cache.value_cache[layer] = gather_tokens(cache.value_cache[layer], idx)
     return cache

@@ -129,7 +129,8 @@ class PeerExchange:
         self.nv.check(self.nv.lib().pkv_exchange_set_spin_limit(self.handle, polls))
 
     def set_wait_us(self, microseconds: int) -> None:
-        """Most microseconds a rank waits for its peers in one call (default 50 000)."""
+        """Most microseconds a rank waits for its peers in one call (default 250 000).  Ranks that prepare their
+        layers at different speeds should meet at a host barrier before the first call."""
         self.nv.check(self.nv.lib().pkv_exchange_set_wait_us(self.handle, microseconds))
 
     def check(self) -> None:

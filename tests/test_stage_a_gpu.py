@@ -64,6 +64,21 @@ def test_signal_topk_and_gather(oracle):
     # ties go to the lower position
     flat = torch.zeros(1, 1, 10, device="cuda")
     assert hc.topk_per_head(flat, 3).tolist() == [[[0, 1, 2]]]
+    # NaN ranks as the largest value (torch.topk's order) and exactly `keep` positions come back
+    nan_row = torch.tensor([[[1.0, float("nan"), 3.0, float("nan"), 2.0, -1.0]]], device="cuda")
+    assert hc.topk_per_head(nan_row, 3).tolist() == [[[1, 2, 3]]]
+    with pytest.raises(RuntimeError):
+        hc.topk_per_head(torch.zeros(1, 1, 8), 2)  # host tensors are refused: there is no CPU path
+    # a whole prompt's candidates per head (radix select): same positions as a sort, ties to the lower position
+    gen = torch.Generator().manual_seed(5)
+    long = torch.randn(2, 4, 40000, generator=gen)
+    long[0, 0, 100:4000] = 0.5          # a long run of equal scores across the selection boundary
+    long[1, 2, 17] = float("nan")
+    for keep in (1, 777, 20000, 39999):
+        got = hc.topk_per_head(long.cuda(), keep).cpu()
+        key = torch.where(torch.isnan(long), torch.full_like(long, float("inf")), long)
+        order = torch.sort(key, dim=-1, descending=True, stable=True).indices[..., :keep]
+        assert torch.equal(got, order.sort(dim=-1).values), keep
     g = hc.gather_tokens(v.cuda(), idx + 40)
     want_g = v.gather(2, (want_idx + 40).unsqueeze(-1).expand(2, 4, 32, 128))
     assert torch.equal(g.cpu(), want_g)
