@@ -97,7 +97,8 @@ typedef struct pkv_segment {
     const void* v_scale;
     const void* v_mins;
     int64_t seq_len;     /* S: tokens in this segment (> 0) */
-    int64_t head_stride; /* PKV_SEG_FP16 only: elements between consecutive KV heads */
+    int64_t head_stride; /* PKV_SEG_FP16: elements between consecutive KV heads.  PKV_SEG_KIVI: token rows between
+                            consecutive KV heads of v_packed / v_scale / v_mins (0 = seq_len, i.e. dense) */
     int32_t kind;        /* PKV_SEG_* */
     int32_t k_bits, v_bits;   /* 2, 4 or 8 (ignored for PKV_SEG_FP16) */
     int32_t k_group, v_group; /* quantisation group sizes (after clamping to the axis length) */
@@ -107,7 +108,13 @@ typedef struct pkv_segment {
     int64_t k_row_pitch;
     int64_t k_meta_pitch;
     int32_t flags;    /* PKV_SEG_FLAG_* */
-    int32_t reserved; /* 0 */
+    /* PKV_SEG_KIVI only; 0 = every token counts.  Otherwise the segment is a run of equal slots of slot_tokens
+     * tokens (32 or 64) of which only the first slot_valid hold tokens; the rest of a slot is padding that the
+     * kernels mask out.  This is how a run of small cold segments (one per cooling step, each quantised on its own)
+     * is presented as ONE segment: every step's tokens sit at the start of a slot whose key group is the step's
+     * own group (see pkv_cold_select_pack_layers). */
+    int16_t slot_tokens;
+    int16_t slot_valid;
 } pkv_segment_t;
 
 /* The packed tensors of this segment may have been written by the kernel that was launched on `stream` directly
@@ -255,6 +262,33 @@ int pkv_cold_select_pack(void* hot_k, void* hot_v, int64_t rows, int64_t capacit
                          int64_t hot_len, int64_t aged, int64_t keep, int bits, int64_t group,
                          uint8_t* k_packed, void* k_scale, void* k_mins, uint8_t* v_packed,
                          void* v_scale, void* v_mins, int64_t* indices, pkv_stream_t stream);
+
+/* The same for every layer of a model in ONE launch, writing into pre-allocated arenas (no counterpart in the
+ * reference, which cools layer by layer with ~50 torch launches each, phasekv_cache.py:322-340).  `layers` is a
+ * DEVICE array of n_layers entries holding each layer's hot buffers and the BASE pointers of its outputs (it stays
+ * valid across calls while the buffers do); all layers share rows, capacity, hot_len, aged, keep.  The outputs of
+ * this call start slot_k_bytes bytes into every row of k_packed, slot_k_groups elements into every row of
+ * k_scale / k_mins, and slot_v_tokens token rows into every (batch, head) block of the value outputs; rows of
+ * k_packed are k_row_pitch bytes apart, rows of k_scale / k_mins k_meta_pitch elements, (batch, head) blocks of the
+ * value outputs v_row_tokens token rows.  With slots of ceil(keep / group) * group tokens, zero-initialised arenas
+ * and one group per `group` tokens, the arena of a layer is one PKV_SEG_KIVI segment with slot_tokens / slot_valid
+ * set, and each step's part of it is bit-identical to what pkv_cold_select_pack writes into tensors of its own. */
+typedef struct pkv_cold_layer {
+    void* hot_k;
+    void* hot_v;
+    uint8_t* k_packed;
+    void* k_scale;
+    void* k_mins;
+    uint8_t* v_packed;
+    void* v_scale;
+    void* v_mins;
+    int64_t* indices; /* [rows, keep] of this call, may be NULL */
+} pkv_cold_layer_t;
+int pkv_cold_select_pack_layers(const pkv_cold_layer_t* layers /* device */, int n_layers, int64_t rows,
+                                int64_t capacity, int head_dim, int64_t hot_len, int64_t aged, int64_t keep,
+                                int bits, int64_t group, int64_t k_row_pitch, int64_t k_meta_pitch,
+                                int64_t v_row_tokens, int64_t slot_k_bytes, int64_t slot_k_groups,
+                                int64_t slot_v_tokens, pkv_stream_t stream);
 
 /* ---------------------------------------------------------------- stage A (dense cache) -------- */
 

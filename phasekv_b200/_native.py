@@ -30,8 +30,15 @@ class Segment(ctypes.Structure):
         ("kind", ctypes.c_int32), ("k_bits", ctypes.c_int32), ("v_bits", ctypes.c_int32),
         ("k_group", ctypes.c_int32), ("v_group", ctypes.c_int32), ("num_splits", ctypes.c_int32),
         ("k_row_pitch", ctypes.c_int64), ("k_meta_pitch", ctypes.c_int64),
-        ("flags", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("flags", ctypes.c_int32), ("slot_tokens", ctypes.c_int16), ("slot_valid", ctypes.c_int16),
     ]
+
+
+class ColdLayer(ctypes.Structure):
+    """``pkv_cold_layer_t``: one layer's hot buffers and the base pointers of its cooling outputs."""
+
+    _fields_ = [(name, ctypes.c_void_p) for name in ("hot_k", "hot_v", "k_packed", "k_scale", "k_mins",
+                                                       "v_packed", "v_scale", "v_mins", "indices")]
 
 
 class NativeError(RuntimeError):
@@ -84,6 +91,8 @@ _SIGNATURES = {
     "pkv_gather_tokens": ([_VP, _VP, _VP, _I64, _I64, _I64, _I64, _VP], _I32),
     "pkv_cold_select_pack": ([_VP, _VP, _I64, _I64, _I32, _I64, _I64, _I64, _I32, _I64,
                               _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP], _I32),
+    "pkv_cold_select_pack_layers": ([_VP, _I32, _I64, _I64, _I32, _I64, _I64, _I64, _I32, _I64, _I64, _I64, _I64,
+                                     _I64, _I64, _I64, _VP], _I32),
 }
 
 #: every symbol include/phasekv_b200.h declares

@@ -56,15 +56,43 @@ __device__ __forceinline__ int gcd_i(int a, int b) {
     return a;
 }
 
+// Where one layer's cooling step reads and writes.  The outputs may be dense tensors of their own or a slot of a
+// pre-allocated arena: rows of the key outputs are k_pitch bytes / k_meta_pitch elements apart, the value
+// outputs of consecutive (batch, head) rows are v_row_tokens token rows apart.
+struct ColdLayer {
+    __half* hot_k;
+    __half* hot_v;
+    uint8_t* k_packed;
+    __half* k_scale;
+    __half* k_mins;
+    uint8_t* v_packed;
+    __half* v_scale;
+    __half* v_mins;
+    long long* indices;
+};
+static_assert(sizeof(ColdLayer) == sizeof(pkv_cold_layer_t), "the device table is an array of pkv_cold_layer_t");
+
+// Grid (rows, layers): every layer of a model cools in the same launch (all layers hold the same number of hot
+// tokens).  `slot_*`: byte / element / token-row offsets of this event's slot inside the layers' arenas, added to
+// the table's base pointers (zero for dense outputs).
 template <int BITS>
 __global__ void __launch_bounds__(kColdThreads)
-cold_select_pack_kernel(__half* __restrict__ hot_k, __half* __restrict__ hot_v, int capacity, int hd,
-                        int hot_len, int aged, int keep, int gs_k, int gs_v,
-                        uint8_t* __restrict__ k_packed, __half* __restrict__ k_scale,
-                        __half* __restrict__ k_mins, uint8_t* __restrict__ v_packed,
-                        __half* __restrict__ v_scale, __half* __restrict__ v_mins,
-                        long long* __restrict__ indices) {
+cold_select_pack_kernel(const ColdLayer* __restrict__ layers, const ColdLayer single, int capacity, int hd,
+                        int hot_len, int aged, int keep, int gs_k, int gs_v, long long k_pitch,
+                        long long k_meta_pitch, long long v_row_tokens, long long slot_k_bytes,
+                        long long slot_k_groups, long long slot_v_tokens) {
     constexpr int VPB = 8 / BITS;
+    const ColdLayer L = layers != nullptr ? layers[blockIdx.y] : single;  // one layer travels in the parameters
+    __half* const hot_k = L.hot_k;
+    __half* const hot_v = L.hot_v;
+    long long* const indices = L.indices;
+    const int v_nb = (hd + VPB - 1) / VPB, v_ng = (hd + gs_v - 1) / gs_v;
+    uint8_t* const k_packed = L.k_packed + slot_k_bytes;
+    __half* const k_scale = L.k_scale + slot_k_groups;
+    __half* const k_mins = L.k_mins + slot_k_groups;
+    uint8_t* const v_packed = L.v_packed + slot_v_tokens * v_nb;
+    __half* const v_scale = L.v_scale + slot_v_tokens * v_ng;
+    __half* const v_mins = L.v_mins + slot_v_tokens * v_ng;
     __shared__ float n2[kMaxAged];
     __shared__ int sel[kMaxAged];
     __shared__ int warp_tot[kColdThreads / 32];
@@ -133,23 +161,22 @@ cold_select_pack_kernel(__half* __restrict__ hot_k, __half* __restrict__ hot_v, 
             const __half* src = hv + (size_t)sel[p] * hd;
             auto load = [&](int a) { return __half2float(src[a]); };
             quantize_run<BITS>(load, r * unit, min(hd, (r + 1) * unit), hd, gs_v,
-                               v_packed + ((size_t)row * keep + p) * nb,
-                               v_scale + ((size_t)row * keep + p) * ng,
-                               v_mins + ((size_t)row * keep + p) * ng);
+                               v_packed + ((size_t)row * v_row_tokens + p) * nb,
+                               v_scale + ((size_t)row * v_row_tokens + p) * ng,
+                               v_mins + ((size_t)row * v_row_tokens + p) * ng);
         }
     }
     // 4. K: per channel, groups along the kept tokens
     {
-        const int nb = (keep + VPB - 1) / VPB, ng = (keep + gs_k - 1) / gs_k;
         const int unit = gs_k / gcd_i(gs_k, VPB) * VPB;
         const int runs = (keep + unit - 1) / unit;
         for (int i = tid; i < hd * runs; i += kColdThreads) {
             const int d = i % hd, r = i / hd;
             auto load = [&](int a) { return __half2float(hk[(size_t)sel[a] * hd + d]); };
             quantize_run<BITS>(load, r * unit, min(keep, (r + 1) * unit), keep, gs_k,
-                               k_packed + ((size_t)row * hd + d) * nb,
-                               k_scale + ((size_t)row * hd + d) * ng,
-                               k_mins + ((size_t)row * hd + d) * ng);
+                               k_packed + ((size_t)row * hd + d) * k_pitch,
+                               k_scale + ((size_t)row * hd + d) * k_meta_pitch,
+                               k_mins + ((size_t)row * hd + d) * k_meta_pitch);
         }
     }
     __syncthreads();
@@ -199,6 +226,54 @@ cold_select_pack_kernel(__half* __restrict__ hot_k, __half* __restrict__ hot_v, 
 
 using namespace pkv;
 
+namespace {
+int launch_cold(const ColdLayer* table_dev, const ColdLayer& single, int n_layers, int64_t rows, int64_t capacity, int head_dim, int64_t hot_len,
+                int64_t aged, int64_t keep, int bits, int64_t group, int64_t k_pitch, int64_t k_meta_pitch,
+                int64_t v_row_tokens, int64_t slot_k_bytes, int64_t slot_k_groups, int64_t slot_v_tokens,
+                cudaStream_t s) {
+    const int gs_k = (int)std::min<int64_t>(group, keep), gs_v = (int)std::min<int64_t>(group, head_dim);
+    const dim3 grid((unsigned)rows, (unsigned)n_layers);
+#define PKV_COLD_LAUNCH(B)                                                                                     \
+    cold_select_pack_kernel<B><<<grid, kColdThreads, 0, s>>>(table_dev, single, (int)capacity, head_dim, (int)hot_len, \
+                                                             (int)aged, (int)keep, gs_k, gs_v, k_pitch, k_meta_pitch, \
+                                                             v_row_tokens, slot_k_bytes, slot_k_groups, slot_v_tokens)
+    if (bits == 2) PKV_COLD_LAUNCH(2);
+    else if (bits == 4) PKV_COLD_LAUNCH(4);
+    else PKV_COLD_LAUNCH(8);
+#undef PKV_COLD_LAUNCH
+    PKV_LAUNCH_CHECK();
+    return PKV_OK;
+}
+
+int check_cold(int64_t rows, int64_t capacity, int head_dim, int64_t hot_len, int64_t aged, int64_t keep, int bits,
+               int64_t group) {
+    if (!valid_bits(bits)) return PKV_E_BITS;
+    if (rows <= 0 || head_dim <= 0 || group <= 0 || aged <= 0 || keep <= 0 || keep > aged ||
+        aged > hot_len || hot_len > capacity)
+        return PKV_E_SHAPE;
+    if (aged > kMaxAged || capacity * (int64_t)head_dim > INT32_MAX || rows > 65535) return PKV_E_LIMIT;
+    return PKV_OK;
+}
+}  // namespace
+
+extern "C" int pkv_cold_select_pack_layers(const pkv_cold_layer_t* layers /* device */, int n_layers, int64_t rows,
+                                           int64_t capacity, int head_dim, int64_t hot_len, int64_t aged, int64_t keep,
+                                           int bits, int64_t group, int64_t k_row_pitch, int64_t k_meta_pitch,
+                                           int64_t v_row_tokens, int64_t slot_k_bytes, int64_t slot_k_groups,
+                                           int64_t slot_v_tokens, pkv_stream_t stream) {
+    const int rc = check_cold(rows, capacity, head_dim, hot_len, aged, keep, bits, group);
+    if (rc != PKV_OK) return rc;
+    if (!layers) return PKV_E_NULL;
+    if (n_layers <= 0 || n_layers > 65535) return PKV_E_LIMIT;
+    const int64_t gs_k = std::min<int64_t>(group, keep);
+    if (k_row_pitch < ceil_div(keep * bits, 8) || k_meta_pitch < ceil_div(keep, gs_k) || v_row_tokens < keep ||
+        slot_k_bytes < 0 || slot_k_groups < 0 || slot_v_tokens < 0)
+        return PKV_E_SHAPE;
+    return launch_cold(reinterpret_cast<const ColdLayer*>(layers), ColdLayer{}, n_layers, rows, capacity, head_dim, hot_len, aged,
+                       keep, bits, group, k_row_pitch, k_meta_pitch, v_row_tokens, slot_k_bytes, slot_k_groups,
+                       slot_v_tokens, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int pkv_cold_select_pack(void* hot_k, void* hot_v, int64_t rows, int64_t capacity, int head_dim,
                                     int64_t hot_len, int64_t aged, int64_t keep, int bits, int64_t group,
                                     uint8_t* k_packed, void* k_scale, void* k_mins, uint8_t* v_packed,
@@ -210,18 +285,11 @@ extern "C" int pkv_cold_select_pack(void* hot_k, void* hot_v, int64_t rows, int6
     if (aged > kMaxAged || capacity * (int64_t)head_dim > INT32_MAX) return PKV_E_LIMIT;
     if (!hot_k || !hot_v || !k_packed || !k_scale || !k_mins || !v_packed || !v_scale || !v_mins)
         return PKV_E_NULL;
-    const int gs_k = (int)std::min<int64_t>(group, keep), gs_v = (int)std::min<int64_t>(group, head_dim);
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-#define PKV_COLD_LAUNCH(B)                                                                            \
-    cold_select_pack_kernel<B><<<(unsigned)rows, kColdThreads, 0, s>>>(                               \
-        static_cast<__half*>(hot_k), static_cast<__half*>(hot_v), (int)capacity, head_dim, (int)hot_len, \
-        (int)aged, (int)keep, gs_k, gs_v, k_packed, static_cast<__half*>(k_scale),                     \
-        static_cast<__half*>(k_mins), v_packed, static_cast<__half*>(v_scale),                         \
-        static_cast<__half*>(v_mins), reinterpret_cast<long long*>(indices))
-    if (bits == 2) PKV_COLD_LAUNCH(2);
-    else if (bits == 4) PKV_COLD_LAUNCH(4);
-    else PKV_COLD_LAUNCH(8);
-#undef PKV_COLD_LAUNCH
-    PKV_LAUNCH_CHECK();
-    return PKV_OK;
+    // one layer, dense outputs
+    const int64_t gs_k = std::min<int64_t>(group, keep);
+    ColdLayer one = {static_cast<__half*>(hot_k), static_cast<__half*>(hot_v), k_packed, static_cast<__half*>(k_scale),
+                     static_cast<__half*>(k_mins), v_packed, static_cast<__half*>(v_scale), static_cast<__half*>(v_mins),
+                     reinterpret_cast<long long*>(indices)};
+    return launch_cold(nullptr, one, 1, rows, capacity, head_dim, hot_len, aged, keep, bits, group,
+                       ceil_div(keep * bits, 8), ceil_div(keep, gs_k), keep, 0, 0, 0, static_cast<cudaStream_t>(stream));
 }

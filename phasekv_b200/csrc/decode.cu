@@ -91,7 +91,8 @@ decode_generic_kernel(const __grid_constant__ DecodeArgs a) {
         float dot[GMAX];
 #pragma unroll
         for (int h = 0; h < GMAX; ++h) dot[h] = 0.f;
-        if (n < t1) {
+        const bool counts = n < t1 && (sg.slot_tokens == 0 || (int)(n % sg.slot_tokens) < sg.slot_valid);
+        if (counts) {
             if (sg.kind == PKV_SEG_KIVI) {
                 const long long nbK = sg.k_pitch, ngK = sg.km_pitch;
                 const uint8_t* kp = sg.kp + (size_t)kvh * hd * nbK + n / kvpb;
@@ -125,7 +126,7 @@ decode_generic_kernel(const __grid_constant__ DecodeArgs a) {
             }
         }
 #pragma unroll
-        for (int h = 0; h < GMAX; ++h) p_s[h * kChunk + tid] = n < t1 ? dot[h] : -INFINITY;
+        for (int h = 0; h < GMAX; ++h) p_s[h * kChunk + tid] = counts ? dot[h] : -INFINITY;
         __syncthreads();
 
         // ---- phase 2: online softmax bookkeeping, one warp per head
@@ -174,9 +175,10 @@ decode_generic_kernel(const __grid_constant__ DecodeArgs a) {
                     }
                 } else {
                     const long long nbV = ceil_div(hd, vvpb), ngV = ceil_div(hd, sg.vgs);
-                    const uint8_t* vp = sg.vp + ((size_t)kvh * S + c0) * nbV + d / vvpb;
-                    const __half* vs = sg.vs + ((size_t)kvh * S + c0) * ngV + d / sg.vgs;
-                    const __half* vm = sg.vm + ((size_t)kvh * S + c0) * ngV + d / sg.vgs;
+                    const size_t vrow = sg.kind == PKV_SEG_KIVI ? (size_t)kvh * sg.v_head_tokens + c0 : (size_t)kvh * S + c0;
+                    const uint8_t* vp = sg.vp + vrow * nbV + d / vvpb;
+                    const __half* vs = sg.vs + vrow * ngV + d / sg.vgs;
+                    const __half* vm = sg.vm + vrow * ngV + d / sg.vgs;
                     const unsigned pos = (unsigned)(d % vvpb);
                     for (int i = 0; i < nvalid; ++i) {
                         const float c = (float)extract_code_rt(vp[(size_t)i * nbV], pos, sg.vbits);
@@ -236,6 +238,15 @@ int check_segments(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int h
         if (!valid_bits(s.k_bits) || !valid_bits(s.v_bits)) return PKV_E_BITS;
         if (s.k_group <= 0 || s.v_group <= 0) return PKV_E_LAYOUT;
         if (!s.k_scale || !s.k_mins || !s.v_scale || !s.v_mins) return PKV_E_NULL;
+        if (s.slot_tokens || s.slot_valid || (s.kind != PKV_SEG_FP16 && s.head_stride)) {
+            if (s.kind != PKV_SEG_KIVI) return PKV_E_LAYOUT;
+            if (s.slot_tokens || s.slot_valid) {
+                if ((s.slot_tokens != 32 && s.slot_tokens != 64) || s.slot_valid <= 0 || s.slot_valid > s.slot_tokens ||
+                    s.k_group != 32 || s.seq_len % s.slot_tokens)
+                    return PKV_E_LAYOUT;
+            }
+            if (s.head_stride && s.head_stride < s.seq_len) return PKV_E_SHAPE;
+        }
         if (s.k_row_pitch || s.k_meta_pitch) {
             if (s.kind != PKV_SEG_KIVI) return PKV_E_LAYOUT;
             if ((s.k_row_pitch && s.k_row_pitch < ceil_div(s.seq_len * s.k_bits, 8)) ||
@@ -270,9 +281,13 @@ static SegDev seg_dev_of(const pkv_segment_t& s) {
     d.vbits = s.kind == PKV_SEG_FP16 ? 8 : s.v_bits;
     d.kgs = s.kind == PKV_SEG_FP16 ? 1 : s.k_group;
     d.vgs = s.kind == PKV_SEG_FP16 ? 1 : s.v_group;
+    d.v_head_tokens = s.seq_len;
     if (s.kind == PKV_SEG_KIVI) {
         d.k_pitch = s.k_row_pitch ? s.k_row_pitch : ceil_div(s.seq_len * s.k_bits, 8);
         d.km_pitch = s.k_meta_pitch ? s.k_meta_pitch : ceil_div(s.seq_len, s.k_group);
+        if (s.head_stride) d.v_head_tokens = s.head_stride;
+        d.slot_tokens = s.slot_tokens;
+        d.slot_valid = s.slot_valid;
     }
     return d;
 }

@@ -216,12 +216,12 @@ struct VSrc {
     bool meta16;  // this head's scale rows start on 16 bytes
 
     __device__ VSrc(const SegDev& sg, int kvh, int lane_) : lane(lane_) {
-        meta16 = (((long long)kvh * sg.S) & 1) == 0;
-        vc = sg.vp + (size_t)kvh * sg.S * (C::VWPT * 4) + 16 * lane;
+        meta16 = (((long long)kvh * sg.v_head_tokens) & 1) == 0;
+        vc = sg.vp + (size_t)kvh * sg.v_head_tokens * (C::VWPT * 4) + 16 * lane;
         const int lt = lane / CPT;
         d_vc = (lt + lt / 8) * (C::VWPT * 4) + 16 * (lane % CPT);
-        vs = reinterpret_cast<const char*>(sg.vs + (size_t)kvh * sg.S * 4) + 16 * lane;
-        vm = reinterpret_cast<const char*>(sg.vm + (size_t)kvh * sg.S * 4) + 16 * lane;
+        vs = reinterpret_cast<const char*>(sg.vs + (size_t)kvh * sg.v_head_tokens * 4) + 16 * lane;
+        vm = reinterpret_cast<const char*>(sg.vm + (size_t)kvh * sg.v_head_tokens * 4) + 16 * lane;
     }
 
     // values of one tile into the stage at `sa`; one warp.  Rows of tokens >= n_valid are zero-filled
@@ -301,7 +301,7 @@ __device__ __forceinline__ unsigned residual_steps(const char* kb, int sub, cons
 template <int BITS, int NGRP = 2>
 __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char* sa, const char* q_lane, float c_qk,
                                              WarpState& st, const LaneSel<BITS>& ls, int lane, int n_valid,
-                                             const char* qabs, int g_off = 0) {
+                                             const char* qabs, int slot, int g_off = 0) {
     using C = Cfg<BITS>;
     static_assert(C::NG == 2 && (NGRP == 1 || NGRP == 2), "a tile is two key groups");
     const int g = lane >> 2, t = lane & 3;
@@ -394,6 +394,11 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
                 const int tok = 32 * G + 4 * g + 2 * j;
                 if (tok >= n_valid) s[0] = s[1] = -INFINITY;
                 if (tok + 1 >= n_valid) s[2] = s[3] = -INFINITY;
+            }
+            if (slot) {  // a run of padded slots: only the first (slot >> 8) tokens of every (slot & 255) count
+                const int in_slot = (32 * G + 4 * g + 2 * j) & ((slot & 255) - 1);
+                if (in_slot >= (slot >> 8)) s[0] = s[1] = -INFINITY;
+                if (in_slot + 1 >= (slot >> 8)) s[2] = s[3] = -INFINITY;
             }
             mx[0] = fmaxf(mx[0], fmaxf(s[0], s[2]));
             mx[1] = fmaxf(mx[1], fmaxf(s[1], s[3]));
@@ -816,6 +821,7 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const
     cudaTriggerProgrammaticLaunchCompletion();
     const LaneSel<BITS> ls(g);
     const float c_qk = a.sm_scale * kLog2e;
+    const int slot = sg.slot_tokens ? (sg.slot_valid << 8) | sg.slot_tokens : 0;
     for (int sp = 0; sp < n_super; ++sp) {
         const int n_sub = sp_count(sp);
         const long long first = sp_first(sp);
@@ -856,11 +862,11 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const
                 const int nv = valid_of(first + sub);
                 if (32 * half < nv)  // a group without a single token contributes nothing
                     compute_tile<BITS, 1>(kb_c, sub, v0_c + sub * (NSTAGE * C::VSTAGE_BYTES), q_c, c_qk, st, ls, lane,
-                                          nv, qabs_c, half);
+                                          nv, qabs_c, slot, half);
             }
         } else if (wid < n_sub) {
             compute_tile<BITS>(kb_c, wid, v0_c + wid * (NSTAGE * C::VSTAGE_BYTES), q_c, c_qk, st, ls, lane,
-                               valid_of(first + wid), qabs_c);
+                               valid_of(first + wid), qabs_c, slot);
         }
     }
     if (ktma) {

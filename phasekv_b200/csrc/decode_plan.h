@@ -30,6 +30,8 @@ struct SegDev {
     int key_tma;     // 1 + index of this segment's key tensor maps in the launch parameters, 0 = none
     int fresh;       // the kernel launched just before may have written the segment: read it only after the
                      // stream dependency is resolved
+    int slot_tokens, slot_valid;  // KIVI: only the first slot_valid tokens of every slot_tokens count (0 = all)
+    long long v_head_tokens;      // KIVI: token rows between KV heads of the value arrays
 };
 
 // Segments are routed to one of two kernels: the tensor-core kernel (`fast`, split_len counts

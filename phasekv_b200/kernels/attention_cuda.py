@@ -298,15 +298,38 @@ def _cached_packed_segment(segment, num_splits: Optional[int]):
     return seg, keep, shape
 
 
-def layer_segments(tiers, num_splits: Optional[int] = None):
-    """Segment descriptors for every tier of a ``LayerTiers`` (batch 1), in prompt, extensions,
-    cold, hot order, plus the tensors that must stay alive while they are in use."""
+def _cold_descriptors(cold: Sequence, num_splits: Optional[int]):
+    """Descriptors of the cold tier.  Consecutive cooling steps that are the slots 0..k-1 of one arena the
+    tensor-core kernel can read (``ColdArena.decode_ready``) become ONE descriptor over the arena; every other
+    step gets its own.  Yields ``(descriptor, tensors to keep alive, origin, (Hkv, hd))`` where ``origin`` is the
+    arena or the segment object."""
+    i = 0
+    while i < len(cold):
+        arena = getattr(cold[i], "_arena", None)
+        if arena is not None and arena.decode_ready and getattr(cold[i], "_arena_event", -1) == 0:
+            k = 1
+            while (i + k < len(cold) and getattr(cold[i + k], "_arena", None) is arena
+                   and cold[i + k]._arena_event == k):
+                k += 1
+            if k == arena.events:
+                yield arena.descriptor(), list(arena.tensors()), arena, (arena.shape[1], arena.shape[2])
+                i += k
+                continue
+        s, kp, shape = _cached_packed_segment(cold[i], num_splits)
+        yield s, kp, cold[i], shape
+        i += 1
+
+
+def _layer_descriptors(tiers, num_splits: Optional[int] = None):
     segs: List[nv.Segment] = []
     keep: list = []
+    origins: list = []
     hkv = hd = None
-    for segment in [tiers.prompt, *tiers.prompt_extensions, *tiers.cold]:
+    for segment in [tiers.prompt, *tiers.prompt_extensions]:
         s, kp, (hkv, hd) = _cached_packed_segment(segment, num_splits)
-        segs.append(s), keep.append(kp)
+        segs.append(s), keep.append(kp), origins.append(segment)
+    for s, kp, origin, (hkv, hd) in _cold_descriptors(tiers.cold, num_splits):
+        segs.append(s), keep.append(kp), origins.append(origin)
     if tiers.hot_len:
         hot_k, hot_v = tiers.hot_views()
         if hot_k.shape[0] != 1:
@@ -314,7 +337,31 @@ def layer_segments(tiers, num_splits: Optional[int] = None):
         s, kp = _fp16_segment(hot_k[0], hot_v[0])
         segs.append(s), keep.extend(kp)
         hkv, hd = hot_k.shape[1], hot_k.shape[3]
-    return segs, keep, hkv, hd
+    return segs, keep, hkv, hd, origins
+
+
+def layer_segments(tiers, num_splits: Optional[int] = None):
+    """Segment descriptors for every tier of a ``LayerTiers`` (batch 1), in prompt, extensions,
+    cold, hot order, plus the tensors that must stay alive while they are in use."""
+    return _layer_descriptors(tiers, num_splits)[:4]
+
+
+def _unread(origin) -> bool:
+    """Whether a packed segment may still be being written by the kernel enqueued just before a decode launch:
+    a segment object no decode launch has read yet, or an arena with a slot filled since its last launch."""
+    if hasattr(origin, "launched_events"):
+        return origin.events > origin.launched_events
+    return not getattr(origin, "_pkv_seen", False)
+
+
+def _mark_read(origin) -> None:
+    if hasattr(origin, "launched_events"):
+        origin.launched_events = origin.events
+        return
+    try:
+        origin._pkv_seen = True
+    except AttributeError:
+        pass
 
 
 def fused_phasekv_decode(q: torch.Tensor, tiers, num_attention_heads: int,
@@ -333,14 +380,13 @@ def fused_phasekv_decode(q: torch.Tensor, tiers, num_attention_heads: int,
     cached = getattr(tiers, "_pkv_call", None)
     fresh = ()
     if cached is None or cached[0] != tag:
-        segs, keep, hkv, hd = layer_segments(tiers, num_splits)
+        segs, keep, hkv, hd, origins = _layer_descriptors(tiers, num_splits)
         arr, n, need = _prepare_call(segs, num_attention_heads, hkv, hd, q.device)
         # A packed segment this entry point has not launched over yet may have been written by the kernel that
         # was enqueued just before this call (prefill packing, a cooling step): its first launch must not read
         # it ahead of the stream dependency.  From the second launch on it is settled.
-        packed = (tiers.prompt, *tiers.prompt_extensions, *tiers.cold)
-        fresh = [i for i, sg in enumerate(packed) if not getattr(sg, "_pkv_seen", False)]
-        for i in fresh:
+        fresh = [(i, o) for i, o in enumerate(origins) if _unread(o)]
+        for i, _ in fresh:
             arr[i].flags |= nv.PKV_SEG_FLAG_FRESH
         cached = [tag, arr, n, need, keep, hkv, hd, tiers.hot_len]
         # reusable only if the hot descriptor points into the caller's own buffers (a strided hot buffer is
@@ -365,14 +411,9 @@ def fused_phasekv_decode(q: torch.Tensor, tiers, num_attention_heads: int,
     plan_kivi_decode(max(1, tiers.prompt.length), num_attention_heads, hd, _device_sm_count(q.device),
                      num_splits, block_n, num_warps)
     out, _ = _launch_decode(q, arr, n, need, hkv, True, False)
-    if fresh:
-        packed = (tiers.prompt, *tiers.prompt_extensions, *tiers.cold)
-        for i in fresh:
-            arr[i].flags &= ~nv.PKV_SEG_FLAG_FRESH
-            try:
-                packed[i]._pkv_seen = True
-            except AttributeError:
-                pass
+    for i, origin in fresh:
+        arr[i].flags &= ~nv.PKV_SEG_FLAG_FRESH
+        _mark_read(origin)
     return out
 
 # --------------------------------------------------------------------------- batched serving

@@ -147,3 +147,52 @@ def test_decode_tier_and_prompt_tier_lifecycle_against_a_cpu_restatement(oracle)
         assert torch.equal(gpu.key_cache[l].cpu(), cpu.key_cache[l]), l
         assert torch.equal(gpu.value_cache[l].cpu(), cpu.value_cache[l]), l
     assert st_gpu.logical_bytes(gpu) == st_cpu.logical_bytes(cpu) > 0
+
+
+def test_prompt_selection_matches_the_reference():
+    """prompt_tier.select_prompt_indices on seeded causal attention matrices: the kept positions per layer and
+    head are the reference's (prompt_tier.py:24-75), including short prompts where sinks and the recent window
+    fill the budget.  The vectors were made by the reference's own function."""
+    import os
+    import types
+
+    import numpy as np
+
+    from phasekv_b200 import hetero_cache as hc
+    from phasekv_b200 import prompt_tier
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "prompt_select.npz"))
+    ties = 0
+    for i in range(int(z["n_cases"][0])):
+        plen, hq, hkv, layers, batch, sink, obs, kernel, avg = (int(v) for v in z[f"c{i}.args"])
+        atts = [torch.from_numpy(a).cuda() for a in z[f"c{i}.att"]]
+        cfg = types.SimpleNamespace(num_key_value_heads=hkv, num_attention_heads=hq)
+        keep = prompt_tier.select_prompt_indices(
+            atts, prompt_len=plen, model_config=cfg, prefill_keep_ratio=float(z[f"c{i}.ratio"][0]), sink_tokens=sink,
+            obs_window=obs, pool_kernel=kernel, pooling="avgpool" if avg else "maxpool")
+        want = torch.from_numpy(z[f"c{i}.keep"])
+        assert len(keep) == layers
+        for l in range(layers):
+            got = keep[l].cpu()
+            assert keep[l].dtype == torch.long and got.shape == want[l].shape
+            assert bool((got[..., 1:] > got[..., :-1]).all())
+            if torch.equal(got, want[l]):
+                continue
+            # Max-pooled votes of neighbouring positions are often EQUAL, and which of several equal votes fills the
+            # last places is not defined by the reference (it is whatever torch.topk does on the device at hand).
+            # Here equal votes go to the lowest position.  The two selections must then hold the same votes:
+            ratio = float(z[f"c{i}.ratio"][0])
+            budget = min(plen, max(1, min(sink, plen), round(plen * ratio)))
+            first = min(sink, plen, budget)                                  # candidates: behind the sinks ...
+            last = plen - min(obs, budget - first, plen - first)             # ... and before the recent window
+            votes = hc.pool_scores(hc.observation_votes(atts[l], hkv, min(obs, plen))[..., first:last], kernel,
+                                   "avgpool" if avg else "maxpool").cpu()
+
+            def chosen_votes(idx):
+                inside = (idx >= first) & (idx < last)
+                per_head = budget - first - (plen - last)
+                assert bool((inside.sum(-1) == per_head).all())
+                picked = votes.gather(-1, (idx - first).clamp(0, last - first - 1))[inside]
+                return picked.view(*idx.shape[:2], per_head).sort(-1).values
+            ties += 1
+            assert torch.equal(chosen_votes(got), chosen_votes(want[l])), (i, l)
+    assert ties <= 4
