@@ -192,6 +192,19 @@ int pkv_decode_attention_batched(const void* q, const void* table_host, const vo
                                  float sm_scale, void* workspace, size_t workspace_bytes, void* out,
                                  pkv_stream_t stream);
 
+/* A chunk of new prompt tokens in one launch pair.  The reference attends to a chunk of N input tokens with N
+ * consecutive single-query calls, each after appending that token's K/V (qwen2_attention.py:99-106: "write one,
+ * compute one"), so that no query sees a later token of its chunk.  Here all N tokens are written to the
+ * float16 tier first and the causal rule is applied by length: `segs` describes the layer as for
+ * pkv_decode_attention, its LAST segment being the float16 tier INCLUDING the N new tokens at its end; query i
+ * (0-based) attends to all other segments in full and to the first seq_len - (N - 1 - i) float16 tokens.
+ * The plan is a pkv_decode_batch_plan table with one entry per query: run it with
+ * pkv_decode_attention_batched on q float16 [N, Hq, hd] -> out float16 [N, Hq, hd].  Same layout rules and
+ * errors as pkv_decode_batch_plan; PKV_E_SHAPE if the last segment is not float16 or shorter than the chunk. */
+int pkv_decode_chunk_plan(const pkv_segment_t* segs /* host */, int n_segments, int chunk_len, int num_q_heads,
+                          int num_kv_heads, int head_dim, int sm_count, void* table /* host, may be NULL */,
+                          size_t table_capacity, size_t* table_bytes, size_t* workspace_bytes);
+
 /* attention_triton.py:257-266 _reduce_splits and :300-307 _merge_partials:
  * m, l float32 [n_parts, Hq] and acc float32 [n_parts, Hq, hd] (contiguous) are combined with
  * M = max m, w = exp(m - M), L = sum w*l, A = sum w*acc.  out float16 [Hq, hd] = A / L;
@@ -321,6 +334,25 @@ int pkv_topk_rows(const float* signal, int64_t rows, int64_t n, int64_t keep, in
  * token_bytes % 16 == 0, 16-byte aligned buffers. */
 int pkv_gather_tokens(const void* src, void* dst, const int64_t* indices, int64_t rows, int64_t src_tokens,
                       int64_t keep, int64_t token_bytes, pkv_stream_t stream);
+
+/* ---------------------------------------------------------------- model adapter ------- */
+
+/* qwen2_attention.py:79-106 (and examples/llama_phasekv_adapter.py:63-85) between the projections and decode
+ * attention, for n_tokens new tokens of one layer (batch 1) in one launch: apply_rotary_pos_emb to q and k, the
+ * .to(float16) of q, k and v, and the write of k and v into the float16 tier (append_hot / append_prompt_token).
+ *   q [n_tokens, Hq, hd], k and v [n_tokens, Hkv, hd] of `dtype` (PKV_DTYPE_F16 / PKV_DTYPE_BF16), with
+ *   *_token_stride elements between consecutive tokens (the projections' row pitch);
+ *   cos, sin [n_tokens, hd] of `rope_dtype` (any PKV_DTYPE_*), rope_token_stride elements between tokens: the
+ *   full-width tables transformers builds (both halves filled);
+ *   q_out float16 [n_tokens, Hq, hd] dense; hot_k / hot_v float16 [Hkv, capacity, hd]: token i goes to slot
+ *   `slot` + i.
+ * Rounded as torch rounds when the rotation runs in `dtype`: x*cos, rotate_half(x)*sin and their sum are each
+ * rounded to `dtype`, then converted to float16. */
+int pkv_rope_append(const void* q, const void* k, const void* v, int dtype, int64_t q_token_stride,
+                    int64_t k_token_stride, int64_t v_token_stride, const void* cos, const void* sin,
+                    int rope_dtype, int64_t rope_token_stride, int n_tokens, int num_q_heads, int num_kv_heads,
+                    int head_dim, void* q_out, void* hot_k, void* hot_v, int64_t capacity, int64_t slot,
+                    pkv_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libphasekv_b200.so")
 
 PKV_SEG_KIVI, PKV_SEG_PER_TOKEN, PKV_SEG_FP16 = 0, 1, 2
 PKV_SEG_FLAG_FRESH = 1
+PKV_DTYPE_F16, PKV_DTYPE_BF16, PKV_DTYPE_F32 = 0, 1, 2
 PKV_E_BITS, PKV_E_SHAPE, PKV_E_NULL, PKV_E_LAYOUT = -1, -2, -3, -4
 PKV_E_WORKSPACE, PKV_E_CUDA, PKV_E_LIMIT = -5, -6, -7
 
@@ -74,6 +75,10 @@ _SIGNATURES = {
                                _VP, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t),
                                ctypes.POINTER(ctypes.c_size_t)], _I32),
     "pkv_decode_attention_batched": ([_VP, _VP, _VP, _F32, _VP, ctypes.c_size_t, _VP, _VP], _I32),
+    "pkv_decode_chunk_plan": ([ctypes.POINTER(Segment), _I32, _I32, _I32, _I32, _I32, _I32, _VP, ctypes.c_size_t,
+                               ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)], _I32),
+    "pkv_rope_append": ([_VP, _VP, _VP, _I32, _I64, _I64, _I64, _VP, _VP, _I32, _I64, _I32, _I32, _I32, _I32,
+                         _VP, _VP, _VP, _I64, _I64, _VP], _I32),
     "pkv_merge_partials": ([_VP, _VP, _VP, _I32, _I32, _I32, _VP, _VP, _VP, _VP, _VP], _I32),
     "pkv_merge_partials_strided": ([_VP, _VP, _VP, _I32, _I64, _I64, _I32, _I32, _VP, _VP, _VP, _VP, _VP], _I32),
     "pkv_exchange_create": ([_I32, _I32, _I32, _I32, ctypes.POINTER(_VP), _VP], _I32),

@@ -711,6 +711,27 @@ extern "C" int pkv_decode_batch_plan(const pkv_segment_t* segs, const int32_t* s
     return PKV_OK;
 }
 
+extern "C" int pkv_decode_chunk_plan(const pkv_segment_t* segs, int n_segments, int chunk_len, int num_q_heads,
+                                     int num_kv_heads, int head_dim, int sm_count, void* table,
+                                     size_t table_capacity, size_t* table_bytes, size_t* workspace_bytes) {
+    if (!segs) return PKV_E_NULL;
+    if (n_segments <= 0 || n_segments > PKV_MAX_SEGMENTS || chunk_len <= 0 || chunk_len > (1 << 16)) return PKV_E_SHAPE;
+    const pkv_segment_t& hot = segs[n_segments - 1];
+    if (hot.kind != PKV_SEG_FP16 || hot.seq_len < chunk_len) return PKV_E_SHAPE;
+    // query i of the chunk is a "sequence" of its own: the same packed segments, and the float16 tier cut off
+    // behind the token the query belongs to
+    std::vector<pkv_segment_t> all((size_t)n_segments * chunk_len);
+    std::vector<int32_t> offsets(chunk_len + 1);
+    for (int i = 0; i < chunk_len; ++i) {
+        offsets[i] = i * n_segments;
+        for (int k = 0; k < n_segments; ++k) all[(size_t)i * n_segments + k] = segs[k];
+        all[(size_t)i * n_segments + n_segments - 1].seq_len = hot.seq_len - (chunk_len - 1 - i);
+    }
+    offsets[chunk_len] = chunk_len * n_segments;
+    return pkv_decode_batch_plan(all.data(), offsets.data(), chunk_len, num_q_heads, num_kv_heads, head_dim, sm_count,
+                                 table, table_capacity, table_bytes, workspace_bytes);
+}
+
 extern "C" int pkv_decode_attention_batched(const void* q, const void* table_host, const void* table_device,
                                             float sm_scale, void* workspace, size_t workspace_bytes, void* out,
                                             pkv_stream_t stream) {

@@ -476,6 +476,61 @@ class BatchDecodePlan:
         return out
 
 
+def fused_phasekv_chunk_decode(q: torch.Tensor, tiers, num_attention_heads: int) -> torch.Tensor:
+    """Causal attention of a chunk of ``n`` new tokens against one layer: ``q`` float16 ``[n, Hq, hd]``, ``tiers`` a
+    ``LayerTiers`` whose float16 tier ALREADY holds the chunk's ``n`` keys and values at its end
+    (``PhaseKVCache.append_rotated`` or ``n`` calls of ``append_prompt_token``).  Row ``i`` of the result
+    ``[n, Hq, hd]`` equals what the reference computes token by token (``qwen2_attention.py:99-106``): query
+    ``i`` against every packed tier and the float16 tokens up to and including its own.
+
+    All ``n`` queries go through one split-K launch and one merge launch when the layer's layout is the
+    tensor-core kernel's (head_dim 128, group 32, GQA group <= 8); other layouts are served query by query."""
+    nv.require_cuda(q, "q")
+    if q.ndim != 3 or q.dtype != torch.float16 or q.shape[1] != num_attention_heads:
+        raise ValueError(f"q must be float16 [n, Hq={num_attention_heads}, hd], got {q.dtype} {tuple(q.shape)}")
+    n = q.shape[0]
+    if n == 0 or tiers.hot_len < n:
+        raise ValueError(f"the float16 tier holds {tiers.hot_len} tokens, fewer than the chunk's {n}")
+    q = q.contiguous()
+    segs, keep, hkv, hd, origins = _layer_descriptors(tiers)
+    if q.shape[2] != hd or num_attention_heads % hkv:
+        raise ValueError(f"q {tuple(q.shape)} does not fit Hkv={hkv}, hd={hd}")
+    fresh = [(i, o) for i, o in enumerate(origins) if _unread(o)]
+    for i, _ in fresh:
+        segs[i].flags |= nv.PKV_SEG_FLAG_FRESH
+    dev = q.device
+    L = nv.lib()
+    arr = (nv.Segment * len(segs))(*segs)
+    sms = _device_sm_count(dev)
+    tb, wb = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    rc = L.pkv_decode_chunk_plan(arr, len(segs), n, num_attention_heads, hkv, hd, sms, None, 0,
+                                 ctypes.byref(tb), ctypes.byref(wb))
+    out = torch.empty_like(q)
+    if rc == nv.PKV_E_LAYOUT:
+        need = ctypes.c_size_t(0)
+        hot_len = arr[len(segs) - 1].seq_len
+        for i in range(n):
+            arr[len(segs) - 1].seq_len = hot_len - (n - 1 - i)
+            nv.check(L.pkv_decode_workspace_bytes(arr, len(segs), num_attention_heads, hkv, hd, sms, ctypes.byref(need)))
+            out[i] = _launch_decode(q[i], arr, len(segs), int(need.value), hkv, True, False)[0]
+    else:
+        nv.check(rc)
+        table_host = torch.empty(tb.value, dtype=torch.uint8).pin_memory()
+        nv.check(L.pkv_decode_chunk_plan(arr, len(segs), n, num_attention_heads, hkv, hd, sms, table_host.data_ptr(),
+                                         tb.value, ctypes.byref(tb), ctypes.byref(wb)))
+        with torch.cuda.device(dev):
+            # (torch's pinned-memory allocator keeps the block alive until this asynchronous copy has run)
+            table_device = table_host.to(dev, non_blocking=True)
+            stream = nv.stream_of(dev)
+            ws = _workspace(dev, stream, int(wb.value))
+            nv.check(L.pkv_decode_attention_batched(q.data_ptr(), table_host.data_ptr(), table_device.data_ptr(),
+                                                    1.0 / (hd ** 0.5), ws.data_ptr(), ws.numel(), out.data_ptr(), stream))
+    for _, origin in fresh:
+        _mark_read(origin)
+    del keep
+    return out
+
+
 def fused_phasekv_decode_batched(q: torch.Tensor, tiers_list, num_attention_heads: int) -> torch.Tensor:
     """``q`` float16 ``[B, Hq, hd]`` against ``tiers_list`` (one ``LayerTiers`` per sequence, or a
     ``BatchDecodePlan`` built from them) -> float16 ``[B, Hq, hd]``, row ``i`` equal to

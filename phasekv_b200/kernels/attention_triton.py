@@ -12,6 +12,7 @@ from .attention_cuda import (  # noqa: F401
     _reduce_splits,
     decode_attention_packed,
     decode_attention_packed_splitk,
+    fused_phasekv_chunk_decode,
     fused_phasekv_decode,
     fused_three_tier_decode,
     fused_three_tier_decode_single,

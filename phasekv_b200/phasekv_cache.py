@@ -29,6 +29,7 @@ from typing import List, Optional, Sequence
 
 import torch
 
+from . import _native as nv
 from .cold_arena import ColdArena, CoolingTable, cool_layers_into_arenas
 from .cold_tier import select_and_pack_cold
 from .hetero_cache import gather_tokens
@@ -42,6 +43,7 @@ except Exception:  # pragma: no cover - transformers is optional
 
 _PACKED_BITS = (2, 4, 8)
 _INDEX_DTYPES = (torch.int8, torch.int16, torch.int32, torch.int64, torch.uint8)
+_ROPE_DTYPES = {torch.float16: nv.PKV_DTYPE_F16, torch.bfloat16: nv.PKV_DTYPE_BF16, torch.float32: nv.PKV_DTYPE_F32}
 
 
 class _Phase(enum.Enum):
@@ -217,6 +219,27 @@ class PhaseKVCache(_CacheBase):
         """The cache grows with every frozen segment; the hot capacity is not a bound on it."""
         return None
 
+    def get_mask_sizes(self, query_length, layer_idx: int = 0):
+        """``(kv_length, kv_offset)`` for the mask a model prepares before calling its layers (the base class
+        would look for its own layer objects in ``self.layers``).  Older transformers pass the cache positions
+        instead of the query length.  The PhaseKV attention layer ignores the mask: visibility follows from what
+        has been written."""
+        if isinstance(query_length, torch.Tensor):
+            query_length = query_length.shape[0]
+        return self.get_seq_length(layer_idx) + int(query_length), 0
+
+    @property
+    def is_compileable(self) -> bool:
+        return False
+
+    @property
+    def is_initialized(self) -> bool:
+        return True
+
+    @property
+    def is_sliding(self) -> List[bool]:
+        return [False] * len(self.layers)
+
     @property
     def true_seq_length(self) -> int:
         return self._seen_tokens
@@ -348,6 +371,67 @@ class PhaseKVCache(_CacheBase):
         self._seen_tokens += self._chunk_len
         self._chunk_len, self._chunk_start = 0, []
         self._phase = _Phase.IDLE
+
+    # ------------------------------------------------------------------ the adapter's fused write
+    @torch.no_grad()
+    def append_rotated(self, layer_idx: int, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                       cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        """What an attention layer does between its projections and decode attention, in one launch: rotary
+        position embedding of ``query [n, Hq, hd]`` and ``key [n, Hkv, hd]`` with ``cos / sin [n, hd]``, conversion
+        of all three to float16 and the write of the ``n`` new keys and ``value [n, Hkv, hd]`` into the float16
+        tier.  Returns the rotated queries, float16 ``[n, Hq, hd]``.
+
+        ``n`` is 1 in a decode step (this is ``append_hot`` then) and the whole chunk inside a prompt chunk (this
+        is ``append_prompt_token`` for each of its tokens then; the caller attends with
+        ``fused_phasekv_chunk_decode``, which applies the causal rule inside the chunk).  The tensors may be views
+        of the projections' outputs (any token stride); batch 1."""
+        layer = self.layer_tiers(layer_idx)
+        in_chunk = self._phase is _Phase.PROMPT_CHUNK
+        where = f"layer {layer_idx} new Q/K/V"
+        for t in (query, key, value, cos, sin):
+            if not isinstance(t, torch.Tensor):
+                raise TypeError(f"{where} and cos/sin must be tensors")
+        hkv, hd = layer.hot_k.shape[1], layer.hot_k.shape[3]
+        n = query.shape[0] if query.ndim == 3 else -1
+        if layer.hot_k.shape[0] != 1:
+            raise ValueError("append_rotated() serves batch 1")
+        if n <= 0 or query.shape[2] != hd or query.shape[1] % hkv or key.shape != (n, hkv, hd) or value.shape != key.shape:
+            raise ValueError(f"{where} must be [n, Hq, {hd}] / [n, {hkv}, {hd}] / [n, {hkv}, {hd}], got "
+                             f"{tuple(query.shape)}/{tuple(key.shape)}/{tuple(value.shape)}")
+        if query.dtype not in (torch.float16, torch.bfloat16) or key.dtype != query.dtype or value.dtype != query.dtype:
+            raise ValueError(f"{where} must all be float16 or all bfloat16")
+        if cos.shape != (n, hd) or sin.shape != (n, hd) or cos.dtype != sin.dtype or cos.dtype not in _ROPE_DTYPES:
+            raise ValueError(f"cos/sin must be [{n}, {hd}] of one floating dtype, got {tuple(cos.shape)}/{tuple(sin.shape)}")
+        for t in (query, key, value, cos, sin):
+            if t.device != layer.hot_k.device:
+                raise ValueError(f"{where} must be on 同一设备 (the device of the hot tier, {layer.hot_k.device})")
+            if t.stride(-1) != 1 or (t.ndim == 3 and t.stride(1) != hd):
+                raise ValueError(f"{where}: heads and head_dim must be dense (only the token stride is free)")
+        if in_chunk:
+            if layer.hot_len - self._chunk_start[layer_idx] + n > self._chunk_len:
+                raise RuntimeError(f"第 {layer_idx} 层已写满 (layer {layer_idx} is full): the prompt chunk holds "
+                                   f"{self._chunk_len} tokens")
+        else:
+            if n != 1:
+                raise ValueError(f"a decode step appends one token, got {n}; call begin_prompt_chunk(length) for new input")
+            if layer_idx in self._written:
+                raise RuntimeError(f"第 {layer_idx} 层在当前 decode 步已追加 (layer {layer_idx} already got this step's "
+                                   "token); call finish_decode_step() after the forward pass")
+        slot = layer.hot_len
+        if slot + n > layer.hot_k.shape[2]:
+            raise RuntimeError(f"layer {layer_idx}: hot tier is full (hot_len={slot}, capacity={layer.hot_k.shape[2]})")
+        out = torch.empty((n, query.shape[1], hd), dtype=torch.float16, device=query.device)
+        with torch.cuda.device(query.device):
+            nv.check(nv.lib().pkv_rope_append(
+                query.data_ptr(), key.data_ptr(), value.data_ptr(), _ROPE_DTYPES[query.dtype], query.stride(0),
+                key.stride(0), value.stride(0), cos.data_ptr(), sin.data_ptr(), _ROPE_DTYPES[cos.dtype], cos.stride(0),
+                n, query.shape[1], hkv, hd, out.data_ptr(), layer.hot_k.data_ptr(), layer.hot_v.data_ptr(),
+                layer.hot_k.shape[2], slot, nv.stream_of(query.device)))
+        layer.hot_len = slot + n
+        if not in_chunk:
+            self._written.add(layer_idx)
+            self._phase = _Phase.DECODE_STEP
+        return out
 
     # ------------------------------------------------------------------ shared write path
     def _write_token(self, layer_idx: int, layer: LayerTiers, key: torch.Tensor, value: torch.Tensor) -> None:
