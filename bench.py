@@ -780,6 +780,106 @@ def measure_longctx(ctx, steps, warmup, layers):
         torch.cuda.empty_cache()
 
 
+def _random_prefill(torch, device, layers, tokens, seed):
+    import types
+    g = torch.Generator().manual_seed(seed)
+    dense = types.SimpleNamespace(key_cache=[], value_cache=[])
+    for _ in range(layers):
+        dense.key_cache.append(torch.randn(1, 4, tokens, 128, generator=g, dtype=torch.float16).to(device))
+        dense.value_cache.append(torch.randn(1, 4, tokens, 128, generator=g, dtype=torch.float16).to(device))
+    return dense
+
+
+def measure_prompt_chunk(ctx, prompt_len=4096, chunk=64):
+    """A chunk of new input tokens against one layer (7B geometry): all queries in one split-K + merge launch pair
+    versus the reference's order, one append and one single-query call per token (qwen2_attention.py:99-106).
+    Device time of ten rounds each, host work included (both are what a caller pays per layer)."""
+    torch, device = ctx.torch, ctx.device
+    from phasekv_b200.kernels.attention_cuda import fused_phasekv_chunk_decode, fused_phasekv_decode
+    from phasekv_b200.phasekv_cache import PhaseKVCache
+    cache = PhaseKVCache.from_dense_prefill(_random_prefill(torch, device, 1, prompt_len, 5), prompt_len=prompt_len)
+    for _ in range(100):
+        k = torch.randn(1, 4, 1, 128, device=device, dtype=torch.float16)
+        cache.append_hot(0, k, k)
+        cache.finish_decode_step()
+    cache.begin_prompt_chunk(chunk)
+    ks = torch.randn(1, 4, chunk, 128, device=device, dtype=torch.float16)
+    q = torch.randn(chunk, 28, 128, device=device, dtype=torch.float16)
+    tiers = cache.layer_tiers(0)
+    start = tiers.hot_len
+
+    def token_loop():
+        tiers.hot_len = start
+        outs = []
+        for i in range(chunk):
+            cache.append_prompt_token(0, ks[:, :, i:i + 1], ks[:, :, i:i + 1])
+            outs.append(fused_phasekv_decode(q[i], tiers, 28))
+        return torch.stack(outs)
+
+    def one_launch_pair():
+        tiers.hot_len = start + chunk
+        return fused_phasekv_chunk_decode(q, tiers, 28)
+    res = {"config": {"workload": "prompt chunk attention, one layer", "prompt_tokens": prompt_len, "chunk_tokens": chunk,
+                      "cold_steps": len(tiers.cold)}}
+    for name, fn in (("token_loop_us", token_loop), ("one_launch_pair_us", one_launch_pair)):
+        res[name] = _timed_eager(torch, fn, 10, ctx.barrier) * 1e3
+    res["max_abs_diff"] = float((token_loop().float() - one_launch_pair().float()).abs().max())
+    res["speedup"] = res["token_loop_us"] / res["one_launch_pair_us"]
+    return res
+
+
+def measure_cold_arena(ctx, prompt_len, layers, generated=1000):
+    """Decode over a cache that has generated `generated` tokens with the reference's defaults (window 32, batch 16,
+    half kept: a cooling step of 8 tokens every 16 tokens).  `arena`: the steps of a layer are slots of one arena and
+    are read as ONE masked segment; `per_step`: the same steps as tensors of their own, one descriptor each (what a
+    list of segments costs); `single_segment`: as many cold tokens in one ordinary segment (the lower bound)."""
+    torch, device = ctx.torch, ctx.device
+    from dataclasses import replace
+
+    from phasekv_b200.kernels import packing
+    from phasekv_b200.kernels.attention_cuda import fused_phasekv_decode
+    from phasekv_b200.kernels.tiers import LayerTiers, PackedKVSegment
+    from phasekv_b200.phasekv_cache import PhaseKVCache
+    cache = PhaseKVCache.from_dense_prefill(_random_prefill(torch, device, layers, prompt_len, 6), prompt_len=prompt_len)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(generated):
+        k = torch.randn(1, 4, 1, 128, device=device, dtype=torch.float16)
+        for l in range(layers):
+            cache.append_hot(l, k, k)
+        cache.finish_decode_step()
+    torch.cuda.synchronize()
+    host_ms = (time.perf_counter() - t0) / generated * 1e3
+    q = torch.randn(28, 128, device=device, dtype=torch.float16)
+
+    def own(pt):
+        return replace(pt, packed=pt.packed.clone(), scale=pt.scale.clone(), mins=pt.mins.clone())
+
+    def per_step(t):
+        return LayerTiers(prompt=t.prompt, cold=[PackedKVSegment(own(s.key), own(s.value)) for s in t.cold],
+                          hot_k=t.hot_k, hot_v=t.hot_v, hot_len=t.hot_len)
+
+    def single(t):
+        k = torch.randn(1, 4, sum(s.length for s in t.cold), 128, device=device, dtype=torch.float16)
+        seg = PackedKVSegment(packing.quantize_pack(k, COLD_BITS, -2, GROUP), packing.quantize_pack(k, COLD_BITS, -1, GROUP))
+        return LayerTiers(prompt=t.prompt, cold=[seg], hot_k=t.hot_k, hot_v=t.hot_v, hot_len=t.hot_len)
+    first = cache.layer_tiers(0)
+    res = {"config": {"workload": "decode after generation, cold tier in arenas", "prompt_tokens": prompt_len,
+                      "layers": layers, "generated_tokens": generated, "cold_steps": len(first.cold),
+                      "cold_tokens": first.cold_len, "hot_tokens": first.hot_len},
+           "cache_update_host_ms_per_token": host_ms}
+    for name, view in (("arena", lambda t: t), ("per_step", per_step), ("single_segment", single)):
+        tl = [view(cache.layer_tiers(l)) for l in range(layers)]
+
+        def run():
+            for t in tl:
+                fused_phasekv_decode(q, t, 28)
+        run()  # settles the descriptors (the first launch over a segment is flagged fresh)
+        res[name + "_us_per_layer"] = time_graph(torch, run, 20, 3) / layers * 1e3
+    res["arena_over_single_segment"] = res["arena_us_per_layer"] / res["single_segment_us_per_layer"]
+    return res
+
+
 def sharded_block(ctx, args):
     """The two configurations that shard over GPUs (sequence-sharded long context, batch-sharded serving) and, on
     one GPU, the pack kernels, measured in the same process group after the headline.  A workload that fails
@@ -802,6 +902,13 @@ def sharded_block(ctx, args):
             block["pack"] = {k: res[k] for k in ("by_bits", "cold_cooling_us", "cold_config", "config")}
         except Exception as exc:
             block["pack"] = {"error": f"{type(exc).__name__}: {exc}"}
+        for name, fn in (("prompt_chunk", lambda: [measure_prompt_chunk(ctx, 4096, 64), measure_prompt_chunk(ctx, args.prompt, 64)]),
+                         ("cold_arena", lambda: measure_cold_arena(ctx, args.prompt, args.layers))):
+            try:
+                block[name] = fn()
+            except Exception as exc:
+                block[name] = {"error": f"{type(exc).__name__}: {exc}"}
+            ctx.torch.cuda.empty_cache()
     return block
 
 

@@ -300,8 +300,13 @@ DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, i
     long long generic_tokens = 0;
     double fast_cost = 0.0;
     std::vector<char> is_fast(n_segs);
+    // The tensor-core kernels take KIVI + float16 or per-token + float16 segments in one launch, not KIVI and
+    // per-token together: in such a mix (no caller of the reference builds one) the per-token segments go to the
+    // general kernel.
+    bool any_kivi = false;
+    for (int i = 0; i < n_segs; ++i) any_kivi |= segs[i].kind == PKV_SEG_KIVI;
     for (int i = 0; i < n_segs; ++i) {
-        is_fast[i] = mma::eligible(segs[i], Hq, Hkv, hd);
+        is_fast[i] = mma::eligible(segs[i], Hq, Hkv, hd) && !(any_kivi && segs[i].kind == PKV_SEG_PER_TOKEN);
         if (is_fast[i]) fast_cost += seg_cost(segs[i]);
         else generic_tokens += segs[i].seq_len;
     }
@@ -438,7 +443,10 @@ int run_splitk(const void* q, const pkv_segment_t* segs, int n_segs, int num_q_h
         }
         for (int i = 0; i < cnt; ++i)
             if (a.segs[i].key_tma < 0) a.segs[i].key_tma = 0;  // could not be described: cp.async
-        const int rc2 = mma::launch(a, launch_work, num_kv_heads, s);
+        bool per_token = false;
+        for (int i = 0; i < cnt; ++i) per_token |= a.segs[i].kind == PKV_SEG_PER_TOKEN;
+        const int rc2 = per_token ? mma::launch_per_token(a, launch_work, num_kv_heads, s)
+                                  : mma::launch(a, launch_work, num_kv_heads, s);
         if (rc2 != PKV_OK) return rc2;
     }
     // layout-generic kernel over everything else (float16 hot tier, per-token layout, ragged shapes)
@@ -648,7 +656,8 @@ extern "C" int pkv_decode_batch_plan(const pkv_segment_t* segs, const int32_t* s
     }
     double units = 0.0;  // 64-token tiles (a float16 tile of 32 tokens moves about as many bytes per token x4)
     for (int i = 0; i < n_segs; ++i) {
-        if (!mma::eligible(segs[i], num_q_heads, num_kv_heads, head_dim)) return PKV_E_LAYOUT;
+        if (!mma::eligible(segs[i], num_q_heads, num_kv_heads, head_dim) || segs[i].kind == PKV_SEG_PER_TOKEN)
+            return PKV_E_LAYOUT;
         if (mma::tiles_of(segs[i]) > INT32_MAX) return PKV_E_LIMIT;
         units += (double)mma::tiles_of(segs[i]);
     }

@@ -12,9 +12,6 @@ constexpr float kLog2e = 1.4426950408889634f;
 #define PKV_K_UNROLL 4
 #endif
 constexpr int kKUnroll = PKV_K_UNROLL;
-#ifndef PKV_ABLATE
-#define PKV_ABLATE 0
-#endif
 #ifndef PKV_KEY_TMA
 #define PKV_KEY_TMA 1
 #endif
@@ -45,7 +42,6 @@ constexpr bool kSmallFirst = PKV_SMALL_FIRST != 0;  // the partial super-tile of
 #endif
 // Low part of p * value_scale for 2-bit codes (wider codes always get it: their codes reach 15 or 255)
 constexpr bool kPvResidual2 = PKV_PV_RESIDUAL_2BIT != 0;
-constexpr int kAblate = PKV_ABLATE;  // timing experiments only: 1 no score loop, 2 no value loop, 4 no key copies, 8 no value copies
 
 struct WarpState {
     float m[2];        // running max (log2 domain) of heads 2t, 2t+1
@@ -197,7 +193,6 @@ struct KSrc {
     }
 
     __device__ __forceinline__ void issue(long long tile, int n_sub, unsigned kb, int tid) const {
-        if (kAblate & 4) return;
         if (n_sub == C::NSUB) issue_impl<true>(tile, n_sub, kb, tid);
         else issue_impl<false>(tile, n_sub, kb, tid);
     }
@@ -215,19 +210,22 @@ struct VSrc {
     int lane;
     bool meta16;  // this head's scale rows start on 16 bytes
 
-    __device__ VSrc(const SegDev& sg, int kvh, int lane_) : lane(lane_) {
-        meta16 = (((long long)kvh * sg.v_head_tokens) & 1) == 0;
-        vc = sg.vp + (size_t)kvh * sg.v_head_tokens * (C::VWPT * 4) + 16 * lane;
+    // codes [heads][head_tokens][hd * BITS / 8 bytes], scale and zero [heads][head_tokens][4] float16: the values of
+    // a KIVI segment, or the keys or the values of a per-token segment
+    __device__ VSrc(const uint8_t* codes, const __half* scale, const __half* zero, long long head_tokens, int kvh,
+                    int lane_) : lane(lane_) {
+        meta16 = (((long long)kvh * head_tokens) & 1) == 0;
+        vc = codes + (size_t)kvh * head_tokens * (C::VWPT * 4) + 16 * lane;
         const int lt = lane / CPT;
         d_vc = (lt + lt / 8) * (C::VWPT * 4) + 16 * (lane % CPT);
-        vs = reinterpret_cast<const char*>(sg.vs + (size_t)kvh * sg.v_head_tokens * 4) + 16 * lane;
-        vm = reinterpret_cast<const char*>(sg.vm + (size_t)kvh * sg.v_head_tokens * 4) + 16 * lane;
+        vs = reinterpret_cast<const char*>(scale + (size_t)kvh * head_tokens * 4) + 16 * lane;
+        vm = reinterpret_cast<const char*>(zero + (size_t)kvh * head_tokens * 4) + 16 * lane;
     }
+    __device__ VSrc(const SegDev& sg, int kvh, int lane_) : VSrc(sg.vp, sg.vs, sg.vm, sg.v_head_tokens, kvh, lane_) {}
 
     // values of one tile into the stage at `sa`; one warp.  Rows of tokens >= n_valid are zero-filled
     // (their probabilities are zero, but garbage scales could be NaN).
     __device__ __forceinline__ void issue(long long tile, unsigned sa, int n_valid) const {
-        if (kAblate & 8) return;
         const uint8_t* v = vc + tile * (C::T * C::VWPT * 4);
         const long long off = tile * (C::T * 8);
         if (n_valid >= C::T && meta16) {
@@ -296,6 +294,10 @@ __device__ __forceinline__ unsigned residual_steps(const char* kb, int sub, cons
     return need;
 }
 
+template <int BITS, int NGRP>
+__device__ __forceinline__ void softmax_pv(float (&sacc)[NGRP * 2][4], const char* sa, WarpState& st,
+                                           const LaneSel<BITS>& ls, int lane, int n_valid, int slot, int g_off);
+
 // NGRP = 2: the whole 64-token tile.  NGRP = 1: only its 32-token group `g_off` (two warps share a tile when a
 // super-tile has few tiles, so that the tail of a CTA's range is spread over all warps).
 template <int BITS, int NGRP = 2>
@@ -304,9 +306,8 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
                                              const char* qabs, int slot, int g_off = 0) {
     using C = Cfg<BITS>;
     static_assert(C::NG == 2 && (NGRP == 1 || NGRP == 2), "a tile is two key groups");
-    const int g = lane >> 2, t = lane & 3;
+    const int t = lane & 3;
     const unsigned res_steps = residual_steps<BITS>(kb, sub, qabs, lane);
-    const unsigned sel_lo = 0x5410u, sel_hi = 0x7632u;
 
     // ---------------- scores: S^T tile-by-tile, M = 16 tokens, N = 8 heads, K = channels
     float sacc[NGRP * 2][4];
@@ -334,7 +335,7 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
                               16 * (sub >> 2);
     // partially unrolled: the fully unrolled loop made the kernel instruction-fetch bound on short contexts
 #pragma unroll (kKUnroll / 2)
-    for (int kp = 0; kp < ((kAblate & 1) ? 0 : 4); ++kp) {
+    for (int kp = 0; kp < 4; ++kp) {
         unsigned zs[4], zm[4];
         ldmatrix_x4_trans(meta_row + C::OFF_KS + 32 * kp * C::MROW, zs[0], zs[1], zs[2], zs[3]);
         ldmatrix_x4_trans(meta_row + C::OFF_KM + 32 * kp * C::MROW, zm[0], zm[1], zm[2], zm[3]);
@@ -376,8 +377,7 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
         }
     }
 
-    // ---------------- online softmax in the log2 domain
-    float mx[2] = {-INFINITY, -INFINITY};
+    // undo the power-of-two code scaling, add the zero terms, go to the log2 domain
 #pragma unroll
     for (int e = 0; e < NGRP; ++e) {
         const int G = NGRP == 2 ? e : g_off;
@@ -390,6 +390,27 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
             s[1] = (s[1] * unscale<BITS>(2 * j) + bias1) * c_qk;
             s[2] = (s[2] * unscale<BITS>(2 * j + 1) + bias0) * c_qk;
             s[3] = (s[3] * unscale<BITS>(2 * j + 1) + bias1) * c_qk;
+        }
+    }
+    softmax_pv<BITS, NGRP>(sacc, sa, st, ls, lane, n_valid, slot, g_off);
+}
+
+// Online softmax (log2 domain) over the scores of one tile and out^T += V^T P with the values staged at `sa`.
+// sacc[2e + j] holds, for key group G (= e, or g_off when NGRP == 1) of the tile, the scores of tokens
+// 32G + 4g + 2j (elements 0, 1: heads 2t, 2t+1) and 32G + 4g + 2j + 1 (elements 2, 3).
+template <int BITS, int NGRP>
+__device__ __forceinline__ void softmax_pv(float (&sacc)[NGRP * 2][4], const char* sa, WarpState& st,
+                                           const LaneSel<BITS>& ls, int lane, int n_valid, int slot, int g_off) {
+    using C = Cfg<BITS>;
+    const int g = lane >> 2, t = lane & 3;
+    const unsigned sel_lo = 0x5410u, sel_hi = 0x7632u;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int e = 0; e < NGRP; ++e) {
+        const int G = NGRP == 2 ? e : g_off;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            float* s = sacc[2 * e + j];
             if (n_valid < C::T) {  // last tile of a ragged segment: rows are tokens 32G + 4g + 2j (+1)
                 const int tok = 32 * G + 4 * g + 2 * j;
                 if (tok >= n_valid) s[0] = s[1] = -INFINITY;
@@ -445,7 +466,7 @@ __device__ __forceinline__ void compute_tile(const char* kb, int sub, const char
     const char* vs_lane = sa + C::OFF_VS + 64 * t;
     const char* vm_lane = sa + C::OFF_VM + 64 * t + 4 * ((g >> 1) & 1);  // word holding zero[.][g], g < 4
 #pragma unroll
-    for (int e = 0; e < ((kAblate & 2) ? 0 : NGRP); ++e) {
+    for (int e = 0; e < NGRP; ++e) {
         const int G = NGRP == 2 ? e : g_off;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -881,6 +902,166 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const
     finish_cta<BITS>(a, st, kvh, smem_f);
 }
 
+// ---------------------------------------------------------------- per-token layout (keys packed along head_dim)
+// Keys of this layout look exactly like values: per token a row of hd * BITS / 8 code bytes and four (scale, zero)
+// pairs, one per group of 32 channels.  The score contraction runs over channels, which now lie NEXT to each other
+// in a word, so an A operand (rows = tokens) pairs two fields of ONE word: field f of the low half with field f of
+// the high half, isolated by a single AND (after a byte shift for fields in the upper byte of a half).  The MMA does
+// not care which channel sits at which k index as long as q is permuted the same way, and the power of two a field
+// position implies is folded into q.  Scale and zero belong to the ROW (token) here, so they cannot ride on the B
+// operand: every group of 32 channels (two k-steps) gets a fresh accumulator and
+//   score(n, h) = sum_G  scale[n, G] * 2^24 * acc_G(n, h)  +  zero[n, G] * sum_{d in G} q[h, d].
+// The B operands (q, permuted and scaled) are the same for every tile and stay in registers.
+//
+// Channels (relative to 16 * kk) at the lane's k indices (2t, 2t+1 | 2t+8, 2t+9) and the factor q carries:
+//   2 bits: (t, t+8 | t+4, t+12) * 4^-t      4 bits: (t, t+4 | t+8, t+12) * 16^-(t&1)      8 bits: (4t, 4t+2 | 4t+1, 4t+3)
+template <int BITS>
+__device__ __forceinline__ void per_token_q(const char* q_s /* [8][kQRowBytes] */, int lane, unsigned (&qb)[8][2]) {
+    const int g = lane >> 2, t = lane & 3;
+    const __half* row = reinterpret_cast<const __half*>(q_s + g * kQRowBytes);
+    const float f = BITS == 2 ? 1.0f / (float)(1 << (2 * t)) : BITS == 4 ? ((t & 1) ? 0.0625f : 1.0f) : 1.0f;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+        int c0, c1, c2, c3;
+        if (BITS == 2) c0 = t, c1 = t + 8, c2 = t + 4, c3 = t + 12;
+        else if (BITS == 4) c0 = t, c1 = t + 4, c2 = t + 8, c3 = t + 12;
+        else c0 = 4 * t, c1 = 4 * t + 2, c2 = 4 * t + 1, c3 = 4 * t + 3;
+        const __half* r = row + 16 * kk;
+        // exact unless the scaled value is a float16 subnormal (|q| < 0.004): then it is off by at most 2^-25
+        qb[kk][0] = pack_half2(__half2float(r[c0]) * f, __half2float(r[c1]) * f);
+        qb[kk][1] = pack_half2(__half2float(r[c2]) * f, __half2float(r[c3]) * f);
+    }
+}
+
+template <int BITS>
+__device__ __forceinline__ void per_token_scores(const char* ka, const unsigned (&qb)[8][2], const float (&qs)[2][4],
+                                                 float c24, int lane, float (&sacc)[4][4]) {
+    using C = Cfg<BITS>;
+    constexpr int kRow = C::VWPT * 4;
+    const int g = lane >> 2, t = lane & 3;
+    const unsigned mask = BITS == 2 ? 0x00030003u << (2 * t) : BITS == 4 ? 0x000F000Fu << (4 * (t & 1)) : 0x00FF00FFu;
+    const int sh = BITS == 4 ? 8 * (t >> 1) : 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {  // i = 2G + j: tokens 32G + 4g + 2j and the one after
+        const int tok = 32 * (i >> 1) + 4 * g + 2 * (i & 1);
+        const char* ra = ka + (tok + tok / 8) * kRow;  // one pad row per 8 tokens; tok is even, so tok + 1 is in the same block
+        const char* rb = ra + kRow;
+        const uint2 sa2 = ldp64(ka + C::OFF_VS + 8 * tok), sb2 = ldp64(ka + C::OFF_VS + 8 * tok + 8);
+        const uint2 za2 = ldp64(ka + C::OFF_VM + 8 * tok), zb2 = ldp64(ka + C::OFF_VM + 8 * tok + 8);
+        float out[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int G = 0; G < 4; ++G) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int kk = 2 * G + hh;
+                unsigned a0, a1, a2, a3;
+                if (BITS == 2) {
+                    const unsigned x = ldp32(ra + 4 * kk), y = ldp32(rb + 4 * kk);
+                    a0 = x & mask, a2 = (x >> 8) & mask, a1 = y & mask, a3 = (y >> 8) & mask;
+                } else if (BITS == 4) {
+                    const uint2 x = ldp64(ra + 8 * kk), y = ldp64(rb + 8 * kk);
+                    a0 = (x.x >> sh) & mask, a2 = (x.y >> sh) & mask, a1 = (y.x >> sh) & mask, a3 = (y.y >> sh) & mask;
+                } else {
+                    const unsigned x = ldp32(ra + 16 * kk + 4 * t), y = ldp32(rb + 16 * kk + 4 * t);
+                    a0 = x & mask, a2 = (x >> 8) & mask, a1 = y & mask, a3 = (y >> 8) & mask;
+                }
+                mma16816(acc, a0, a1, a2, a3, qb[kk][0], qb[kk][1]);
+            }
+            const unsigned sw_a = (G & 2) ? sa2.y : sa2.x, sw_b = (G & 2) ? sb2.y : sb2.x;
+            const unsigned zw_a = (G & 2) ? za2.y : za2.x, zw_b = (G & 2) ? zb2.y : zb2.x;
+            const __half2 sh_a = *reinterpret_cast<const __half2*>(&sw_a), sh_b = *reinterpret_cast<const __half2*>(&sw_b);
+            const __half2 zh_a = *reinterpret_cast<const __half2*>(&zw_a), zh_b = *reinterpret_cast<const __half2*>(&zw_b);
+            const float ks_a = ((G & 1) ? __high2float(sh_a) : __low2float(sh_a)) * c24;
+            const float ks_b = ((G & 1) ? __high2float(sh_b) : __low2float(sh_b)) * c24;
+            const float kz_a = (G & 1) ? __high2float(zh_a) : __low2float(zh_a);
+            const float kz_b = (G & 1) ? __high2float(zh_b) : __low2float(zh_b);
+            out[0] = fmaf(ks_a, acc[0], fmaf(kz_a, qs[0][G], out[0]));
+            out[1] = fmaf(ks_a, acc[1], fmaf(kz_a, qs[1][G], out[1]));
+            out[2] = fmaf(ks_b, acc[2], fmaf(kz_b, qs[0][G], out[2]));
+            out[3] = fmaf(ks_b, acc[3], fmaf(kz_b, qs[1][G], out[3]));
+        }
+        sacc[i][0] = out[0], sacc[i][1] = out[1], sacc[i][2] = out[2], sacc[i][3] = out[3];
+    }
+}
+
+// Warps that can hold a two-stage ring of (key stage, value stage) each
+template <int BITS>
+struct PerTokenWarps {
+    static constexpr int kFit = (kSmemBytes - kHeadBytes) / (2 * NSTAGE * Cfg<BITS>::VSTAGE_BYTES);
+    static constexpr int value = kFit < NWARPS ? kFit : NWARPS;
+};
+
+// Every warp streams its own tiles (keys and values of 64 tokens each) through a private two-stage ring: no CTA
+// barrier inside the loop.
+template <int BITS>
+__device__ __forceinline__ void run_cta_per_token(const CtaCtx& a, const SegDev& sg, long long tile0, long long tile1,
+                                                  int kvh, float* smem_f) {
+    using C = Cfg<BITS>;
+    constexpr int W = PerTokenWarps<BITS>::value;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const unsigned smem_base = (unsigned)__cvta_generic_to_shared(smem_f);
+    const char* smem_c = reinterpret_cast<const char*>(smem_f);
+    const int h0 = kvh * a.G;
+    auto valid_of = [&](long long tl) { return (int)min((long long)C::T, sg.S - tl * C::T); };
+    const VSrc<BITS> ksrc(sg.kp, sg.ks, sg.km, sg.S, kvh, lane), vsrc(sg.vp, sg.vs, sg.vm, sg.S, kvh, lane);
+    constexpr int kStage = 2 * C::VSTAGE_BYTES;  // keys, then values
+    const int ring = kHeadBytes + wid * (NSTAGE * kStage);
+    auto issue = [&](long long tile, int stage) {
+        const int nv = valid_of(tile);
+        ksrc.issue(tile, smem_base + ring + stage * kStage, nv);
+        vsrc.issue(tile, smem_base + ring + stage * kStage + C::VSTAGE_BYTES, nv);
+    };
+    WarpState st;
+    init_state(st);
+    const bool mine = wid < W && tile0 + wid < tile1;
+    const bool early = !sg.fresh;
+    if (!early) cudaGridDependencySynchronize();
+    if (mine) issue(tile0 + wid, 0);
+    cp_async_commit();
+    if (early) cudaGridDependencySynchronize();
+    // q of the GQA group (zero rows for heads >= G), and per head and channel group the sum of q
+    if (tid < 128) {
+        const int head = tid >> 4, ch = tid & 15;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (head < a.G) v = *reinterpret_cast<const uint4*>(a.q + (size_t)(h0 + head) * HD + 8 * ch);
+        *reinterpret_cast<uint4*>(reinterpret_cast<char*>(smem_f) + kBarBytes + head * kQRowBytes + 16 * ch) = v;
+    } else if (tid < 160) {
+        const int head = (tid - 128) >> 2, grp = (tid - 128) & 3;
+        float sum = 0.f;
+        if (head < a.G)
+            for (int d = 0; d < 32; ++d) sum += __half2float(a.q[(size_t)(h0 + head) * HD + 32 * grp + d]);
+        reinterpret_cast<float*>(reinterpret_cast<char*>(smem_f) + kOffQAbs)[4 * head + grp] = sum;
+    }
+    cudaTriggerProgrammaticLaunchCompletion();
+    __syncthreads();
+    const float c_qk = a.sm_scale * kLog2e;
+    unsigned qb[8][2];
+    per_token_q<BITS>(smem_c + kBarBytes, lane, qb);
+    float qs[2][4];
+#pragma unroll
+    for (int G = 0; G < 4; ++G) {
+        qs[0][G] = reinterpret_cast<const float*>(smem_c + kOffQAbs)[4 * (2 * t) + G] * c_qk;
+        qs[1][G] = reinterpret_cast<const float*>(smem_c + kOffQAbs)[4 * (2 * t + 1) + G] * c_qk;
+    }
+    const LaneSel<BITS> ls(g);
+    int it = 0;
+    for (long long tile = tile0 + wid; mine && tile < tile1; tile += W, ++it) {
+        if (tile + W < tile1) issue(tile + W, (it + 1) & 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        const char* stage = smem_c + ring + (it & 1) * kStage;
+        float sacc[4][4];
+        per_token_scores<BITS>(stage, qb, qs, c_qk * 16777216.f, lane, sacc);
+        softmax_pv<BITS, 2>(sacc, stage + C::VSTAGE_BYTES, st, ls, lane, valid_of(tile), 0, 0);
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+    finish_cta<BITS>(a, st, kvh, smem_f);
+}
+
 __device__ __forceinline__ long long tiles_in(const SegDev& sg) {
     return sg.kind == PKV_SEG_FP16 ? (sg.S + TH - 1) / TH : (sg.S + 63) / 64;
 }
@@ -895,17 +1076,40 @@ __device__ __forceinline__ void run_item(const CtaCtx& a, const SegDev& sg, cons
     else run_cta<8>(a, sg, kmaps, tile0, tile1, kvh, smem_f);
 }
 
+// Which work item a CTA of the single-sequence kernels has
+__device__ __forceinline__ void item_of(const MmaArgs& a, int& si, int& split) {
+    const int w = blockIdx.x;
+    si = 0;
+    while (si + 1 < a.n_segs && w >= a.segs[si + 1].work_begin) ++si;
+    split = w - a.segs[si].work_begin;
+}
+
 // One sequence, segment descriptors inside the parameter block; work item w of a segment covers
 // split_len tiles.
 __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_mma_kernel(const __grid_constant__ MmaArgs a) {
     extern __shared__ __align__(1024) float smem_f[];
-    const int w = blockIdx.x, kvh = blockIdx.y;
-    int si = 0;
-    while (si + 1 < a.n_segs && w >= a.segs[si + 1].work_begin) ++si;
+    int si, split;
+    item_of(a, si, split);
     const SegDev& sg = a.segs[si];
-    const int split = w - sg.work_begin;
+    const int kvh = blockIdx.y;
     const CtaCtx ctx = {a.q, a.pm, a.pl, a.pacc, (size_t)a.work_offset + blockIdx.x, a.Hq, a.G, a.sm_scale};
     run_item(ctx, sg, sg.key_tma ? &a.kmaps[sg.key_tma - 1] : nullptr, (long long)split * sg.split_len, sg.split_len, kvh, smem_f);
+}
+
+// The same for launches whose packed segments are in the per-token layout (float16 segments ride along).  A
+// kernel of its own: the KIVI kernel is sensitive to its code size and register count.
+__global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_mma_per_token_kernel(const __grid_constant__ MmaArgs a) {
+    extern __shared__ __align__(1024) float smem_f[];
+    int si, split;
+    item_of(a, si, split);
+    const SegDev& sg = a.segs[si];
+    const int kvh = blockIdx.y;
+    const CtaCtx ctx = {a.q, a.pm, a.pl, a.pacc, (size_t)a.work_offset + blockIdx.x, a.Hq, a.G, a.sm_scale};
+    const long long tile0 = (long long)split * sg.split_len, tile1 = min(tiles_in(sg), tile0 + sg.split_len);
+    if (sg.kind == PKV_SEG_FP16) run_cta_fp16(ctx, sg, tile0, tile1, kvh, smem_f);
+    else if (sg.kbits == 2) run_cta_per_token<2>(ctx, sg, tile0, tile1, kvh, smem_f);
+    else if (sg.kbits == 4) run_cta_per_token<4>(ctx, sg, tile0, tile1, kvh, smem_f);
+    else run_cta_per_token<8>(ctx, sg, tile0, tile1, kvh, smem_f);
 }
 
 // Many sequences, descriptors and an explicit work list in device memory (see BatchTable).
@@ -925,9 +1129,9 @@ bool eligible(const pkv_segment_t& s, int Hq, int Hkv, int hd) {
         const uintptr_t bits = reinterpret_cast<uintptr_t>(s.k_packed) | reinterpret_cast<uintptr_t>(s.v_packed);
         return (bits & 15u) == 0 && s.head_stride % 8 == 0;
     }
-    if (s.kind != PKV_SEG_KIVI) return false;
+    if (s.kind != PKV_SEG_KIVI && s.kind != PKV_SEG_PER_TOKEN) return false;
     // a segment shorter than one group has its key group clamped to its length: still one group per 32 tokens
-    const bool k_group_ok = s.k_group == 32 || (s.seq_len < 32 && s.k_group == s.seq_len);
+    const bool k_group_ok = s.k_group == 32 || (s.kind == PKV_SEG_KIVI && s.seq_len < 32 && s.k_group == s.seq_len);
     if (s.k_bits != s.v_bits || !k_group_ok || s.v_group != 32) return false;
     const uintptr_t bits = reinterpret_cast<uintptr_t>(s.k_packed) | reinterpret_cast<uintptr_t>(s.k_scale) |
                            reinterpret_cast<uintptr_t>(s.k_mins) | reinterpret_cast<uintptr_t>(s.v_packed) |
@@ -972,6 +1176,11 @@ int launch_pdl(Kernel kernel, const Args& a, int work, int Hkv, cudaStream_t str
 int launch(const MmaArgs& a, int work, int Hkv, cudaStream_t stream) {
     static thread_local bool configured[64] = {};
     return launch_pdl(decode_mma_kernel, a, work, Hkv, stream, configured);
+}
+
+int launch_per_token(const MmaArgs& a, int work, int Hkv, cudaStream_t stream) {
+    static thread_local bool configured[64] = {};
+    return launch_pdl(decode_mma_per_token_kernel, a, work, Hkv, stream, configured);
 }
 
 int launch_batched(const BatchArgs& a, int work, int Hkv, cudaStream_t stream) {

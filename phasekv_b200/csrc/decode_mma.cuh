@@ -1,4 +1,5 @@
-// Tensor-core split-K decode over KIVI-packed segments (head_dim 128, group 32, GQA group <= 8).
+// Tensor-core split-K decode over packed segments (head_dim 128, group 32, GQA group <= 8): KIVI layout, and the
+// per-token layout in a kernel of its own (see run_cta_per_token).
 //
 // Idea.  The packed codes are never converted to numbers by arithmetic.  A b-bit code c sitting at
 // bit position p (p + b <= 10) of a 16-bit lane IS the float16 subnormal c * 2^(p-24), and
@@ -341,8 +342,10 @@ namespace mma {
 // Whether the tensor-core kernel can take this segment (otherwise the generic kernel does).
 bool eligible(const pkv_segment_t& s, int Hq, int Hkv, int hd);
 long long tiles_of(const pkv_segment_t& s);
-// Launch over `work` CTAs per KV head; a.segs[*].work_begin is relative to this launch.
+// Launch over `work` CTAs per KV head; a.segs[*].work_begin is relative to this launch.  KIVI and float16 segments.
 int launch(const MmaArgs& a, int work, int Hkv, cudaStream_t stream);
+// The same for per-token and float16 segments.
+int launch_per_token(const MmaArgs& a, int work, int Hkv, cudaStream_t stream);
 // Launch over a device-resident work list of `work` items per KV head.
 int launch_batched(const BatchArgs& a, int work, int Hkv, cudaStream_t stream);
 // Tensor maps for the keys of `s` (a KIVI segment the tensor-core kernel takes).  False when the layout cannot be

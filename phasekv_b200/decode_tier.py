@@ -26,7 +26,7 @@ def maintain(cache, *, step: int, model_config, state: hc.HeteroTierState, decod
     if keep_b < batch:
         keep_per_layer = []
         for layer in range(hc.cache_num_layers(cache)):
-            v = cache.value_cache[layer]
+            v = hc.layer_kv(cache, layer)[1]
             b, hkv = v.shape[0], v.shape[1]
             signal = hc.value_norm_signal(v, slice(base, base + batch))
             sel = hc.topk_per_head(signal, keep_b) + base
@@ -47,8 +47,9 @@ def _quantize_cold(cache, token_slice: slice, state: hc.HeteroTierState) -> None
 
 
 def _quantize_slice(cache, layer: int, token_slice: slice, bits: int, group_size: int) -> None:
-    for tensors, axis in ((cache.key_cache, -2), (cache.value_cache, -1)):
-        t = tensors[layer]
-        if not t.is_contiguous():
-            t = tensors[layer] = t.contiguous()
-        quant.fake_quant_(t, token_slice.start, token_slice.stop, bits, axis, group_size)
+    key, value = hc.layer_kv(cache, layer)
+    if not (key.is_contiguous() and value.is_contiguous()):
+        key, value = key.contiguous(), value.contiguous()
+        hc.set_layer_kv(cache, layer, key, value)
+    quant.fake_quant_(key, token_slice.start, token_slice.stop, bits, -2, group_size)
+    quant.fake_quant_(value, token_slice.start, token_slice.stop, bits, -1, group_size)

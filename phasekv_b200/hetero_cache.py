@@ -1,5 +1,6 @@
-"""Stage-A three-tier bookkeeping on a dense KV cache (any object with ``key_cache`` / ``value_cache`` lists of
-``[B, Hkv, S, hd]`` tensors), on CUDA.
+"""Stage-A three-tier bookkeeping on a dense KV cache, on CUDA.  The cache is any object with ``key_cache`` /
+``value_cache`` lists of ``[B, Hkv, S, hd]`` tensors (transformers 4.x ``DynamicCache``, or a stand-in) or with
+``layers[i].keys`` / ``.values`` (transformers 5.x); ``layer_kv`` / ``set_layer_kv`` hide the difference.
 
 Same surface as the part of the reference's ``src/phasekv/hetero_cache.py`` that the decode tier needs:
 ``cache_num_layers`` (:36), ``cache_seq_len`` (:40), ``value_norm_signal`` (:98), ``topk_per_head`` (:157),
@@ -22,14 +23,36 @@ from . import quant
 #: rows longer than this exceed the shared memory of the rank-counting top-k kernel
 
 
+def _per_layer_lists(cache) -> bool:
+    return hasattr(cache, "key_cache") and hasattr(cache, "value_cache")
+
+
 def cache_num_layers(cache) -> int:
-    return len(cache.key_cache)
+    return len(cache.key_cache) if _per_layer_lists(cache) else len(cache.layers)
+
+
+def layer_kv(cache, layer_idx: int):
+    """``(K, V)`` of one layer, ``(None, None)`` if the layer holds nothing yet."""
+    if _per_layer_lists(cache):
+        if len(cache.key_cache) <= layer_idx:
+            return None, None
+        return cache.key_cache[layer_idx], cache.value_cache[layer_idx]
+    if len(cache.layers) <= layer_idx:
+        return None, None
+    layer = cache.layers[layer_idx]
+    return getattr(layer, "keys", None), getattr(layer, "values", None)
+
+
+def set_layer_kv(cache, layer_idx: int, key: torch.Tensor, value: torch.Tensor) -> None:
+    if _per_layer_lists(cache):
+        cache.key_cache[layer_idx], cache.value_cache[layer_idx] = key, value
+    else:
+        cache.layers[layer_idx].keys, cache.layers[layer_idx].values = key, value
 
 
 def cache_seq_len(cache, layer_idx: int = 0) -> int:
-    if len(cache.key_cache) <= layer_idx or cache.key_cache[layer_idx] is None:
-        return 0
-    return cache.key_cache[layer_idx].shape[-2]
+    key, _ = layer_kv(cache, layer_idx)
+    return 0 if key is None else key.shape[-2]
 
 
 def num_kv_heads_of(model_config) -> int:
@@ -136,12 +159,11 @@ def evict_per_head(cache, keep_indices: Sequence[Optional[torch.Tensor]]):
         idx = keep_indices[layer]
         if idx is None:
             continue
-        k = cache.key_cache[layer]
+        k, v = layer_kv(cache, layer)
         idx = torch.sort(idx.to(device=k.device, dtype=torch.long), dim=-1).values
         if idx.numel() and (int(idx.min()) < 0 or int(idx.max()) >= k.shape[2]):
             raise ValueError(f"layer {layer}: keep_indices must lie in [0, {k.shape[2]})")
-        cache.key_cache[layer] = gather_tokens(k, idx)
-        cache.value_cache[layer] = gather_tokens(cache.value_cache[layer], idx)
+        set_layer_kv(cache, layer, gather_tokens(k, idx), gather_tokens(v, idx))
     return cache
 
 
@@ -166,9 +188,10 @@ class HeteroTierState:
 
     def logical_bytes(self, cache) -> int:
         """Bytes the three tiers would take at their bit widths (the physical tensors stay 16-bit)."""
-        if cache_num_layers(cache) == 0 or cache.key_cache[0] is None:
+        first_key = layer_kv(cache, 0)[0] if cache_num_layers(cache) else None
+        if first_key is None:
             return 0
-        b, hkv, seq, head_dim = cache.key_cache[0].shape
+        b, hkv, seq, head_dim = first_key.shape
         layers = cache_num_layers(cache)
         k0 = max(0, min(self.prompt_len_phys, seq))
         cold = max(0, min(self.cold_len, seq - k0))

@@ -158,25 +158,30 @@ def decode_attention_packed(q: torch.Tensor, packed_k: PackedTensor, packed_v: P
     return decode_attention_packed_splitk(q, packed_k, packed_v, num_attention_heads, 1, block_n)
 
 
+def _split_request(num_splits: Optional[int], length: int) -> Optional[int]:
+    return None if num_splits is None else max(1, min(int(num_splits), length))
+
+
 def decode_attention_packed_splitk(q: torch.Tensor, packed_k: PackedTensor, packed_v: PackedTensor,
-                                   num_attention_heads: int, num_splits: int = 8,
+                                   num_attention_heads: int, num_splits: Optional[int] = 8,
                                    block_n: int = 64) -> torch.Tensor:
-    """Split-K flash-decoding over one per-token-layout segment."""
+    """Split-K flash-decoding over one per-token-layout segment.  ``num_splits`` is honoured as given (the
+    reference's default of 8 leaves most of a large GPU idle); ``None`` lets the library size the grid."""
     hkv, S, hd = packed_k.orig_shape
     q = _check_query(q, num_attention_heads, hd, hkv)
     vpb, gs = _vals_per_byte(packed_k.bits), packed_k.group_size
     if hd % vpb != 0 or hd % gs != 0:
         raise ValueError(f"head_dim({hd}) must be divisible by vpb({vpb}) and group_size({gs})")
-    seg, keep = _packed_segment(packed_k, packed_v, max(1, min(int(num_splits), S)))
+    seg, keep = _packed_segment(packed_k, packed_v, _split_request(num_splits, S))
     out, _ = _run_decode(q, [seg], keep, num_attention_heads, hkv, True, False)
     return out
 
 
-def _three_tier_segments(kv, num_splits: int):
+def _three_tier_segments(kv, num_splits: Optional[int]):
     segs, keep, hkv, hd = [], [], None, None
     for k, v in ((kv.prompt_k, kv.prompt_v), (kv.cold_k, kv.cold_v)):
         if k is not None:
-            s, kp = _packed_segment(k, v, max(1, min(int(num_splits), k.orig_shape[1])))
+            s, kp = _packed_segment(k, v, _split_request(num_splits, k.orig_shape[1]))
             segs.append(s), keep.extend(kp)
             hkv, _, hd = k.orig_shape
     if kv.hot_k is not None and kv.hot_k.shape[-2] > 0:
@@ -188,9 +193,10 @@ def _three_tier_segments(kv, num_splits: int):
     return segs, keep, hkv, hd
 
 
-def fused_three_tier_decode(q, kv, num_attention_heads, num_splits: int = 8, block_n: int = 64):
+def fused_three_tier_decode(q, kv, num_attention_heads, num_splits: Optional[int] = 8, block_n: int = 64):
     """One attention over [packed prompt] + [packed cold] + [float16 hot] (per-token layout,
-    ``kv`` a ``ThreeTierKV`` with ``[Hkv, len, hd]`` tiers).  Returns ``[Hq, hd]`` float16."""
+    ``kv`` a ``ThreeTierKV`` with ``[Hkv, len, hd]`` tiers).  Returns ``[Hq, hd]`` float16.  ``num_splits=None``
+    lets the library size the grid."""
     segs, keep, hkv, hd = _three_tier_segments(kv, num_splits)
     q = _check_query(q, num_attention_heads, hd, hkv)
     out, _ = _run_decode(q, segs, keep, num_attention_heads, hkv, True, False)

@@ -196,3 +196,52 @@ def test_prompt_selection_matches_the_reference():
             ties += 1
             assert torch.equal(chosen_votes(got), chosen_votes(want[l])), (i, l)
     assert ties <= 4
+
+
+@torch.inference_mode()
+def test_compressor_hooks_drive_a_transformers_cache_of_this_generation():
+    """PhaseKVCompressor.on_prefill / on_decode_step (compressor.py:134-148 of the reference) over the dense cache a
+    randomly initialised Qwen2 returns: whatever cache class the installed transformers uses (per-layer lists in 4.x,
+    layer objects in 5.x), the result equals the same hooks run on plain per-layer lists of the same tensors."""
+    transformers = pytest.importorskip("transformers")
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+    from phasekv_b200 import hetero_cache as hc
+    from phasekv_b200.compressor import PhaseKVCompressor
+    torch.manual_seed(3)
+    config = Qwen2Config(vocab_size=97, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, max_position_embeddings=256, attention_dropout=0.0, attn_implementation="eager")
+    model = Qwen2ForCausalLM(config).to("cuda", torch.float16).eval()
+    ids = torch.randint(1, 97, (1, 80), generator=torch.Generator().manual_seed(5)).cuda()
+    out = model(input_ids=ids, use_cache=True, output_attentions=True)
+    cache = out.past_key_values
+    settings = types.SimpleNamespace(prefill_keep_ratio=0.5, decode_keep_ratio=0.5, recent_window=4, sink_tokens=2, bits=2,
+                                     extra={"cold_bits": 4, "group_size": 16, "lazy_g": 4, "obs_window": 8, "pool_kernel": 5})
+    ours, plain = PhaseKVCompressor(settings), PhaseKVCompressor(settings)
+    lists = types.SimpleNamespace(key_cache=[hc.layer_kv(cache, l)[0].clone() for l in range(2)],
+                                  value_cache=[hc.layer_kv(cache, l)[1].clone() for l in range(2)])
+    ours.reset(config), plain.reset(config)
+    ours.on_prefill(cache, attentions=out.attentions, prompt_len=80, model_config=config)
+    plain.on_prefill(lists, attentions=out.attentions, prompt_len=80, model_config=config)
+    assert hc.cache_seq_len(cache) == 40 == ours.state.prompt_len_phys and cache.get_seq_length() == 40
+    token = out.logits[:, -1].argmax(-1, keepdim=True)
+    for step in range(12):
+        before = hc.cache_seq_len(cache)
+        step_out = model(input_ids=token, past_key_values=cache, use_cache=True,
+                         position_ids=torch.tensor([[80 + step]], device="cuda"))
+        assert hc.cache_seq_len(cache) == before + 1
+        for l in range(2):       # the plain lists receive the very same new token
+            k, v = hc.layer_kv(cache, l)
+            lists.key_cache[l] = torch.cat([lists.key_cache[l], k[:, :, -1:, :]], dim=2)
+            lists.value_cache[l] = torch.cat([lists.value_cache[l], v[:, :, -1:, :]], dim=2)
+        ours.on_decode_step(cache, step=step, model_config=config)
+        plain.on_decode_step(lists, step=step, model_config=config)
+        token = step_out.logits[:, -1].argmax(-1, keepdim=True)
+        assert torch.isfinite(step_out.logits).all()
+    assert ours.state.cold_len == plain.state.cold_len > 0
+    for l in range(2):
+        k, v = hc.layer_kv(cache, l)
+        assert torch.equal(k, lists.key_cache[l]) and torch.equal(v, lists.value_cache[l])
+    assert ours.cache_memory_bytes(cache) == plain.cache_memory_bytes(lists) > 0
+    assert ours.describe()["phasekv"]["cold_bits"] == 4
+    with pytest.raises(ValueError):
+        PhaseKVCompressor(types.SimpleNamespace(extra={"use_planner": True}))
