@@ -110,8 +110,11 @@ def _exact_attention(oracle, q, key, value, heads):
         codes = oracle.unpack_low_bits(pt.packed, pt.bits, pt.axis_len).double()
         groups = torch.arange(pt.axis_len) // pt.group_size
         return (codes * pt.scale.double()[..., groups] + pt.mins.double()[..., groups]).movedim(-1, pt.axis)
-    rep = heads // key.orig_shape[1]
-    dk, dv = dense(key)[0].repeat_interleave(rep, 0), dense(value)[0].repeat_interleave(rep, 0)
+    dk, dv = dense(key), dense(value)
+    if dk.ndim == 4:  # a batch dimension of one
+        dk, dv = dk[0], dv[0]
+    rep = heads // dk.shape[0]
+    dk, dv = dk.repeat_interleave(rep, 0), dv.repeat_interleave(rep, 0)
     probs = torch.softmax(torch.einsum("hd,hsd->hs", q.double(), dk) / q.shape[-1] ** 0.5, dim=-1)
     return torch.einsum("hs,hsd->hd", probs, dv).float()
 
@@ -240,6 +243,65 @@ def test_per_token_layout_entry_points(oracle, attn, bits):
     kv = ThreeTierKV(to_gpu_packed(pk), to_gpu_packed(pv), to_gpu_packed(ck), to_gpu_packed(cv), Kh.cuda(), Vh.cuda())
     attention_close(attn.fused_three_tier_decode(q.cuda(), kv, hq), ref3)
     attention_close(attn.fused_three_tier_decode_single(q.cuda(), kv, hq), ref3)
+
+
+# (bits, Hq, S) -> the per-token cases beyond the 2e-3 bar, as in RAGGED_EXCEPTIONS: the oracle's own float16
+# rounding of the dequantised keys (keys with x8 outlier channels, a 64-token context) puts IT 3.0e-3 from the exact
+# attention; the kernel is 6.1e-4 from it.
+PER_TOKEN_EXCEPTIONS = {(4, 28, 64): {"kernel_vs_oracle": 3.17e-3, "oracle_vs_exact": 2.97e-3}}
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+@pytest.mark.parametrize("hq,hkv", [(28, 4), (8, 4), (32, 4)])
+def test_per_token_layout_sizes_splits_and_outlier_channels(oracle, attn, bits, hq, hkv):
+    """The tensor-core kernel of the per-token layout: lengths on and off the 64-token tile grid (odd lengths make
+    the scale rows of odd heads 8-byte aligned only), one token, library-sized and forced grids, GQA groups of
+    7, 2 and 8, keys with outlier channels (which make the softmax peaky: the hard case for the probabilities).
+    Every case is held to the parity bar against the oracle except the enumerated one, and every case to 1.5e-3
+    from the exact float64 attention over the codes."""
+    gen = torch.Generator().manual_seed(bits * 100 + hq)
+    for S, splits in ((1, None), (31, 8), (64, None), (65, 1), (1501, None), (4113, 128), (20000, None), (20000, 3)):
+        K, V = torch.randn(hkv, S, 128, generator=gen).half(), torch.randn(hkv, S, 128, generator=gen).half()
+        K[:, :, [5, 40, 77, 100]] *= 8
+        q = torch.randn(hq, 128, generator=gen).half()
+        pk, pv = oracle.quantize_pack(K, bits, -1, 32), oracle.quantize_pack(V, bits, -1, 32)
+        ref = oracle.attention_dense(q, oracle.unpack_dequantize(pk), oracle.unpack_dequantize(pv), hq).float()
+        exact = _exact_attention(oracle, q, pk, pv, hq)
+        out = attn.decode_attention_packed_splitk(q.cuda(), to_gpu_packed(pk), to_gpu_packed(pv), hq,
+                                                  num_splits=splits).float().cpu()
+        where = f"S={S} bits={bits} Hq={hq}"
+        e_exact, e_oracle = (out - exact).abs().max().item(), (out - ref).abs().max().item()
+        assert e_exact <= 1.5e-3, f"{where}: {e_exact:.2e} from the exact attention"
+        known = PER_TOKEN_EXCEPTIONS.get((bits, hq, S))
+        if known is None:
+            attention_close(out, ref)
+        else:
+            assert e_oracle <= known["kernel_vs_oracle"] * 1.05, f"{where}: {e_oracle:.2e} from the oracle"
+            assert e_exact < (ref - exact).abs().max().item(), f"{where}: the kernel should be nearer the exact result"
+
+
+def test_per_token_and_kivi_segments_in_one_call_use_the_general_kernel(oracle, attn):
+    """No caller of the reference mixes the two layouts in one attention; the C entry point still takes such a list
+    (the per-token segments are then served by the general kernel) and the result is the same attention."""
+    import ctypes
+
+    from phasekv_b200 import _native as nv
+    gen = torch.Generator().manual_seed(77)
+    hkv, hq, hd = 4, 28, 128
+    K1, V1 = torch.randn(hkv, 700, hd, generator=gen).half(), torch.randn(hkv, 700, hd, generator=gen).half()
+    K2, V2 = torch.randn(hkv, 300, hd, generator=gen).half(), torch.randn(hkv, 300, hd, generator=gen).half()
+    q = torch.randn(hq, hd, generator=gen).half()
+    k1, v1 = oracle.quantize_pack(K1, 2, -2, 32), oracle.quantize_pack(V1, 2, -1, 32)      # KIVI
+    k2, v2 = oracle.quantize_pack(K2, 4, -1, 32), oracle.quantize_pack(V2, 4, -1, 32)      # per token
+    k_all = torch.cat([oracle.unpack_dequantize(k1), oracle.unpack_dequantize(k2)], dim=1)
+    v_all = torch.cat([oracle.unpack_dequantize(v1), oracle.unpack_dequantize(v2)], dim=1)
+    ref = oracle.attention_dense(q, k_all, v_all, hq)
+    from phasekv_b200.kernels import attention_cuda
+    s1, keep1 = attention_cuda._packed_segment(to_gpu_packed(k1), to_gpu_packed(v1), None)
+    s2, keep2 = attention_cuda._packed_segment(to_gpu_packed(k2), to_gpu_packed(v2), None)
+    assert (s1.kind, s2.kind) == (nv.PKV_SEG_KIVI, nv.PKV_SEG_PER_TOKEN)
+    out, _ = attention_cuda._run_decode(q.cuda(), [s1, s2], [keep1, keep2], hq, hkv, True, False)
+    attention_close(out, ref)
 
 
 def test_partials_merge_like_the_reference_algebra(oracle, attn):
