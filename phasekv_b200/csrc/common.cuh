@@ -60,4 +60,37 @@ __device__ __forceinline__ float quantise_round(float d, float sc, float inv_sc)
     return t;
 }
 
+// The same rounding for the hot loops of the pack kernels, without a branch per element.  Adding 1.5 * 2^23 to a
+// value in [0, 2^22) rounds it to an integer, ties to even, and leaves that integer in the low mantissa bits:
+// rint and the float-to-integer conversion in one addition.  `near` collects whether any product came within a
+// hair of a half-integer (see quantise_round): the caller then redoes its handful of elements with the real
+// division.  d >= 0 (a value minus its group's minimum), so only the upper clamp is needed, and the clamp may be
+// applied before rounding because rounding is monotonic.
+constexpr float kRoundMagic = 12582912.0f;
+//
+// How close is "a hair": the product is within 1.5 ulp of the quotient, so a margin of four ulp of the largest code
+// around the half-integers is safe, and it is narrow enough that the redo stays rare even though it is taken by a
+// whole warp when any of its lanes asks for it.
+template <int BITS>
+__device__ __forceinline__ constexpr float near_half() {
+    return BITS == 2 ? 0.499999f : BITS == 4 ? 0.499996f : 0.49994f;
+}
+template <int BITS>
+__device__ __forceinline__ unsigned quantise_bits(float d, float inv_sc, bool& near) {
+    constexpr float QMAX = (float)((1 << BITS) - 1);
+    const float r = fminf(d * inv_sc, QMAX);
+    const float b = r + kRoundMagic;
+    near |= fabsf(r - (b - kRoundMagic)) > near_half<BITS>();
+    return __float_as_uint(b);  // the code sits in the low bits
+}
+__device__ __forceinline__ unsigned quantise_exact(float d, float sc, float qmax) {
+    return (unsigned)fminf(fmaxf(rintf(__fdiv_rn(d, sc)), 0.f), qmax);
+}
+// bits [pos, pos + len) of `into` replaced by the low `len` bits of `field`
+__device__ __forceinline__ unsigned insert_bits(unsigned field, unsigned into, int pos, int len) {
+    unsigned r;
+    asm("bfi.b32 %0, %1, %2, %3, %4;" : "=r"(r) : "r"(field), "r"(into), "r"(pos), "r"(len));
+    return r;
+}
+
 }  // namespace pkv

@@ -113,17 +113,24 @@ template <int BITS>
 __device__ __forceinline__ unsigned long long quantise8(const uint4& raw, float lo, float sc, float inv) {
     constexpr float QMAX = (float)((1 << BITS) - 1);
     const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-    unsigned long long codes = 0ull;
+    float d[8];
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
         const float2 f = __half22float2(h2[c]);
-        float q0 = quantise_round(__fsub_rn(f.x, lo), sc, inv);
-        float q1 = quantise_round(__fsub_rn(f.y, lo), sc, inv);
-        q0 = fminf(fmaxf(q0, 0.f), QMAX);
-        q1 = fminf(fmaxf(q1, 0.f), QMAX);
-        codes |= (unsigned long long)((unsigned)q0 | ((unsigned)q1 << BITS)) << (2 * c * BITS);
+        d[2 * c] = __fsub_rn(f.x, lo);
+        d[2 * c + 1] = __fsub_rn(f.y, lo);
     }
-    return codes;
+    unsigned w[2] = {0u, 0u};
+    bool near = false;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        w[(i * BITS) / 32] = insert_bits(quantise_bits<BITS>(d[i], inv, near), w[(i * BITS) / 32], (i * BITS) % 32, BITS);
+    if (near) {  // rare: a product too close to a half-integer to trust; the whole word again with real divisions
+        w[0] = w[1] = 0u;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[(i * BITS) / 32] |= quantise_exact(d[i], sc, QMAX) << ((i * BITS) % 32);
+    }
+    return (unsigned long long)w[0] | ((unsigned long long)w[1] << 32);
 }
 
 // Fast path for the value layout: the axis is the contiguous last dimension (inner == 1), the group is 32
@@ -225,14 +232,24 @@ quantize_pack_keytile_kernel(const __half* __restrict__ x, int64_t A, int64_t in
 #pragma unroll
         for (int k = 0; k < WPG; ++k) w0[k] = w1[k] = 0u;
 #pragma unroll
-        for (int a = 0; a < 32; ++a) {
-            const float2 f = __half22float2(col[a * kStride]);
-            float q0 = quantise_round(__fsub_rn(f.x, lo0), sc0, inv0);
-            float q1 = quantise_round(__fsub_rn(f.y, lo1), sc1, inv1);
-            q0 = fminf(fmaxf(q0, 0.f), QMAX);
-            q1 = fminf(fmaxf(q1, 0.f), QMAX);
-            w0[(a * BITS) / 32] |= (unsigned)q0 << ((a * BITS) % 32);
-            w1[(a * BITS) / 32] |= (unsigned)q1 << ((a * BITS) % 32);
+        for (int k = 0; k < WPG; ++k) {  // one packed word (32 / BITS positions) of both channels at a time
+            constexpr int PER = 32 / BITS;
+            bool near = false;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) {
+                const float2 f = __half22float2(col[(k * PER + j) * kStride]);
+                w0[k] = insert_bits(quantise_bits<BITS>(__fsub_rn(f.x, lo0), inv0, near), w0[k], j * BITS, BITS);
+                w1[k] = insert_bits(quantise_bits<BITS>(__fsub_rn(f.y, lo1), inv1, near), w1[k], j * BITS, BITS);
+            }
+            if (near) {  // rare: some product was too close to a half-integer; the word again with real divisions
+                w0[k] = w1[k] = 0u;
+#pragma unroll 1
+                for (int j = 0; j < PER; ++j) {
+                    const float2 f = __half22float2(col[(k * PER + j) * kStride]);
+                    w0[k] |= quantise_exact(__fsub_rn(f.x, lo0), sc0, QMAX) << (j * BITS);
+                    w1[k] |= quantise_exact(__fsub_rn(f.y, lo1), sc1, QMAX) << (j * BITS);
+                }
+            }
         }
 #pragma unroll
         for (int k = 0; k < WPG; ++k) {
