@@ -13,6 +13,12 @@ point with q copied from pinned host memory and the output copied back, every st
 With more than one GPU (launched by torch.distributed.run) every rank decodes its own sequence
 (batch sharding, no collective); the reported time is the maximum over ranks.
 
+After the headline the same process measures, and adds to the JSON line under ``sharded``, the two configurations
+that shard over GPUs (``longctx``: 262144 prompt tokens sequence-sharded with one exchange of partials per layer;
+``serving``: 64 sequences batch-sharded) and, on one GPU, the quantise+pack kernels (``pack``), the one-launch
+attention of a chunk of new prompt tokens against the token-by-token order (``prompt_chunk``) and decode over a
+cold tier kept in arenas after 1000 generated tokens (``cold_arena``).
+
 ``--impl reference`` times the CPU restatement of the reference's dequantise-then-attend
 (oracle/) on the host cores for the same layer shape, one layer per step.
 """
@@ -36,8 +42,9 @@ UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the kernels of one layer (split-K + merge), per prompt length, from
 # ncu captures of this workload with a few layers (traffic per launch does not depend on the layer count).
-# A prompt length without a capture reports null.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {}
+# A prompt length without a capture reports null.  At 32768 tokens: split-K launch 13 140 736 + merge launch 508 160
+# (the capture summarised in profiles/decode_mma_kernel_qwen7b_32k.md).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {32768: 13648896}
 NCU_TRAFFIC_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum, split-K + merge kernels of one layer"
 
 
