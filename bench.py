@@ -7,8 +7,10 @@ packed prompt tier of ``--prompt`` tokens (default 32768), a 4-bit cold tier of 
 float16 hot tier of 128 tokens, batch 1, 28 query / 4 KV heads, head_dim 128.  The 28 layers own
 distinct KV buffers (364 MB at 32768 tokens, larger than the 126 MB L2), so a step streams its
 bytes from HBM.  ``value`` is algorithmic bytes per second with everything resident in HBM and
-the step replayed as a CUDA graph; ``e2e`` is the same step through the public Python entry
-point with q copied from pinned host memory and the output copied back, every step.
+the step replayed as a CUDA graph; ``e2e`` is the same step with host buffers: every step the queries are copied
+from pinned host memory, ``pkv_decode_attention`` is called once per layer through the C ABI (no graph), the outputs
+are copied back and the host waits for them (``e2e.python_entry_*``: the same through the reference-facing Python
+function ``fused_phasekv_decode`` with per-layer copies).
 
 With more than one GPU (launched by torch.distributed.run) every rank decodes its own sequence
 (batch sharding, no collective); the reported time is the maximum over ranks.
@@ -239,21 +241,7 @@ def time_graph(torch, fn, steps, warmup, barrier=None, sampler=None, agree_max=N
     return ms
 
 
-def time_e2e(torch, ls: LayerSet, device, steps, warmup):
-    """Public API per layer with host buffers: q from pinned memory, output back to pinned memory."""
-    from phasekv_b200.kernels.attention_triton import fused_phasekv_decode
-    s = ls.shape
-    q_host = [q.cpu().pin_memory() for q in ls.q]
-    o_host = [torch.empty_like(q).pin_memory() for q in q_host]
-    q_dev = [torch.empty_like(q) for q in ls.q]
-
-    def step():
-        for i in range(ls.layers):
-            q_dev[i].copy_(q_host[i], non_blocking=True)
-            o = fused_phasekv_decode(q_dev[i], ls.tiers[i], s.num_q_heads)
-            o_host[i].copy_(o, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
+def _timed_steps(torch, step, steps, warmup):
     for _ in range(warmup):
         step()
     torch.cuda.synchronize()
@@ -263,8 +251,51 @@ def time_e2e(torch, ls: LayerSet, device, steps, warmup):
         step()
     e1.record()
     e1.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def time_e2e(torch, ls: LayerSet, native: "NativeStep", device, steps, warmup):
+    """The step with HOST buffers, copies inside the timed region.  Two ways to call:
+
+    * `c_abi`: what a serving runtime does: every step the queries of all layers are copied from pinned host memory,
+      `pkv_decode_attention` is called once per layer (plain calls, no graph: the cache may have changed since the
+      last step), the outputs are copied back to pinned host memory, and the host waits for them;
+    * `python_entry`: the reference-facing Python function `fused_phasekv_decode(q, tiers, Hq)` per layer with a
+      host-to-device and a device-to-host copy per layer, as a caller of the reference's module would write it.
+
+    Returns (c_abi ms, python_entry ms, bytes in per step, bytes out per step, host outputs of the c_abi way)."""
+    from phasekv_b200.kernels.attention_triton import fused_phasekv_decode
+    s = ls.shape
+    nv, L = native.nv, native.L
+    q_host = torch.stack([q.cpu() for q in ls.q]).pin_memory()           # [layers, Hq, hd]
+    o_host = torch.empty_like(q_host).pin_memory()
+    q_dev, o_dev = torch.empty_like(q_host, device=device), torch.empty_like(q_host, device=device)
+    scale = 1.0 / (s.head_dim ** 0.5)
+
+    def step_c_abi():
+        q_dev.copy_(q_host, non_blocking=True)
+        stream = nv.stream_of(device)
+        for i, (arr, n) in enumerate(native.calls):
+            nv.check(L.pkv_decode_attention(q_dev[i].data_ptr(), arr, n, s.num_q_heads, s.num_kv_heads, s.head_dim, scale,
+                                            native.sms, native.ws.data_ptr(), native.ws.numel(), o_dev[i].data_ptr(),
+                                            None, None, None, stream))
+        o_host.copy_(o_dev, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    q_dev_l = [torch.empty_like(q) for q in ls.q]
+    o_host_l = [torch.empty_like(q).cpu().pin_memory() for q in ls.q]
+
+    def step_python():
+        for i in range(ls.layers):
+            q_dev_l[i].copy_(q_host[i], non_blocking=True)
+            o = fused_phasekv_decode(q_dev_l[i], ls.tiers[i], s.num_q_heads)
+            o_host_l[i].copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    ms_c = _timed_steps(torch, step_c_abi, steps, warmup)
+    ms_py = _timed_steps(torch, step_python, steps, warmup)
     per_step_bytes = ls.layers * s.num_q_heads * s.head_dim * 2
-    return e0.elapsed_time(e1) / steps, per_step_bytes, per_step_bytes, o_host
+    return ms_c, ms_py, per_step_bytes, per_step_bytes, o_host
 
 
 def sdpa_baselines(torch, device, prompt_len, layers, steps, warmup):
@@ -887,6 +918,97 @@ def measure_cold_arena(ctx, prompt_len, layers, generated=1000):
     return res
 
 
+def measure_adapter_layer(ctx, prompt_len=32768, chunk=64):
+    """One attention layer of Qwen2.5-7B geometry (hidden 3584, 28 query / 4 KV heads, random weights) over a PhaseKVCache,
+    through the adapter: projections, rotary embedding, append and attention.  `fused` is this package's adapter
+    (one rotary+convert+append launch, one launch pair of attention, also for a chunk of new prompt tokens);
+    `reference_order` performs the same layer the way the reference's adapter does (qwen2_attention.py:79-109):
+    torch rotary embedding, three conversions, then per token an append and a single-query attention call.
+    Wall-clock microseconds per layer call, host work included (the reference reports a 22 ms/token launch floor
+    for a whole model; this is the per-layer share of that floor)."""
+    torch, device = ctx.torch, ctx.device
+    try:
+        from transformers import Qwen2Config
+        from transformers.models.qwen2.modeling_qwen2 import Qwen2Attention, Qwen2RotaryEmbedding, apply_rotary_pos_emb
+    except Exception as exc:  # transformers is optional
+        return {"unavailable": f"transformers: {exc}"}
+    from phasekv_b200.kernels.attention_cuda import fused_phasekv_decode
+    from phasekv_b200.phasekv_cache import PhaseKVCache
+    from phasekv_b200.qwen2_attention import PhaseKVQwen2Attention
+    cfg = Qwen2Config(vocab_size=128, hidden_size=3584, intermediate_size=64, num_hidden_layers=1, num_attention_heads=28,
+                      num_key_value_heads=4, max_position_embeddings=prompt_len + 4096, attention_dropout=0.0,
+                      attn_implementation="eager")
+    torch.manual_seed(0)
+    attn = PhaseKVQwen2Attention(Qwen2Attention(cfg, 0).to(device, torch.float16).eval()).eval()
+    rotary = Qwen2RotaryEmbedding(cfg).to(device)
+
+    def fresh_cache():
+        cache = PhaseKVCache.from_dense_prefill(_random_prefill(torch, device, 1, prompt_len, 9), prompt_len=prompt_len)
+        g = torch.Generator(device=device).manual_seed(11)   # both variants see the same cache and inputs
+        for _ in range(40):
+            k = torch.randn(1, 4, 1, 128, device=device, dtype=torch.float16, generator=g)
+            cache.append_hot(0, k, k)
+            cache.finish_decode_step()
+        return cache, g
+
+    def fused(cache, hidden, positions):
+        pe = rotary(hidden, positions)
+        return attn(hidden, position_embeddings=pe, past_key_values=cache, use_cache=True)[0]
+
+    def reference_order(cache, hidden, positions):
+        base = attn.original
+        n = hidden.shape[1]
+        q = base.q_proj(hidden).view(1, n, 28, 128).transpose(1, 2)
+        k = base.k_proj(hidden).view(1, n, 4, 128).transpose(1, 2)
+        v = base.v_proj(hidden).view(1, n, 4, 128).transpose(1, 2)
+        cos, sin = rotary(hidden, positions)
+        q, k = apply_rotary_pos_emb(q, k, cos, sin)
+        q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
+        append = cache.append_prompt_token if cache.prompt_chunk_len else cache.append_hot
+        tiers = cache.layer_tiers(0)
+        outs = []
+        for i in range(n):
+            append(0, k[:, :, i:i + 1, :], v[:, :, i:i + 1, :])
+            outs.append(fused_phasekv_decode(q[0, :, i, :], tiers, 28))
+        return base.o_proj(torch.stack(outs, 0).reshape(1, n, 3584))
+    res = {"config": {"workload": "one attention layer through the model adapter, Qwen2.5-7B geometry", "prompt_tokens": prompt_len,
+                      "chunk_tokens": chunk, "timed_as": "wall clock per call incl. host work: best of three blocks of 20 decode steps; mean of 5 chunks"}}
+    with torch.inference_mode():
+        for name, fn in (("fused", fused), ("reference_order", reference_order)):
+            cache, g = fresh_cache()
+            hidden = torch.randn(1, 1, 3584, device=device, dtype=torch.float16, generator=g)
+            blocks = []
+            for block in range(4):      # the first block warms up (lazy initialisation, the first cooling step's arena)
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for rep in range(20):
+                    pos = torch.tensor([[cache.true_seq_length]], device=device)
+                    last = fn(cache, hidden, pos)
+                    cache.finish_decode_step()
+                torch.cuda.synchronize()
+                blocks.append((time.perf_counter() - t0) / 20 * 1e6)
+            res[f"decode_{name}_us"] = min(blocks[1:])
+            last_decode = last.float()
+            hidden = torch.randn(1, chunk, 3584, device=device, dtype=torch.float16, generator=g)
+            for rep in range(7):
+                pos = torch.arange(cache.true_seq_length, cache.true_seq_length + chunk, device=device).unsqueeze(0)
+                if rep == 2:
+                    torch.cuda.synchronize()
+                    t0 = time.perf_counter()
+                cache.begin_prompt_chunk(chunk)
+                out = fn(cache, hidden, pos)
+                cache.finish_prompt_chunk()
+            torch.cuda.synchronize()
+            res[f"chunk_{name}_us"] = (time.perf_counter() - t0) / 5 * 1e6
+            res[f"_{name}"] = (last_decode, out.float())
+        res["max_abs_diff_decode"] = float((res["_fused"][0] - res["_reference_order"][0]).abs().max())
+        res["max_abs_diff_chunk"] = float((res["_fused"][1] - res["_reference_order"][1]).abs().max())
+        del res["_fused"], res["_reference_order"]
+    res["decode_speedup"] = res["decode_reference_order_us"] / res["decode_fused_us"]
+    res["chunk_speedup"] = res["chunk_reference_order_us"] / res["chunk_fused_us"]
+    return res
+
+
 def sharded_block(ctx, args):
     """The two configurations that shard over GPUs (sequence-sharded long context, batch-sharded serving) and, on
     one GPU, the pack kernels, measured in the same process group after the headline.  A workload that fails
@@ -910,7 +1032,8 @@ def sharded_block(ctx, args):
         except Exception as exc:
             block["pack"] = {"error": f"{type(exc).__name__}: {exc}"}
         for name, fn in (("prompt_chunk", lambda: [measure_prompt_chunk(ctx, 4096, 64), measure_prompt_chunk(ctx, args.prompt, 64)]),
-                         ("cold_arena", lambda: measure_cold_arena(ctx, args.prompt, args.layers))):
+                         ("cold_arena", lambda: measure_cold_arena(ctx, args.prompt, args.layers)),
+                         ("adapter_layer", lambda: measure_adapter_layer(ctx, args.prompt, 64))):
             try:
                 block[name] = fn()
             except Exception as exc:
@@ -927,8 +1050,8 @@ def measure_decode(ctx, args):
     torch.cuda.synchronize()
     clocks = ClockSampler(ctx.local_rank)
     ms = time_graph(torch, native.run, args.steps, max(args.warmup, 3), ctx.barrier, sampler=clocks)
-    ms_e2e, h2d, d2h, o_host = time_e2e(torch, ls, device, max(3, min(args.steps, 20)), 3)
-    ms, ms_e2e = ctx.max_over_ranks([ms, ms_e2e])
+    ms_e2e, ms_e2e_py, h2d, d2h, o_host = time_e2e(torch, ls, native, device, max(3, min(args.steps, 20)), 3)
+    ms, ms_e2e, ms_e2e_py = ctx.max_over_ranks([ms, ms_e2e, ms_e2e_py])
     step_bytes = ls.bytes_per_layer * ls.layers * world
     value = step_bytes / (ms * 1e-3) / 1e9
     e2e_value = step_bytes / (ms_e2e * 1e-3) / 1e9
@@ -943,7 +1066,11 @@ def measure_decode(ctx, args):
         "us_per_layer": per_launch_ms * 1e3,
         "pct_of_8TBps": 100.0 * achieved / 8000.0,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": ms_e2e},
+                "ms_per_step": ms_e2e,
+                "called_as": "pkv_decode_attention per layer (C ABI, no graph), q of the step copied from pinned host "
+                             "memory, outputs copied back, host waits",
+                "python_entry_ms_per_step": ms_e2e_py,
+                "python_entry_value": step_bytes / (ms_e2e_py * 1e-3) / 1e9},
         "gpu_launches": native.launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.prompt), "traffic_source": NCU_TRAFFIC_SOURCE,

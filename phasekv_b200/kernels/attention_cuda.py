@@ -380,8 +380,13 @@ def fused_phasekv_decode(q: torch.Tensor, tiers, num_attention_heads: int,
     # and the scratch size are kept on the tiers object and reused while every segment object, the hot buffers
     # and the hot length are the same.
     hot = tiers.hot_k if tiers.hot_len else None
-    tag = (tuple((id(s), s.key.packed.data_ptr()) for s in (tiers.prompt, *tiers.prompt_extensions, *tiers.cold)),
-           None if hot is None else (hot.data_ptr(), tiers.hot_v.data_ptr(), tuple(hot.shape), hot.stride()),
+    cold = tiers.cold
+    # frozen segments are only ever appended to their lists, so the lists' lengths and last members identify them
+    # (a caller that swaps a segment in the middle of a list gets a new LayerTiers, as the cache's reorder does)
+    last = cold[-1] if cold else (tiers.prompt_extensions[-1] if tiers.prompt_extensions else tiers.prompt)
+    tag = (id(tiers.prompt), tiers.prompt.key.packed.data_ptr(), len(tiers.prompt_extensions), len(cold), id(last),
+           last.key.packed.data_ptr(),
+           None if hot is None else (hot.data_ptr(), tiers.hot_v.data_ptr(), hot.shape[2], hot.stride(1)),
            num_splits, num_attention_heads)
     cached = getattr(tiers, "_pkv_call", None)
     fresh = ()

@@ -283,12 +283,13 @@ class PhaseKVCache(_CacheBase):
     def finish_decode_step(self) -> None:
         """Once per single-token forward pass: cool what has aged out, then advance the true length by one."""
         self._refuse_inside_chunk("call finish_prompt_chunk(), not finish_decode_step()")
-        missing = sorted(set(range(len(self.layers))) - self._written)
-        if missing:
+        if len(self._written) != len(self.layers):
+            missing = sorted(set(range(len(self.layers))) - self._written)
             raise RuntimeError(f"finish_decode_step() needs one token in 每一层 (every layer); 尚未追加的层为 {missing}")
-        lengths = {(layer.physical_len, layer.hot_len) for layer in self.layers}
-        if len(lengths) != 1:
-            raise RuntimeError(f"(physical, hot) lengths differ between layers before cooling: {sorted(lengths)}")
+        # all layers move in lockstep; the cheap signature first (physical_len walks every cold segment)
+        if len({(layer.hot_len, len(layer.cold), len(layer.prompt_extensions)) for layer in self.layers}) != 1:
+            lengths = sorted({(layer.physical_len, layer.hot_len) for layer in self.layers})
+            raise RuntimeError(f"(physical, hot) lengths differ between layers before cooling: {lengths}")
         self._cool_aged_tokens()
         self._seen_tokens += 1
         self._written.clear()
