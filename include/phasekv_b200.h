@@ -141,6 +141,11 @@ int pkv_decode_launches(const pkv_segment_t* segs /* host */, int n_segs, int nu
  * single-query attention of q float16 [Hq, hd] over the concatenation of `segs`, without ever
  * writing dequantised K/V to memory.  One split-K launch covers all segments (more than 24 segments, or
  * segments that only the layout-generic kernel takes, add launches), one merge launch follows.
+ * Which kernel serves a segment: with head_dim 128, a GQA group of at most 8, 16-byte aligned buffers, equal
+ * K and V widths and groups of 32, PKV_SEG_KIVI and PKV_SEG_FP16 segments go to the tensor-core kernel, and so do
+ * PKV_SEG_PER_TOKEN segments (a kernel of their own) unless the same call also holds a PKV_SEG_KIVI segment;
+ * everything else goes to the general kernel (any head_dim <= 256 that is a multiple of 4, any group sizes,
+ * different K and V widths).  The result does not depend on the route beyond rounding.
  * Outputs (each may be NULL):
  *   out  float16 [Hq, hd]  = acc / l
  *   m, l float32 [Hq], acc float32 [Hq, hd]: the un-normalised partial of attention_triton.py:257-266,
@@ -175,7 +180,7 @@ int pkv_decode_attention_static(const void* q, const pkv_segment_t* segs /* host
  * position-independent table (segment descriptors, work list, per-sequence ranges of partials) into `table`
  * (host memory, 16-byte aligned).  `table_bytes` receives the bytes used, `workspace_bytes` the device scratch
  * the launch needs.  With table == NULL only the two sizes are computed.  Every segment must be one the
- * tensor-core kernel takes (KIVI layout with head_dim 128, group 32, equal K/V bits, or float16; GQA group
+ * tensor-core kernel takes (KIVI layout with head_dim 128, group 32, equal K/V bits, or float16, not the per-token layout; GQA group
  * <= 8; 16-byte aligned buffers), otherwise PKV_E_LAYOUT: serve such sequences one by one.
  * PKV_E_WORKSPACE when table_capacity is too small.  The plan depends on lengths and pointers only, so it
  * stays valid until one of them changes.

@@ -186,3 +186,70 @@ def test_batch_plan_covers_every_tile_once():
     bad = (nv.Segment * 1)(nv.Segment(*[0x1000 * (k + 1) for k in range(6)], 64, 0, nv.PKV_SEG_PER_TOKEN, 4, 4, 32, 32, 0))
     one = (ctypes.c_int32 * 2)(0, 1)
     assert L.pkv_decode_batch_plan(bad, one, 1, 28, 4, 128, 148, None, 0, ctypes.byref(tb), ctypes.byref(wb)) == nv.PKV_E_LAYOUT
+
+
+def test_chunk_plan_applies_the_causal_rule_by_length():
+    """pkv_decode_chunk_plan is host-only: query i of a chunk of N new tokens must see every packed segment in full
+    and the float16 tier up to and including its own token (seq_len - (N - 1 - i) tokens)."""
+    import struct
+
+    from phasekv_b200 import _native as nv
+    L = nv.lib()
+    base = 0x20000000
+    prompt = nv.Segment(*(base + 0x100000 * k for k in range(6)), 4096, 0, nv.PKV_SEG_KIVI, 2, 2, 32, 32, 0)
+    arena = nv.Segment(*(base + 0x1000000 + 0x100000 * k for k in range(6)), 5 * 32, 64 * 32, nv.PKV_SEG_KIVI, 4, 4, 32, 32, 0,
+                       64 * 16, 64, 0, 32, 8)
+    hot = nv.Segment(base + 0x2000000, None, None, base + 0x2100000, None, None, 45, 96 * 128, nv.PKV_SEG_FP16, 8, 8, 1, 1, 0)
+    arr = (nv.Segment * 3)(prompt, arena, hot)
+    n = 7
+    tb, wb = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    nv.check(L.pkv_decode_chunk_plan(arr, 3, n, 28, 4, 128, 148, None, 0, ctypes.byref(tb), ctypes.byref(wb)))
+    buf = ctypes.create_string_buffer(tb.value + 16)
+    addr = (ctypes.addressof(buf) + 15) & ~15
+    nv.check(L.pkv_decode_chunk_plan(arr, 3, n, 28, 4, 128, 148, addr, tb.value, ctypes.byref(tb), ctypes.byref(wb)))
+    raw = ctypes.string_at(addr, tb.value)
+    magic, batch, n_segs, n_work, n_parts, hq, hkv, hd, o_segs, o_work, o_ranges, nbytes = struct.unpack_from("<I7i4I", raw)
+    assert (magic, batch, n_segs) == (0x42564B50, n, 3 * n) and wb.value == n_parts * 28 * 130 * 4
+    seg_bytes = (o_work - o_segs) // n_segs
+    assert seg_bytes * n_segs <= o_work - o_segs and seg_bytes >= 7 * 8
+    lengths = [struct.unpack_from("<q", raw, o_segs + seg_bytes * i + 6 * 8)[0] for i in range(n_segs)]  # after six pointers
+    for i in range(n):
+        assert lengths[3 * i:3 * i + 3] == [4096, 5 * 32, 45 - (n - 1 - i)], i
+    # every query owns a contiguous range of partials, and all work items point at its own three segments
+    for w in range(n_work):
+        seg, seq, t0, nt, part = struct.unpack_from("<5i", raw, o_work + 32 * w)
+        assert seg // 3 == seq and nt > 0
+    # the chunk cannot be longer than the float16 tier, and the last segment must be that tier
+    assert L.pkv_decode_chunk_plan(arr, 3, 46, 28, 4, 128, 148, None, 0, ctypes.byref(tb), ctypes.byref(wb)) == nv.PKV_E_SHAPE
+    assert L.pkv_decode_chunk_plan(arr, 2, 1, 28, 4, 128, 148, None, 0, ctypes.byref(tb), ctypes.byref(wb)) == nv.PKV_E_SHAPE
+    assert L.pkv_decode_chunk_plan(None, 3, 1, 28, 4, 128, 148, None, 0, ctypes.byref(tb), ctypes.byref(wb)) == nv.PKV_E_NULL
+    # a layout the tensor-core kernel does not take: the caller serves the chunk query by query
+    hot64 = nv.Segment(base, None, None, base + 0x100000, None, None, 9, 96 * 64, nv.PKV_SEG_FP16, 8, 8, 1, 1, 0)
+    assert L.pkv_decode_chunk_plan((nv.Segment * 1)(hot64), 1, 3, 14, 2, 64, 148, None, 0, ctypes.byref(tb),
+                                   ctypes.byref(wb)) == nv.PKV_E_LAYOUT
+
+
+def test_adapter_and_cooling_entry_points_check_arguments_first():
+    from phasekv_b200 import _native as nv
+    L = nv.lib()
+    p = 0x30000000
+    ok = dict(q=p, k=p, v=p, dtype=nv.PKV_DTYPE_F16, qs=28 * 128, ks=4 * 128, vs=4 * 128, cos=p, sin=p, rdt=nv.PKV_DTYPE_F32,
+              rs=128, n=3, hq=28, hkv=4, hd=128, qo=p, hk=p, hv=p, cap=48, slot=10)
+
+    def rope(**over):
+        a = dict(ok, **over)
+        return L.pkv_rope_append(a["q"], a["k"], a["v"], a["dtype"], a["qs"], a["ks"], a["vs"], a["cos"], a["sin"], a["rdt"],
+                                 a["rs"], a["n"], a["hq"], a["hkv"], a["hd"], a["qo"], a["hk"], a["hv"], a["cap"], a["slot"], None)
+    assert rope(q=None) == nv.PKV_E_NULL and rope(hv=None) == nv.PKV_E_NULL
+    assert rope(n=0) == nv.PKV_E_SHAPE and rope(hd=63) == nv.PKV_E_SHAPE
+    assert rope(slot=46) == nv.PKV_E_SHAPE          # three tokens do not fit behind slot 46 of 48
+    assert rope(qs=100) == nv.PKV_E_SHAPE           # a token stride shorter than a token
+    assert rope(dtype=nv.PKV_DTYPE_F32) == nv.PKV_E_LAYOUT
+    # cooling of all layers: (layers, n_layers, rows, capacity, hd, hot_len, aged, keep, bits, group, pitches..., offsets...)
+    def cool(layers=p, n_layers=2, rows=4, capacity=48, hd=128, hot_len=48, aged=16, keep=8, bits=4, group=32):
+        return L.pkv_cold_select_pack_layers(layers, n_layers, rows, capacity, hd, hot_len, aged, keep, bits, group,
+                                             64 * 16, 64, 64 * 32, 0, 0, 0, None)
+    assert cool(layers=None) == nv.PKV_E_NULL
+    assert cool(n_layers=0) == nv.PKV_E_LIMIT
+    assert cool(bits=3) == nv.PKV_E_BITS
+    assert cool(keep=17) == nv.PKV_E_SHAPE and cool(hot_len=49) == nv.PKV_E_SHAPE
