@@ -18,8 +18,9 @@ With more than one GPU (launched by torch.distributed.run) every rank decodes it
 After the headline the same process measures, and adds to the JSON line under ``sharded``, the two configurations
 that shard over GPUs (``longctx``: 262144 prompt tokens sequence-sharded with one exchange of partials per layer;
 ``serving``: 64 sequences batch-sharded) and, on one GPU, the quantise+pack kernels (``pack``), the one-launch
-attention of a chunk of new prompt tokens against the token-by-token order (``prompt_chunk``) and decode over a
-cold tier kept in arenas after 1000 generated tokens (``cold_arena``).
+attention of a chunk of new prompt tokens against the token-by-token order (``prompt_chunk``), decode over a
+cold tier kept in arenas after 1000 generated tokens (``cold_arena``), one attention layer through the model adapter
+(``adapter_layer``) and a whole decode step of the attention path replayed from one CUDA graph (``graphed_step``).
 
 ``--impl reference`` times the CPU restatement of the reference's dequantise-then-attend
 (oracle/) on the host cores for the same layer shape, one layer per step.
@@ -1009,6 +1010,56 @@ def measure_adapter_layer(ctx, prompt_len=32768, chunk=64):
     return res
 
 
+def measure_graphed_step(ctx, prompt_len, layers, tokens=200):
+    """A whole decode step of the attention path (per layer: rotary embedding + float16 conversion + append, then
+    attention over all tiers; at the end of the step the reference's lazy cooling) for `tokens` generated tokens:
+    `graphed`: the step's launches captured once with device-resident lengths and replayed per token
+    (phasekv_b200.graph_step); `eager`: the same through append_rotated + fused_phasekv_decode per layer.
+    Wall clock per token, host work and cooling steps included; q, k, v of the token are already on the device."""
+    torch, device = ctx.torch, ctx.device
+    from phasekv_b200.graph_step import GraphedDecodeStep
+    from phasekv_b200.kernels.attention_cuda import fused_phasekv_decode
+    from phasekv_b200.phasekv_cache import PhaseKVCache
+    g = torch.Generator(device=device).manual_seed(3)
+    q = torch.randn(layers, 28, 128, device=device, dtype=torch.float16, generator=g)
+    k = torch.randn(layers, 4, 128, device=device, dtype=torch.float16, generator=g)
+    v = torch.randn(layers, 4, 128, device=device, dtype=torch.float16, generator=g)
+    cos = torch.ones(128, device=device)
+    sin = torch.zeros(128, device=device)
+    res = {"config": {"workload": "decode step of the attention path incl. KV append and lazy cooling, all layers",
+                      "prompt_tokens": prompt_len, "layers": layers, "generated_tokens": tokens,
+                      "timed_as": "wall clock per token incl. host work"}}
+    outs = {}
+    for name in ("graphed", "eager"):
+        cache = PhaseKVCache.from_dense_prefill(_random_prefill(torch, device, layers, prompt_len, 4), prompt_len=prompt_len)
+        runner = GraphedDecodeStep(cache, 28) if name == "graphed" else None
+
+        def token():
+            if runner is not None:
+                return runner.step(q, k, v, cos, sin)
+            out = [fused_phasekv_decode(cache.append_rotated(l, q[l:l + 1], k[l:l + 1], v[l:l + 1], cos[None], sin[None])[0],
+                                        cache.layer_tiers(l), 28) for l in range(layers)]
+            cache.finish_decode_step()
+            return torch.stack(out)
+        for _ in range(20):
+            token()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(tokens):
+            last = token()
+        torch.cuda.synchronize()
+        res[f"{name}_us_per_token"] = (time.perf_counter() - t0) / tokens * 1e6
+        outs[name] = last.float().clone()
+        if runner is not None:
+            res["graph_captures"] = runner.captures
+        res["cold_steps"] = len(cache.layer_tiers(0).cold)
+        del cache, runner
+        torch.cuda.empty_cache()
+    res["max_abs_diff"] = float((outs["graphed"] - outs["eager"]).abs().max())
+    res["speedup"] = res["eager_us_per_token"] / res["graphed_us_per_token"]
+    return res
+
+
 def sharded_block(ctx, args):
     """The two configurations that shard over GPUs (sequence-sharded long context, batch-sharded serving) and, on
     one GPU, the pack kernels, measured in the same process group after the headline.  A workload that fails
@@ -1033,7 +1084,8 @@ def sharded_block(ctx, args):
             block["pack"] = {"error": f"{type(exc).__name__}: {exc}"}
         for name, fn in (("prompt_chunk", lambda: [measure_prompt_chunk(ctx, 4096, 64), measure_prompt_chunk(ctx, args.prompt, 64)]),
                          ("cold_arena", lambda: measure_cold_arena(ctx, args.prompt, args.layers)),
-                         ("adapter_layer", lambda: measure_adapter_layer(ctx, args.prompt, 64))):
+                         ("adapter_layer", lambda: measure_adapter_layer(ctx, args.prompt, 64)),
+                         ("graphed_step", lambda: measure_graphed_step(ctx, args.prompt, args.layers))):
             try:
                 block[name] = fn()
             except Exception as exc:

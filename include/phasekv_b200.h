@@ -115,6 +115,12 @@ typedef struct pkv_segment {
      * own group (see pkv_cold_select_pack_layers). */
     int16_t slot_tokens;
     int16_t slot_valid;
+    /* PKV_SEG_FP16 and PKV_SEG_KIVI; NULL = seq_len is the length.  Otherwise a DEVICE address of an int32 holding
+     * the number of tokens that count, read when the kernel runs (after everything earlier in the stream):
+     * min(seq_len, *seq_len_dev) tokens are attended to, and seq_len is the CAPACITY the launch is sized for.  This
+     * keeps a captured CUDA graph of decode calls valid while the float16 tier (or a run of cold slots) grows: the
+     * owner of the cache updates the int32 in stream order instead of re-describing the segment. */
+    const int32_t* seq_len_dev;
 } pkv_segment_t;
 
 /* The packed tensors of this segment may have been written by the kernel that was launched on `stream` directly
@@ -352,12 +358,15 @@ int pkv_gather_tokens(const void* src, void* dst, const int64_t* indices, int64_
  *   q_out float16 [n_tokens, Hq, hd] dense; hot_k / hot_v float16 [Hkv, capacity, hd]: token i goes to slot
  *   `slot` + i.
  * Rounded as torch rounds when the rotation runs in `dtype`: x*cos, rotate_half(x)*sin and their sum are each
- * rounded to `dtype`, then converted to float16. */
+ * rounded to `dtype`, then converted to float16.
+ * slot_dev (optional, DEVICE int32): when given, the first slot is *slot_dev + slot, read when the kernel runs, so
+ * that a captured graph keeps appending behind a growing tier; a slot outside [0, capacity - n_tokens] writes
+ * nothing to the tier (the rotated queries are still produced). */
 int pkv_rope_append(const void* q, const void* k, const void* v, int dtype, int64_t q_token_stride,
                     int64_t k_token_stride, int64_t v_token_stride, const void* cos, const void* sin,
                     int rope_dtype, int64_t rope_token_stride, int n_tokens, int num_q_heads, int num_kv_heads,
                     int head_dim, void* q_out, void* hot_k, void* hot_v, int64_t capacity, int64_t slot,
-                    pkv_stream_t stream);
+                    const int32_t* slot_dev, pkv_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -32,6 +32,7 @@ class Segment(ctypes.Structure):
         ("k_group", ctypes.c_int32), ("v_group", ctypes.c_int32), ("num_splits", ctypes.c_int32),
         ("k_row_pitch", ctypes.c_int64), ("k_meta_pitch", ctypes.c_int64),
         ("flags", ctypes.c_int32), ("slot_tokens", ctypes.c_int16), ("slot_valid", ctypes.c_int16),
+        ("seq_len_dev", ctypes.c_void_p),
     ]
 
 
@@ -78,7 +79,7 @@ _SIGNATURES = {
     "pkv_decode_chunk_plan": ([ctypes.POINTER(Segment), _I32, _I32, _I32, _I32, _I32, _I32, _VP, ctypes.c_size_t,
                                ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)], _I32),
     "pkv_rope_append": ([_VP, _VP, _VP, _I32, _I64, _I64, _I64, _VP, _VP, _I32, _I64, _I32, _I32, _I32, _I32,
-                         _VP, _VP, _VP, _I64, _I64, _VP], _I32),
+                         _VP, _VP, _VP, _I64, _I64, _VP, _VP], _I32),
     "pkv_merge_partials": ([_VP, _VP, _VP, _I32, _I32, _I32, _VP, _VP, _VP, _VP, _VP], _I32),
     "pkv_merge_partials_strided": ([_VP, _VP, _VP, _I32, _I64, _I64, _I32, _I32, _VP, _VP, _VP, _VP, _VP], _I32),
     "pkv_exchange_create": ([_I32, _I32, _I32, _I32, ctypes.POINTER(_VP), _VP], _I32),

@@ -28,6 +28,7 @@ struct RopeArgs {
     __half *q_out, *hot_k, *hot_v;
     long long q_stride, k_stride, v_stride, rope_stride;  // elements between consecutive tokens
     long long capacity, slot;                             // hot buffers [Hkv, capacity, hd]; first slot written
+    const int* slot_dev;                                  // optional: the first slot is *slot_dev + slot
     int n_tokens, Hq, Hkv, hd;
 };
 
@@ -36,10 +37,13 @@ template <class T, class R>
 __global__ void __launch_bounds__(kRopeThreads) rope_append_kernel(const RopeArgs a) {
     const int t = blockIdx.y, h = blockIdx.x;
     const int half = a.hd >> 1;
+    const long long slot = a.slot + (a.slot_dev ? (long long)*a.slot_dev : 0);
+    const bool in_tier = slot >= 0 && slot + a.n_tokens <= a.capacity;  // (always true for a host-given slot)
+    if (h >= a.Hq && !in_tier) return;
     if (h >= a.Hq + a.Hkv) {  // a value vector: converted and stored
         const int kvh = h - a.Hq - a.Hkv;
         const T* src = static_cast<const T*>(a.v) + t * a.v_stride + (long long)kvh * a.hd;
-        __half* dst = a.hot_v + ((long long)kvh * a.capacity + a.slot + t) * a.hd;
+        __half* dst = a.hot_v + ((long long)kvh * a.capacity + slot + t) * a.hd;
         for (int d = threadIdx.x; d < a.hd; d += kRopeThreads) dst[d] = __float2half_rn(ld_f32(src + d));
         return;
     }
@@ -48,7 +52,7 @@ __global__ void __launch_bounds__(kRopeThreads) rope_append_kernel(const RopeArg
     const T* src = is_q ? static_cast<const T*>(a.q) + t * a.q_stride + (long long)head * a.hd
                         : static_cast<const T*>(a.k) + t * a.k_stride + (long long)head * a.hd;
     __half* dst = is_q ? a.q_out + ((long long)t * a.Hq + head) * a.hd
-                       : a.hot_k + ((long long)head * a.capacity + a.slot + t) * a.hd;
+                       : a.hot_k + ((long long)head * a.capacity + slot + t) * a.hd;
     const R* cs = static_cast<const R*>(a.cos) + t * a.rope_stride;
     const R* sn = static_cast<const R*>(a.sin) + t * a.rope_stride;
     for (int d = threadIdx.x; d < a.hd; d += kRopeThreads) {
@@ -82,12 +86,13 @@ extern "C" int pkv_rope_append(const void* q, const void* k, const void* v, int 
                                int64_t k_token_stride, int64_t v_token_stride, const void* cos, const void* sin,
                                int rope_dtype, int64_t rope_token_stride, int n_tokens, int num_q_heads,
                                int num_kv_heads, int head_dim, void* q_out, void* hot_k, void* hot_v,
-                               int64_t capacity, int64_t slot, pkv_stream_t stream) {
+                               int64_t capacity, int64_t slot, const int32_t* slot_dev, pkv_stream_t stream) {
     using namespace pkv;
     if (!q || !k || !v || !cos || !sin || !q_out || !hot_k || !hot_v) return PKV_E_NULL;
     if (n_tokens <= 0 || n_tokens > 65535 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || (head_dim & 1))
         return PKV_E_SHAPE;
-    if (slot < 0 || slot + n_tokens > capacity) return PKV_E_SHAPE;
+    if (!slot_dev && (slot < 0 || slot + n_tokens > capacity)) return PKV_E_SHAPE;
+    if (n_tokens > capacity) return PKV_E_SHAPE;
     if (q_token_stride < (int64_t)num_q_heads * head_dim || k_token_stride < (int64_t)num_kv_heads * head_dim ||
         v_token_stride < (int64_t)num_kv_heads * head_dim || rope_token_stride < 0)
         return PKV_E_SHAPE;
@@ -95,7 +100,7 @@ extern "C" int pkv_rope_append(const void* q, const void* k, const void* v, int 
     a.q = q, a.k = k, a.v = v, a.cos = cos, a.sin = sin;
     a.q_out = static_cast<__half*>(q_out), a.hot_k = static_cast<__half*>(hot_k), a.hot_v = static_cast<__half*>(hot_v);
     a.q_stride = q_token_stride, a.k_stride = k_token_stride, a.v_stride = v_token_stride, a.rope_stride = rope_token_stride;
-    a.capacity = capacity, a.slot = slot;
+    a.capacity = capacity, a.slot = slot, a.slot_dev = slot_dev;
     a.n_tokens = n_tokens, a.Hq = num_q_heads, a.Hkv = num_kv_heads, a.hd = head_dim;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (dtype == PKV_DTYPE_F16) return launch_rope<__half>(a, rope_dtype, s);

@@ -63,7 +63,9 @@ decode_generic_kernel(const __grid_constant__ DecodeArgs a) {
     while (si + 1 < a.n_segs && w >= a.segs[si + 1].work_begin) ++si;
     const SegDev& sg = a.segs[si];
     const long long t0 = (long long)(w - sg.work_begin) * sg.split_len;
-    const long long t1 = min(sg.S, t0 + sg.split_len);
+    // (a length kept in device memory is read behind everything earlier in the stream: this kernel is an ordinary launch)
+    const long long S_eff = sg.len_dev ? min(sg.S, max(0LL, (long long)*sg.len_dev)) : sg.S;
+    const long long t1 = min(S_eff, t0 + sg.split_len);  // an item past the end writes an empty partial (m = -inf, l = 0)
 
     const int h0 = kvh * a.G + hc * GMAX;
     const int nh = min(GMAX, a.G - hc * GMAX);
@@ -235,6 +237,7 @@ int check_segments(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int h
             continue;
         }
         if (s.kind != PKV_SEG_KIVI && s.kind != PKV_SEG_PER_TOKEN) return PKV_E_LAYOUT;
+        if (s.seq_len_dev && s.kind != PKV_SEG_KIVI) return PKV_E_LAYOUT;
         if (!valid_bits(s.k_bits) || !valid_bits(s.v_bits)) return PKV_E_BITS;
         if (s.k_group <= 0 || s.v_group <= 0) return PKV_E_LAYOUT;
         if (!s.k_scale || !s.k_mins || !s.v_scale || !s.v_mins) return PKV_E_NULL;
@@ -282,6 +285,7 @@ static SegDev seg_dev_of(const pkv_segment_t& s) {
     d.kgs = s.kind == PKV_SEG_FP16 ? 1 : s.k_group;
     d.vgs = s.kind == PKV_SEG_FP16 ? 1 : s.v_group;
     d.v_head_tokens = s.seq_len;
+    d.len_dev = s.seq_len_dev;
     if (s.kind == PKV_SEG_KIVI) {
         d.k_pitch = s.k_row_pitch ? s.k_row_pitch : ceil_div(s.seq_len * s.k_bits, 8);
         d.km_pitch = s.k_meta_pitch ? s.k_meta_pitch : ceil_div(s.seq_len, s.k_group);
@@ -735,6 +739,7 @@ extern "C" int pkv_decode_chunk_plan(const pkv_segment_t* segs, int n_segments, 
         offsets[i] = i * n_segments;
         for (int k = 0; k < n_segments; ++k) all[(size_t)i * n_segments + k] = segs[k];
         all[(size_t)i * n_segments + n_segments - 1].seq_len = hot.seq_len - (chunk_len - 1 - i);
+        all[(size_t)i * n_segments + n_segments - 1].seq_len_dev = nullptr;  // the causal cut is a host length
     }
     offsets[chunk_len] = chunk_len * n_segments;
     return pkv_decode_batch_plan(all.data(), offsets.data(), chunk_len, num_q_heads, num_kv_heads, head_dim, sm_count,

@@ -618,15 +618,16 @@ constexpr int HROW = HD + 8;                      // halves per padded row
 constexpr int HOT_TILE_BYTES = TH * HROW * 2;     // one of K or V
 constexpr int HOT_RING_BYTES = 2 * HOT_TILE_BYTES;
 
-__device__ __forceinline__ void issue_hot_tile(const SegDev& sg, int kvh, long long tile, unsigned sa, int lane) {
+__device__ __forceinline__ void issue_hot_tile(const SegDev& sg, long long S, int kvh, long long tile, unsigned sa,
+                                               int lane) {
     const __half* kb = reinterpret_cast<const __half*>(sg.kp) + (size_t)kvh * sg.head_stride;
     const __half* vb = reinterpret_cast<const __half*>(sg.vp) + (size_t)kvh * sg.head_stride;
 #pragma unroll 4
     for (int it = 0; it < TH * 16 / 32; ++it) {
         const int idx = it * 32 + lane, tok = idx >> 4, ch = idx & 15;
         const long long gt = tile * TH + tok;
-        const unsigned nbytes = gt < sg.S ? 16u : 0u;
-        const size_t off = (size_t)min(gt, sg.S - 1) * HD + ch * 8;
+        const unsigned nbytes = gt < S ? 16u : 0u;
+        const size_t off = (size_t)min(gt, S - 1) * HD + ch * 8;
         cp_async16_zfill(sa + (tok * HROW + ch * 8) * 2, kb + off, nbytes);
         cp_async16_zfill(sa + HOT_TILE_BYTES + (tok * HROW + ch * 8) * 2, vb + off, nbytes);
     }
@@ -703,8 +704,9 @@ __device__ __forceinline__ void compute_hot_tile(unsigned sa, const unsigned (&q
     }
 }
 
-__device__ __forceinline__ void run_cta_fp16(const CtaCtx& a, const SegDev& sg, long long tile0, long long tile1,
-                                             int kvh, float* smem_f) {
+// S: the tokens that count (the segment's length, or what its device-resident length says)
+__device__ __forceinline__ void run_cta_fp16(const CtaCtx& a, const SegDev& sg, long long S, long long tile0,
+                                             long long tile1, int kvh, float* smem_f) {
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const unsigned smem_base = (unsigned)__cvta_generic_to_shared(smem_f);
@@ -728,10 +730,10 @@ __device__ __forceinline__ void run_cta_fp16(const CtaCtx& a, const SegDev& sg, 
     constexpr int kHotWarps = kSmemBytes / HOT_RING_BYTES < NWARPS ? kSmemBytes / HOT_RING_BYTES : NWARPS;
     const unsigned ring = smem_base + wid * HOT_RING_BYTES;
     for (long long tile = tile0 + wid; wid < kHotWarps && tile < tile1; tile += kHotWarps) {
-        issue_hot_tile(sg, kvh, tile, ring, lane);
+        issue_hot_tile(sg, S, kvh, tile, ring, lane);
         cp_async_wait<0>();
         __syncwarp();
-        compute_hot_tile(ring, qh, c_qk, st, (int)min((long long)TH, sg.S - tile * TH), lane);
+        compute_hot_tile(ring, qh, c_qk, st, (int)min((long long)TH, S - tile * TH), lane);
         __syncwarp();
     }
     finish_cta<0>(a, st, kvh, smem_f);
@@ -742,15 +744,15 @@ __device__ __forceinline__ void run_cta_fp16(const CtaCtx& a, const SegDev& sg, 
 // segment and the range is long enough to pay for the barrier set-up, 16-byte cp.async by every thread otherwise,
 // ordinary loads for ragged rows), each warp streams the values of its own tile, one __syncthreads per super-tile.
 template <int BITS>
-__device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const KeyMaps* kmaps, long long tile0,
-                                        long long tile1, int kvh, float* smem_f) {
+__device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, long long S, const KeyMaps* kmaps,
+                                        long long tile0, long long tile1, int kvh, float* smem_f) {
     using C = Cfg<BITS>;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const unsigned smem_base = (unsigned)__cvta_generic_to_shared(smem_f);
     const int h0 = kvh * a.G;
     // tokens of tile `tl` that exist (the last tile of a ragged segment is partial)
-    auto valid_of = [&](long long tl) { return (int)min((long long)C::T, sg.S - tl * C::T); };
+    auto valid_of = [&](long long tl) { return (int)min((long long)C::T, S - tl * C::T); };
 
     const KSrc<BITS> ksrc(sg, kvh, tile0);
 
@@ -815,7 +817,7 @@ __device__ __forceinline__ void run_cta(const CtaCtx& a, const SegDev& sg, const
 
     // Super-tile 0 of a settled packed segment is fetched before the dependency wait.  A segment that the kernel
     // launched just before this one may have written (flagged by the caller) is read only after it.
-    const bool early = !sg.fresh;
+    const bool early = !sg.fresh && sg.len_dev == nullptr;
     if (!early) cudaGridDependencySynchronize();
     if (ksrc.aligned) issue_first();
     if (ktma) __syncthreads();  // the mbarriers are initialised for every thread that will wait on them
@@ -1062,18 +1064,42 @@ __device__ __forceinline__ void run_cta_per_token(const CtaCtx& a, const SegDev&
     finish_cta<BITS>(a, st, kvh, smem_f);
 }
 
-__device__ __forceinline__ long long tiles_in(const SegDev& sg) {
-    return sg.kind == PKV_SEG_FP16 ? (sg.S + TH - 1) / TH : (sg.S + 63) / 64;
+__device__ __forceinline__ long long tiles_in(const SegDev& sg, long long S) {
+    return sg.kind == PKV_SEG_FP16 ? (S + TH - 1) / TH : (S + 63) / 64;
+}
+
+// The tokens of a segment that count: its length, or, for a segment whose length lives in device memory, what that
+// says now (never more than the capacity the launch was sized for).  The value may have been written by the
+// previous kernel of the stream, so it is read behind the dependency wait.
+__device__ __forceinline__ long long live_length(const SegDev& sg) {
+    if (sg.len_dev == nullptr) return sg.S;
+    cudaGridDependencySynchronize();
+    return min(sg.S, max(0LL, (long long)*sg.len_dev));
+}
+
+// A work item past the end of a segment whose length shrank below the launch's capacity: nothing to attend to.
+__device__ __forceinline__ void write_empty_partial(const CtaCtx& a, int kvh) {
+    cudaGridDependencySynchronize();
+    cudaTriggerProgrammaticLaunchCompletion();
+    const int h0 = kvh * a.G;
+    for (int idx = threadIdx.x; idx < a.G * (HD / 4); idx += NTHREADS)
+        *reinterpret_cast<float4*>(a.pacc + (a.widx * a.Hq + h0) * HD + 4 * idx) = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (threadIdx.x < a.G) {
+        a.pm[a.widx * a.Hq + h0 + threadIdx.x] = -INFINITY;
+        a.pl[a.widx * a.Hq + h0 + threadIdx.x] = 0.f;
+    }
 }
 
 // Tiles [tile0, tile0 + n_tiles) of segment `sg` for KV head `kvh`, one partial written to row a.widx.
 __device__ __forceinline__ void run_item(const CtaCtx& a, const SegDev& sg, const KeyMaps* kmaps, long long tile0,
                                          long long n_tiles, int kvh, float* smem_f) {
-    const long long tile1 = min(tiles_in(sg), tile0 + n_tiles);
-    if (sg.kind == PKV_SEG_FP16) run_cta_fp16(a, sg, tile0, tile1, kvh, smem_f);
-    else if (sg.kbits == 2) run_cta<2>(a, sg, kmaps, tile0, tile1, kvh, smem_f);
-    else if (sg.kbits == 4) run_cta<4>(a, sg, kmaps, tile0, tile1, kvh, smem_f);
-    else run_cta<8>(a, sg, kmaps, tile0, tile1, kvh, smem_f);
+    const long long S = live_length(sg);
+    const long long tile1 = min(tiles_in(sg, S), tile0 + n_tiles);
+    if (tile0 >= tile1) return write_empty_partial(a, kvh);
+    if (sg.kind == PKV_SEG_FP16) run_cta_fp16(a, sg, S, tile0, tile1, kvh, smem_f);
+    else if (sg.kbits == 2) run_cta<2>(a, sg, S, kmaps, tile0, tile1, kvh, smem_f);
+    else if (sg.kbits == 4) run_cta<4>(a, sg, S, kmaps, tile0, tile1, kvh, smem_f);
+    else run_cta<8>(a, sg, S, kmaps, tile0, tile1, kvh, smem_f);
 }
 
 // Which work item a CTA of the single-sequence kernels has
@@ -1105,8 +1131,10 @@ __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_mma_per_token_ke
     const SegDev& sg = a.segs[si];
     const int kvh = blockIdx.y;
     const CtaCtx ctx = {a.q, a.pm, a.pl, a.pacc, (size_t)a.work_offset + blockIdx.x, a.Hq, a.G, a.sm_scale};
-    const long long tile0 = (long long)split * sg.split_len, tile1 = min(tiles_in(sg), tile0 + sg.split_len);
-    if (sg.kind == PKV_SEG_FP16) run_cta_fp16(ctx, sg, tile0, tile1, kvh, smem_f);
+    const long long S = live_length(sg);
+    const long long tile0 = (long long)split * sg.split_len, tile1 = min(tiles_in(sg, S), tile0 + sg.split_len);
+    if (tile0 >= tile1) return write_empty_partial(ctx, kvh);
+    if (sg.kind == PKV_SEG_FP16) run_cta_fp16(ctx, sg, S, tile0, tile1, kvh, smem_f);
     else if (sg.kbits == 2) run_cta_per_token<2>(ctx, sg, tile0, tile1, kvh, smem_f);
     else if (sg.kbits == 4) run_cta_per_token<4>(ctx, sg, tile0, tile1, kvh, smem_f);
     else run_cta_per_token<8>(ctx, sg, tile0, tile1, kvh, smem_f);

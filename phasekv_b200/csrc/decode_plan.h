@@ -32,6 +32,7 @@ struct SegDev {
                      // stream dependency is resolved
     int slot_tokens, slot_valid;  // KIVI: only the first slot_valid tokens of every slot_tokens count (0 = all)
     long long v_head_tokens;      // KIVI: token rows between KV heads of the value arrays
+    const int* len_dev;           // optional: min(S, *len_dev) tokens count, read at run time; S is the capacity
 };
 
 // Segments are routed to one of two kernels: the tensor-core kernel (`fast`, split_len counts

@@ -427,7 +427,7 @@ class PhaseKVCache(_CacheBase):
                 query.data_ptr(), key.data_ptr(), value.data_ptr(), _ROPE_DTYPES[query.dtype], query.stride(0),
                 key.stride(0), value.stride(0), cos.data_ptr(), sin.data_ptr(), _ROPE_DTYPES[cos.dtype], cos.stride(0),
                 n, query.shape[1], hkv, hd, out.data_ptr(), layer.hot_k.data_ptr(), layer.hot_v.data_ptr(),
-                layer.hot_k.shape[2], slot, nv.stream_of(query.device)))
+                layer.hot_k.shape[2], slot, None, nv.stream_of(query.device)))
         layer.hot_len = slot + n
         if not in_chunk:
             self._written.add(layer_idx)

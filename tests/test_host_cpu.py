@@ -239,10 +239,12 @@ def test_adapter_and_cooling_entry_points_check_arguments_first():
     def rope(**over):
         a = dict(ok, **over)
         return L.pkv_rope_append(a["q"], a["k"], a["v"], a["dtype"], a["qs"], a["ks"], a["vs"], a["cos"], a["sin"], a["rdt"],
-                                 a["rs"], a["n"], a["hq"], a["hkv"], a["hd"], a["qo"], a["hk"], a["hv"], a["cap"], a["slot"], None)
+                                 a["rs"], a["n"], a["hq"], a["hkv"], a["hd"], a["qo"], a["hk"], a["hv"], a["cap"], a["slot"],
+                                 a.get("slot_dev"), None)
     assert rope(q=None) == nv.PKV_E_NULL and rope(hv=None) == nv.PKV_E_NULL
     assert rope(n=0) == nv.PKV_E_SHAPE and rope(hd=63) == nv.PKV_E_SHAPE
     assert rope(slot=46) == nv.PKV_E_SHAPE          # three tokens do not fit behind slot 46 of 48
+    assert rope(n=49, slot=0, slot_dev=p) == nv.PKV_E_SHAPE   # with a device-resident slot only the capacity is checkable
     assert rope(qs=100) == nv.PKV_E_SHAPE           # a token stride shorter than a token
     assert rope(dtype=nv.PKV_DTYPE_F32) == nv.PKV_E_LAYOUT
     # cooling of all layers: (layers, n_layers, rows, capacity, hd, hot_len, aged, keep, bits, group, pitches..., offsets...)
