@@ -45,8 +45,7 @@ UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the kernels of one layer (split-K + merge), per prompt length, from
 # ncu captures of this workload with a few layers (traffic per launch does not depend on the layer count).
-# A prompt length without a capture reports null.  At 32768 tokens: split-K launch 13 140 736 + merge launch 508 160
-# (the capture summarised in profiles/decode_mma_kernel_qwen7b_32k.md).
+# A prompt length without a capture reports null.  At 32768 tokens: split-K launch 13 140 736 + merge launch 508 160.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = {32768: 13648896}
 NCU_TRAFFIC_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum, split-K + merge kernels of one layer"
 
@@ -1060,6 +1059,79 @@ def measure_graphed_step(ctx, prompt_len, layers, tokens=200):
     return res
 
 
+def measure_per_token_layout(ctx, layers):
+    """The per-token layout of the reference's published micro-benchmark (K and V both quantised along head_dim,
+    4 KV heads x S x 128, 28 query heads) on its own tensor-core kernel: distinct layers (more than the L2 holds)
+    replayed from a CUDA graph, library-sized grid.  Bytes = packed K + V."""
+    torch, device = ctx.torch, ctx.device
+    from phasekv_b200.kernels import packing as pk
+    from phasekv_b200.kernels.attention_cuda import decode_attention_packed_splitk
+    peak, _ = measured_peak()
+    res = {"config": {"workload": "per-token layout decode attention, 28q/4kv heads, hd 128, gs 32", "timed_as": "cuda graph",
+                      "l2_policy": "distinct KV per layer, at least 300 MB resident"}}
+    q = torch.randn(28, 128, device=device, dtype=torch.float16)
+    for bits in (2, 4):
+        for S in (4096, 32768, 131072):
+            per_layer = 2 * 4 * S * (128 * bits // 8 + 16)
+            n_layers = max(layers, int(3e8 // per_layer) + 1)
+            g = torch.Generator(device=device).manual_seed(S + bits)
+            kv = []
+            for _ in range(n_layers):
+                x = torch.randn(4, S, 128, device=device, dtype=torch.float16, generator=g)
+                kv.append((pk.quantize_pack(x, bits, -1, 32), pk.quantize_pack(x.flip(1).contiguous(), bits, -1, 32)))
+                del x
+
+            def run():
+                for a, b in kv:
+                    decode_attention_packed_splitk(q, a, b, 28, num_splits=None)
+            ms = time_graph(torch, run, 20, 3)
+            us = ms / n_layers * 1e3
+            res[f"{bits}bit_{S}"] = {"us_per_layer": us, "GBps": per_layer / us / 1e3, "frac_of_peak": per_layer / us / 1e3 / peak,
+                                     "layers_resident": n_layers}
+            del kv
+            torch.cuda.empty_cache()
+    return res
+
+
+def measure_general_kernel(ctx):
+    """Shapes the tensor-core kernels do not take run on the general kernel: the Qwen2-0.5B attention shape of the
+    CPU-plumbing configuration (14 query / 2 KV heads, head_dim 64; prompt 2-bit with value groups of 64, 128 cold
+    tokens at 4 bits, 64 float16 tokens) at its own 1024 prompt tokens and at 32768.  Distinct layers replayed from a
+    CUDA graph (the parity of this configuration is a test, tests/test_decode_gpu.py)."""
+    torch, device = ctx.torch, ctx.device
+    from phasekv_b200 import workloads
+    from phasekv_b200.kernels import packing as pk
+    from phasekv_b200.kernels.attention_cuda import fused_phasekv_decode
+    from phasekv_b200.kernels.tiers import LayerTiers, PackedKVSegment
+    shape = workloads.QWEN2_0_5B
+    peak, _ = measured_peak()
+    res = {"config": {"workload": "qwen2-0.5b attention shape on the general kernel (hd 64, gsK 32 / gsV 64)",
+                      "timed_as": "cuda graph", "l2_policy": "distinct KV per layer, at least 300 MB resident at 32768"}}
+    for S in (1024, 32768):
+        nbytes = workloads.decode_algorithmic_bytes(shape, S, 2, 128, 4, 64, 32, 64)
+        n_layers = 24 if S == 1024 else max(24, int(3e8 // nbytes) + 1)
+        gen = torch.Generator(device=device).manual_seed(S)
+        tiers = []
+        for _ in range(n_layers):
+            def packed(tokens, bits):
+                k = torch.randn(1, 2, tokens, 64, device=device, dtype=torch.float16, generator=gen)
+                return PackedKVSegment(pk.quantize_pack(k, bits, -2, 32), pk.quantize_pack(k.flip(2).contiguous(), bits, -1, 64))
+            hot = torch.randn(1, 2, 64, 64, device=device, dtype=torch.float16, generator=gen)
+            tiers.append(LayerTiers(prompt=packed(S, 2), cold=[packed(128, 4)], hot_k=hot, hot_v=hot.flip(2).contiguous(), hot_len=64))
+        q = torch.randn(14, 64, device=device, dtype=torch.float16, generator=gen)
+
+        def run():
+            for t in tiers:
+                fused_phasekv_decode(q, t, 14)
+        run()
+        us = time_graph(torch, run, 20, 3) / n_layers * 1e3
+        res[str(S)] = {"us_per_layer": us, "GBps": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak,
+                       "algorithmic_bytes": nbytes, "layers_resident": n_layers}
+        del tiers
+        torch.cuda.empty_cache()
+    return res
+
+
 def sharded_block(ctx, args):
     """The two configurations that shard over GPUs (sequence-sharded long context, batch-sharded serving) and, on
     one GPU, the pack kernels, measured in the same process group after the headline.  A workload that fails
@@ -1085,7 +1157,9 @@ def sharded_block(ctx, args):
         for name, fn in (("prompt_chunk", lambda: [measure_prompt_chunk(ctx, 4096, 64), measure_prompt_chunk(ctx, args.prompt, 64)]),
                          ("cold_arena", lambda: measure_cold_arena(ctx, args.prompt, args.layers)),
                          ("adapter_layer", lambda: measure_adapter_layer(ctx, args.prompt, 64)),
-                         ("graphed_step", lambda: measure_graphed_step(ctx, args.prompt, args.layers))):
+                         ("graphed_step", lambda: measure_graphed_step(ctx, args.prompt, args.layers)),
+                         ("per_token_layout", lambda: measure_per_token_layout(ctx, args.layers)),
+                         ("general_kernel", lambda: measure_general_kernel(ctx))):
             try:
                 block[name] = fn()
             except Exception as exc:

@@ -628,9 +628,8 @@ merge_batched_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
 
 // Tiles per work item.  `per_sm` is the layer's work per SM in 64-token tiles.  Few tiles per SM: one wave,
 // the tiles spread evenly.  Many: about three waves of long items; the short cold and hot segments, sorted to
-// the end of the work list, fill the tail.  (Measured on B200 with 64 sequences of ~8832 tokens: 2-3 waves
-// 135 us per layer, 4 waves 144, 6-8 waves 148: every item pays its first-load latency, warp merge and
-// partial write once.)  Items are whole super-tiles (what the CTA's warps compute side by side).
+// the end of the work list, fill the tail (more, shorter items cost more: every item pays its first-load
+// latency, warp merge and partial write once).  Items are whole super-tiles (what the CTA's warps compute side by side).
 int item_tiles(double per_sm) {
     constexpr int kSuper = mma::Cfg<2>::NSUB;  // tiles the CTA's warps compute side by side
     const int waves = (int)std::max(1.0, std::min(3.0, per_sm / kSuper));

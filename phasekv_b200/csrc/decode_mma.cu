@@ -16,9 +16,6 @@ constexpr int kKUnroll = PKV_K_UNROLL;
 #define PKV_KEY_TMA 1
 #endif
 // Keys through tiled TMA copies (tensor maps made on the host) where the layout allows; 0 = cp.async everywhere.
-// Untiled bulk copies (cp.async.bulk, one request per key row or per 8 value rows) were measured before this and
-// lost to cp.async: 384 requests of 192 bytes per super-tile 14.1 / 35.0 us at 32768 / 131072 tokens, values only
-// 12.3 / 29.2 us, cp.async for both 11.8 / 28.4 us.
 constexpr bool kKeyTma = PKV_KEY_TMA != 0;
 #ifndef PKV_TMA_MIN_SUPER
 #define PKV_TMA_MIN_SUPER 3
@@ -29,9 +26,8 @@ constexpr int kTmaMinSuper = PKV_TMA_MIN_SUPER;
 #ifndef PKV_PAIR_SPLIT
 #define PKV_PAIR_SPLIT 1
 #endif
-// warp pairs share the tiles of short super-tiles.  (Giving EVERY tile to a warp pair, 16 warps of 121 registers,
-// measured 13.4 / 35.2 us at 32768 / 131072 tokens against 12.2 / 28.4: each half pays the per-tile q loads, zero-term
-// MMAs and state rescale again.)
+// warp pairs share the tiles of short super-tiles (a pair pays the per-tile q loads, zero-term MMAs and state
+// rescale twice, so full super-tiles keep one warp per tile)
 constexpr bool kPairSplit = PKV_PAIR_SPLIT != 0;
 #ifndef PKV_SMALL_FIRST
 #define PKV_SMALL_FIRST 1

@@ -32,6 +32,7 @@ def test_static_scratch_entry_point_matches_regular_one(oracle):
     from phasekv_b200 import _native as nv
     from phasekv_b200 import workloads
     from phasekv_b200.kernels.attention_cuda import layer_segments
+    from conftest import attention_close
     from util import make_tiers
     shape = workloads.QWEN2_5_7B
     gen = torch.Generator().manual_seed(2024)
@@ -42,11 +43,12 @@ def test_static_scratch_entry_point_matches_regular_one(oracle):
             k, v = workloads.make_kv(gen, shape.num_kv_heads, length, shape.head_dim)
             segs.append((oracle.quantize_pack(k, bits, -2, 32), oracle.quantize_pack(v, bits, -1, 32)))
         hk, hv = workloads.make_kv(gen, shape.num_kv_heads, hot, shape.head_dim)
-        q = workloads.make_query(gen, shape.num_q_heads, shape.head_dim)[0, :, 0, :].cuda()
-        cases.append((make_tiers(segs, hk, hv, hot_len=hot), q))
+        q_cpu = workloads.make_query(gen, shape.num_q_heads, shape.head_dim)[0, :, 0, :]
+        want = oracle.segments_decode_reference(q_cpu, segs, hk, hv, shape.num_q_heads)
+        cases.append((make_tiers(segs, hk, hv, hot_len=hot), q_cpu.cuda(), want))
     sms = nv.sm_count(torch.device("cuda", 0))
     for rep in range(2):  # two calls in a row per case: the array keeps what the previous call wrote
-        for tiers, q in cases:
+        for tiers, q, want in cases:
             seg_list, keep, hkv, hd = layer_segments(tiers)
             arr = (nv.Segment * len(seg_list))(*seg_list)
             need = ctypes.c_size_t(0)
@@ -57,6 +59,7 @@ def test_static_scratch_entry_point_matches_regular_one(oracle):
             for a, b in zip(got, ref):
                 torch.testing.assert_close(a.float(), b.float(), atol=2e-3, rtol=1e-2)
             assert torch.equal(got[0], ref[0])  # same kernels, same order of operations
+            attention_close(got[0], want)       # and the parity bar against the oracle itself
 
 
 def test_static_scratch_rejects_oversized_requests():
