@@ -19,9 +19,11 @@ namespace pkv {
 namespace {
 
 constexpr int GMAX = 8;        // query heads served per CTA pass
-constexpr int kThreads = 128;  // threads per CTA of the generic kernel
-constexpr int kChunk = 128;    // tokens per inner step (= kThreads)
-constexpr int kMaxDimsPerThread = 2;  // head_dim <= 256
+constexpr int kThreads = 512;  // threads per CTA of the general kernel
+constexpr int kChunk = 128;    // tokens per inner step
+constexpr int kTokThreads = kThreads / kChunk;  // threads that share a token's score
+constexpr int kMaxHeadDim = 256;
+constexpr int kMaxParts = 8;   // token groups of the p * v phase
 
 struct DecodeArgs {
     const __half* q;
@@ -46,15 +48,43 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-__global__ void __launch_bounds__(kThreads)
+// Shared memory of the general kernel: q (float32, pre-scaled), the chunk's scores / probabilities, the running
+// softmax state, then the chunk's keys and values DEQUANTISED to float16 — exactly the values the reference's
+// unpack_dequantize yields (code * scale and + zero rounded separately in float32, then rounded to float16) — keys
+// as [channel][token] so that one thread per token reads without bank conflicts, values as [token][channel].
+constexpr int kPadK = 8, kPadV = 8;  // float16 elements of padding per staged row
+inline size_t generic_smem_bytes(int hd) {
+    return sizeof(float) * ((size_t)GMAX * hd + (size_t)kTokThreads * GMAX * kChunk + 3 * GMAX) +
+           sizeof(__half) * ((size_t)hd * (kChunk + kPadK) + (size_t)kChunk * (hd + kPadV));
+}
+
+// Division by a run-time constant that usually is a power of two
+struct Divisor {
+    int d, shift;
+    __device__ explicit Divisor(int d_) : d(d_), shift(-1) {
+        if ((d_ & (d_ - 1)) == 0)
+            for (shift = 0; (1 << shift) < d_; ++shift) {}
+    }
+    __device__ __forceinline__ int operator()(int x) const { return shift >= 0 ? x >> shift : x / d; }
+};
+
+__device__ __forceinline__ __half dequantise(unsigned code, __half scale, __half zero) {
+    return __float2half_rn(__fadd_rn(__fmul_rn((float)code, __half2float(scale)), __half2float(zero)));
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
 decode_generic_kernel(const __grid_constant__ DecodeArgs a) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     const int hd = a.hd;
     float* q_s = smem;                    // [GMAX][hd], pre-multiplied by sm_scale
-    float* p_s = q_s + GMAX * hd;         // [GMAX][kChunk]
-    float* alpha_s = p_s + GMAX * kChunk; // [GMAX]
+    float* p_s = q_s + GMAX * hd;         // [kTokThreads][GMAX][kChunk]: partial scores; [0] then holds the probabilities
+    float* alpha_s = p_s + kTokThreads * GMAX * kChunk;  // [GMAX]
     float* m_s = alpha_s + GMAX;
     float* l_s = m_s + GMAX;
+    __half* kd = reinterpret_cast<__half*>(l_s + GMAX);  // [hd][kChunk + kPadK]
+    __half* vd = kd + (size_t)hd * (kChunk + kPadK);     // [kChunk][hd + kPadV]
+    constexpr int KROW = kChunk + kPadK;
+    const int VROW = hd + kPadV;
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int w = blockIdx.x, kvh = blockIdx.y, hc = blockIdx.z;
@@ -77,58 +107,163 @@ decode_generic_kernel(const __grid_constant__ DecodeArgs a) {
         m_s[tid] = -INFINITY;
         l_s[tid] = 0.f;
     }
-    float acc[GMAX][kMaxDimsPerThread];
+    // out += p * v: thread (part, d0) owns channel d0 for the tokens part, part + parts, ... of a chunk; the
+    // parts are summed at the end
+    const int parts = min(kMaxParts, kThreads / hd);
+    const int part = tid / hd;
+    const int d0 = tid - part * hd;
+    const bool pv_thread = part < parts;
+    float acc[GMAX];
 #pragma unroll
-    for (int h = 0; h < GMAX; ++h)
-#pragma unroll
-        for (int k = 0; k < kMaxDimsPerThread; ++k) acc[h][k] = 0.f;
-    __syncthreads();
+    for (int h = 0; h < GMAX; ++h) acc[h] = 0.f;
 
-    const int kvpb = 8 / sg.kbits, vvpb = 8 / sg.vbits;
+    const int kbits = sg.kbits, vbits = sg.vbits;
+    const int kvpb = 8 / kbits;
     const long long S = sg.S;
+    const __half zero_h = __float2half_rn(0.f);
 
     for (long long c0 = t0; c0 < t1; c0 += kChunk) {
-        // ---- phase 1: one token per thread, scores for all heads of the group
-        const long long n = c0 + tid;
-        float dot[GMAX];
+        const int nvalid = (int)min((long long)kChunk, t1 - c0);
+        __syncthreads();  // the previous chunk's tiles are no longer read (and q_s / m_s are set, first time round)
+        // ---- stage the chunk.  A work item is one code BYTE (8 / bits consecutive elements that share a scale and a
+        // zero whenever the group size is a multiple of that count, which every caller's is); consecutive threads take
+        // consecutive bytes of the memory layout at hand.  Index arithmetic is 32-bit and, where the sizes are powers
+        // of two, shifts.
+        if (sg.kind == PKV_SEG_KIVI) {
+            const long long nbK = sg.k_pitch, ngK = sg.km_pitch;
+            const uint8_t* kp = sg.kp + (size_t)kvh * hd * nbK;
+            const __half* ks = sg.ks + (size_t)kvh * hd * ngK;
+            const __half* km = sg.km + (size_t)kvh * hd * ngK;
+            if (c0 % kvpb == 0 && sg.kgs % kvpb == 0) {
+                // keys: channel rows, tokens along the row; kChunk / kvpb bytes of every row belong to the chunk
+                const int bpr = kChunk / kvpb;  // a power of two
+                const Divisor by_bpr(bpr), by_group(sg.kgs);
+                const long long byte0 = c0 / kvpb, group0 = c0 / sg.kgs;
+                const int in_group0 = (int)(c0 - group0 * sg.kgs);
+                // the loads of a batch of work items are issued together, then the batch is dequantised and stored:
+                // a CTA often has a single chunk, so nothing else hides the latency of a load
+                constexpr int B = 8;
+                const int total = hd * bpr;
+                for (int base = tid; base < total; base += kThreads * B) {
+                    unsigned byte[B];
+                    __half sc[B], zr[B];
 #pragma unroll
-        for (int h = 0; h < GMAX; ++h) dot[h] = 0.f;
-        const bool counts = n < t1 && (sg.slot_tokens == 0 || (int)(n % sg.slot_tokens) < sg.slot_valid);
-        if (counts) {
-            if (sg.kind == PKV_SEG_KIVI) {
-                const long long nbK = sg.k_pitch, ngK = sg.km_pitch;
-                const uint8_t* kp = sg.kp + (size_t)kvh * hd * nbK + n / kvpb;
-                const __half* ks = sg.ks + (size_t)kvh * hd * ngK + n / sg.kgs;
-                const __half* km = sg.km + (size_t)kvh * hd * ngK + n / sg.kgs;
+                    for (int u = 0; u < B; ++u) {
+                        const int idx = base + u * kThreads;
+                        const int d = by_bpr(idx), tok = (idx - d * bpr) * kvpb;
+                        byte[u] = 0u, sc[u] = zr[u] = zero_h;
+                        if (idx < total && tok < nvalid) {
+                            const long long g = group0 + by_group(in_group0 + tok);
+                            byte[u] = kp[(size_t)d * nbK + byte0 + (idx - d * bpr)];
+                            sc[u] = ks[(size_t)d * ngK + g];
+                            zr[u] = km[(size_t)d * ngK + g];
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < B; ++u) {
+                        const int idx = base + u * kThreads;
+                        if (idx >= total) break;
+                        const int d = by_bpr(idx), tok = (idx - d * bpr) * kvpb;
+                        __half* dst = kd + d * KROW + tok;
+                        for (int e = 0; e < kvpb; ++e)
+                            dst[e] = tok + e < nvalid ? dequantise(extract_code_rt(byte[u], e, kbits), sc[u], zr[u]) : zero_h;
+                    }
+                }
+            } else {  // a chunk that starts inside a byte, or groups that split one: element by element
+                const int tok = tid % kChunk;  // thread (tok, sub) walks channels sub, sub + kTokThreads, ...
+                const long long n = c0 + tok;
+                const long long byte_idx = n / kvpb, grp = n / sg.kgs;
                 const unsigned pos = (unsigned)(n % kvpb);
-                for (int d = 0; d < hd; ++d) {
-                    const float c = (float)extract_code_rt(kp[(size_t)d * nbK], pos, sg.kbits);
-                    const float kv = fmaf(c, __half2float(ks[(size_t)d * ngK]), __half2float(km[(size_t)d * ngK]));
-#pragma unroll
-                    for (int h = 0; h < GMAX; ++h) dot[h] = fmaf(q_s[h * hd + d], kv, dot[h]);
+                for (int d = tid / kChunk; d < hd; d += kTokThreads) {
+                    __half val = zero_h;
+                    if (tok < nvalid)
+                        val = dequantise(extract_code_rt(kp[(size_t)d * nbK + byte_idx], pos, kbits),
+                                         ks[(size_t)d * ngK + grp], km[(size_t)d * ngK + grp]);
+                    kd[d * KROW + tok] = val;
                 }
-            } else if (sg.kind == PKV_SEG_PER_TOKEN) {
-                const long long nbK = ceil_div(hd, kvpb), ngK = ceil_div(hd, sg.kgs);
-                const uint8_t* kp = sg.kp + ((size_t)kvh * S + n) * nbK;
-                const __half* ks = sg.ks + ((size_t)kvh * S + n) * ngK;
-                const __half* km = sg.km + ((size_t)kvh * S + n) * ngK;
-                for (int d = 0; d < hd; ++d) {
-                    const float c = (float)extract_code_rt(kp[d / kvpb], (unsigned)(d % kvpb), sg.kbits);
-                    const float kv = fmaf(c, __half2float(ks[d / sg.kgs]), __half2float(km[d / sg.kgs]));
+            }
+        } else if (sg.kind == PKV_SEG_FP16) {
+            const __half* kr = reinterpret_cast<const __half*>(sg.kp) + (size_t)kvh * sg.head_stride + (size_t)c0 * hd;
+            for (int idx = tid; idx < hd * kChunk; idx += kThreads) {
+                const int tok = idx / hd, d = idx - tok * hd;
+                kd[d * KROW + tok] = tok < nvalid ? kr[(size_t)tok * hd + d] : zero_h;
+            }
+        }
+        // rows of tokens with channels along the row: values of both packed layouts, keys of the per-token layout
+        auto stage_token_rows = [&](const uint8_t* codes, const __half* scale, const __half* zero, size_t row0, int bits,
+                                    int gs, bool transposed) {
+            const int vpb = 8 / bits;
+            const int nb = (hd + vpb - 1) / vpb, ng = (hd + gs - 1) / gs;
+            const bool shared_meta = gs % vpb == 0 && hd % vpb == 0;
+            const Divisor by_nb(nb), by_group(gs);
+            constexpr int B = 8;
+            const int total = nb * kChunk;
+            for (int base = tid; base < total; base += kThreads * B) {
+                unsigned byte[B];
+                __half sc[B], zr[B];
 #pragma unroll
-                    for (int h = 0; h < GMAX; ++h) dot[h] = fmaf(q_s[h * hd + d], kv, dot[h]);
+                for (int u = 0; u < B; ++u) {  // all loads of the batch first
+                    const int idx = base + u * kThreads;
+                    const int tok = by_nb(idx), d = (idx - tok * nb) * vpb;
+                    byte[u] = 0u, sc[u] = zr[u] = zero_h;
+                    if (idx < total && tok < nvalid) {
+                        byte[u] = codes[(row0 + tok) * nb + (idx - tok * nb)];
+                        sc[u] = scale[(row0 + tok) * ng + by_group(d)];
+                        zr[u] = zero[(row0 + tok) * ng + by_group(d)];
+                    }
                 }
-            } else {
-                const __half* kr = reinterpret_cast<const __half*>(sg.kp) + (size_t)kvh * sg.head_stride + (size_t)n * hd;
-                for (int d = 0; d < hd; ++d) {
-                    const float kv = __half2float(kr[d]);
+#pragma unroll
+                for (int u = 0; u < B; ++u) {
+                    const int idx = base + u * kThreads;
+                    if (idx >= total) break;
+                    const int tok = by_nb(idx), d = (idx - tok * nb) * vpb;
+                    const bool live = tok < nvalid;
+                    for (int e = 0; e < vpb && d + e < hd; ++e) {
+                        __half s_e = sc[u], z_e = zr[u];
+                        if (live && !shared_meta) {
+                            s_e = scale[(row0 + tok) * ng + by_group(d + e)];
+                            z_e = zero[(row0 + tok) * ng + by_group(d + e)];
+                        }
+                        const __half val = live ? dequantise(extract_code_rt(byte[u], e, bits), s_e, z_e) : zero_h;
+                        if (transposed) kd[(d + e) * KROW + tok] = val;
+                        else vd[tok * VROW + d + e] = val;
+                    }
+                }
+            }
+        };
+        if (sg.kind == PKV_SEG_PER_TOKEN)
+            stage_token_rows(sg.kp, sg.ks, sg.km, (size_t)kvh * S + c0, kbits, sg.kgs, true);
+        if (sg.kind == PKV_SEG_FP16) {
+            const __half* vr = reinterpret_cast<const __half*>(sg.vp) + (size_t)kvh * sg.head_stride + (size_t)c0 * hd;
+            for (int idx = tid; idx < hd * kChunk; idx += kThreads) {
+                const int tok = idx / hd, d = idx - tok * hd;
+                vd[tok * VROW + d] = tok < nvalid ? vr[(size_t)tok * hd + d] : zero_h;
+            }
+        } else {
+            stage_token_rows(sg.vp, sg.vs, sg.vm, (sg.kind == PKV_SEG_KIVI ? (size_t)kvh * sg.v_head_tokens : (size_t)kvh * S) + c0,
+                             vbits, sg.vgs, false);
+        }
+        __syncthreads();
+
+        // ---- phase 1: kTokThreads threads per token, each over a quarter of the channels; partial scores of all heads
+        {
+            const int tok = tid % kChunk, sub = tid / kChunk;
+            const long long n = c0 + tok;
+            const bool counts = tok < nvalid && (sg.slot_tokens == 0 || (int)(n % sg.slot_tokens) < sg.slot_valid);
+            float dot[GMAX];
+#pragma unroll
+            for (int h = 0; h < GMAX; ++h) dot[h] = 0.f;
+            if (counts) {
+                const int per = hd / kTokThreads;  // head_dim is a multiple of 4
+                for (int d = sub * per; d < (sub + 1) * per; ++d) {
+                    const float kv = __half2float(kd[d * KROW + tok]);
 #pragma unroll
                     for (int h = 0; h < GMAX; ++h) dot[h] = fmaf(q_s[h * hd + d], kv, dot[h]);
                 }
             }
-        }
 #pragma unroll
-        for (int h = 0; h < GMAX; ++h) p_s[h * kChunk + tid] = counts ? dot[h] : -INFINITY;
+            for (int h = 0; h < GMAX; ++h) p_s[(sub * GMAX + h) * kChunk + tok] = counts ? dot[h] : -INFINITY;
+        }
         __syncthreads();
 
         // ---- phase 2: online softmax bookkeeping, one warp per head
@@ -137,7 +272,10 @@ decode_generic_kernel(const __grid_constant__ DecodeArgs a) {
             float mx = -INFINITY;
 #pragma unroll
             for (int i = 0; i < kChunk / 32; ++i) {
-                v[i] = p_s[h * kChunk + lane + 32 * i];
+                float sum = 0.f;  // (-inf in every part for a token that does not count)
+#pragma unroll
+                for (int sub = 0; sub < kTokThreads; ++sub) sum += p_s[(sub * GMAX + h) * kChunk + lane + 32 * i];
+                v[i] = sum;
                 mx = fmaxf(mx, v[i]);
             }
             mx = warp_max(mx);
@@ -146,13 +284,13 @@ decode_generic_kernel(const __grid_constant__ DecodeArgs a) {
             float sum = 0.f;
 #pragma unroll
             for (int i = 0; i < kChunk / 32; ++i) {
-                const float p = expf(v[i] - m_new);  // -inf -> 0
+                const float p = m_new == -INFINITY ? 0.f : expf(v[i] - m_new);  // -inf -> 0; a chunk of masked slots only
                 p_s[h * kChunk + lane + 32 * i] = p;
                 sum += p;
             }
             sum = warp_sum(sum);
             if (lane == 0) {
-                const float alpha = expf(m_old - m_new);  // first chunk: exp(-inf) = 0
+                const float alpha = m_new == -INFINITY ? 1.f : expf(m_old - m_new);  // first chunk: exp(-inf) = 0
                 alpha_s[h] = alpha;
                 m_s[h] = m_new;
                 l_s[h] = l_s[h] * alpha + sum;
@@ -160,53 +298,41 @@ decode_generic_kernel(const __grid_constant__ DecodeArgs a) {
         }
         __syncthreads();
 
-        // ---- phase 3: one head_dim column per thread, acc += p * v
-        const int nvalid = (int)min((long long)kChunk, t1 - c0);
+        // ---- phase 3: acc += p * v
+        if (pv_thread) {
 #pragma unroll
-        for (int k = 0; k < kMaxDimsPerThread; ++k) {
-            const int d = tid + k * kThreads;
-            if (d < hd) {
+            for (int h = 0; h < GMAX; ++h) acc[h] *= alpha_s[h];
+            for (int i = part; i < nvalid; i += parts) {
+                const float vv = __half2float(vd[i * VROW + d0]);
 #pragma unroll
-                for (int h = 0; h < GMAX; ++h) acc[h][k] *= alpha_s[h];
-                if (sg.kind == PKV_SEG_FP16) {
-                    const __half* vr = reinterpret_cast<const __half*>(sg.vp) + (size_t)kvh * sg.head_stride + (size_t)c0 * hd + d;
-                    for (int i = 0; i < nvalid; ++i) {
-                        const float vv = __half2float(vr[(size_t)i * hd]);
-#pragma unroll
-                        for (int h = 0; h < GMAX; ++h) acc[h][k] = fmaf(p_s[h * kChunk + i], vv, acc[h][k]);
-                    }
-                } else {
-                    const long long nbV = ceil_div(hd, vvpb), ngV = ceil_div(hd, sg.vgs);
-                    const size_t vrow = sg.kind == PKV_SEG_KIVI ? (size_t)kvh * sg.v_head_tokens + c0 : (size_t)kvh * S + c0;
-                    const uint8_t* vp = sg.vp + vrow * nbV + d / vvpb;
-                    const __half* vs = sg.vs + vrow * ngV + d / sg.vgs;
-                    const __half* vm = sg.vm + vrow * ngV + d / sg.vgs;
-                    const unsigned pos = (unsigned)(d % vvpb);
-                    for (int i = 0; i < nvalid; ++i) {
-                        const float c = (float)extract_code_rt(vp[(size_t)i * nbV], pos, sg.vbits);
-                        const float vv = fmaf(c, __half2float(vs[(size_t)i * ngV]), __half2float(vm[(size_t)i * ngV]));
-#pragma unroll
-                        for (int h = 0; h < GMAX; ++h) acc[h][k] = fmaf(p_s[h * kChunk + i], vv, acc[h][k]);
-                    }
-                }
+                for (int h = 0; h < GMAX; ++h) acc[h] = fmaf(p_s[h * kChunk + i], vv, acc[h]);
             }
         }
-        __syncthreads();
     }
+
+    if (parts > 1) {  // sum the token groups (the staged tiles are free now)
+        __syncthreads();
+        float* red = reinterpret_cast<float*>(kd);  // [parts - 1][GMAX][hd]
+        if (pv_thread && part > 0)
+#pragma unroll
+            for (int h = 0; h < GMAX; ++h) red[((size_t)(part - 1) * GMAX + h) * hd + d0] = acc[h];
+        __syncthreads();
+        if (part == 0)
+            for (int p = 1; p < parts; ++p)
+#pragma unroll
+                for (int h = 0; h < GMAX; ++h) acc[h] += red[((size_t)(p - 1) * GMAX + h) * hd + d0];
+    }
+    __syncthreads();  // m_s / l_s of the last chunk (or their initial values, for an empty item)
 
     const size_t widx = (size_t)(a.work_offset + w);
     if (tid < nh) {
         a.pm[widx * a.Hq + h0 + tid] = m_s[tid];
         a.pl[widx * a.Hq + h0 + tid] = l_s[tid];
     }
+    if (part == 0) {
 #pragma unroll
-    for (int k = 0; k < kMaxDimsPerThread; ++k) {
-        const int d = tid + k * kThreads;
-        if (d < hd) {
-#pragma unroll
-            for (int h = 0; h < GMAX; ++h)
-                if (h < nh) a.pacc[(widx * a.Hq + h0 + h) * hd + d] = acc[h][k];
-        }
+        for (int h = 0; h < GMAX; ++h)
+            if (h < nh) a.pacc[(widx * a.Hq + h0 + h) * hd + d0] = acc[h];
     }
 }
 
@@ -226,7 +352,7 @@ int check_segments(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, int h
     if (!segs) return PKV_E_NULL;
     if (n_segs <= 0 || n_segs > PKV_MAX_SEGMENTS) return PKV_E_LIMIT;
     if (Hq <= 0 || Hkv <= 0 || hd <= 0 || Hq % Hkv) return PKV_E_SHAPE;
-    if (hd > kThreads * kMaxDimsPerThread) return PKV_E_LIMIT;
+    if (hd > kMaxHeadDim) return PKV_E_LIMIT;
     if (hd % 4) return PKV_E_LAYOUT;
     for (int i = 0; i < n_segs; ++i) {
         const pkv_segment_t& s = segs[i];
@@ -314,8 +440,8 @@ DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, i
         if (is_fast[i]) fast_cost += seg_cost(segs[i]);
         else generic_tokens += segs[i].seq_len;
     }
-    // generic kernel: about four CTAs per SM over its share of the layer
-    const long long target = std::max<long long>(1, (4LL * sm_count) / ((long long)Hkv * head_chunks));
+    // general kernel: two CTAs of 16 warps per SM over its share of the layer
+    const long long target = std::max<long long>(1, (2LL * sm_count) / ((long long)Hkv * head_chunks));
     // tensor-core kernel: one CTA per SM (it owns the SM's shared memory), one wave
     const double fast_ctas_per_head = std::max(1.0, (double)sm_count * mma::CTAS_PER_SM / Hkv);
     for (int i = 0; i < n_segs; ++i) {
@@ -409,6 +535,8 @@ int run_splitk(const void* q, const pkv_segment_t* segs, int n_segs, int num_q_h
         // force a reconfiguration between launches
         cudaFuncSetAttribute(merge_partials_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)generic_smem_bytes(kMaxHeadDim));
         carved = true;
     }
     const int G = num_q_heads / num_kv_heads;
@@ -454,7 +582,7 @@ int run_splitk(const void* q, const pkv_segment_t* segs, int n_segs, int num_q_h
         if (rc2 != PKV_OK) return rc2;
     }
     // layout-generic kernel over everything else (float16 hot tier, per-token layout, ragged shapes)
-    const size_t smem = sizeof(float) * ((size_t)GMAX * head_dim + (size_t)GMAX * kChunk + 3 * GMAX);
+    const size_t smem = generic_smem_bytes(head_dim);
     for (size_t first = 0; first < plan.generic.size(); first += kMaxInlineSegs) {
         const int cnt = (int)std::min<size_t>(kMaxInlineSegs, plan.generic.size() - first);
         DecodeArgs a;
