@@ -5,11 +5,12 @@
 
 namespace pkv {
 
-// Log-sum-exp merge of n_parts partials, one query head per CTA of 256 threads.
-// Warp w owns parts p = w (mod 8) and lane owns four consecutive dims (float4; head_dim <= 256 means
+// Log-sum-exp merge of n_parts partials, one query head per CTA.
+// Warp w owns parts p = w (mod kMergeWarps) and lane owns four consecutive dims (float4; head_dim <= 256 means
 // up to two float4 per lane), so every load of a thread is independent of the others and of the
 // weights: they are all issued before the first use, one memory round trip for the whole merge.
 constexpr int kMergeThreads = 256;
+constexpr int kMergeWarps = kMergeThreads / 32;
 constexpr int kMergeMaxInflight = 6;  // parts per thread held in registers at once
 
 // pm, pl, pacc point at the first of the n_parts partials ([Hq] and [Hq][hd] each); consecutive partials are
@@ -25,26 +26,26 @@ __device__ __forceinline__ void merge_reduce(const float* __restrict__ pm, const
                                              const float* __restrict__ pacc, int n_parts, size_t ml_stride,
                                              size_t acc_stride, int hd, int h, float& M_out, float& L_out,
                                              float& A_out) {
-    __shared__ float red_m[8];
-    __shared__ float red_l[8];
-    __shared__ __align__(16) float red_acc[8][256];
+    __shared__ float red_m[kMergeWarps];
+    __shared__ float red_l[kMergeWarps];
+    __shared__ __align__(16) float red_acc[kMergeWarps][256];
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int nvec = hd >> 2;  // float4 per row (hd % 4 == 0 is checked on the host)
     const bool v0 = lane < nvec, v1 = lane + 32 < nvec;
 
-    // Every load of a batch (acc rows, m, l of up to 8 * kMergeMaxInflight parts) is issued before anything
+    // Every load of a batch (acc rows, m, l of up to kMergeWarps * kMergeMaxInflight parts) is issued before anything
     // is reduced, so a typical merge (a few dozen parts) is one memory round trip.  Batches are combined
     // with a running maximum, like the online softmax itself.
     float run_m = -INFINITY;  // block-wide running max (identical in every thread)
     float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
     float ls = 0.f;
-    for (int base = 0; base < n_parts; base += 8 * kMergeMaxInflight) {
+    for (int base = 0; base < n_parts; base += kMergeWarps * kMergeMaxInflight) {
         float4 r0[kMergeMaxInflight], r1[kMergeMaxInflight];
         float wm[kMergeMaxInflight], wl[kMergeMaxInflight];
         float mx = -INFINITY;
 #pragma unroll
         for (int u = 0; u < kMergeMaxInflight; ++u) {
-            const int p = base + wid + 8 * u;
+            const int p = base + wid + kMergeWarps * u;
             r0[u] = r1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
             wm[u] = -INFINITY;
             wl[u] = 0.f;
@@ -63,7 +64,7 @@ __device__ __forceinline__ void merge_reduce(const float* __restrict__ pm, const
         __syncthreads();
         mx = run_m;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) mx = fmaxf(mx, red_m[w]);
+        for (int w = 0; w < kMergeWarps; ++w) mx = fmaxf(mx, red_m[w]);
         const float rescale = expf(run_m - mx);  // first batch: exp(-inf) = 0 on zero accumulators
         run_m = mx;
         ls *= rescale;
@@ -86,11 +87,11 @@ __device__ __forceinline__ void merge_reduce(const float* __restrict__ pm, const
     __syncthreads();
     float L = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) L += red_l[w];
+    for (int w = 0; w < kMergeWarps; ++w) L += red_l[w];
     float A = 0.f;
     if (tid < hd) {
 #pragma unroll
-        for (int w = 0; w < 8; ++w) A += red_acc[w][tid];
+        for (int w = 0; w < kMergeWarps; ++w) A += red_acc[w][tid];
     }
     M_out = mx;
     L_out = L;
