@@ -529,14 +529,19 @@ int run_splitk(const void* q, const pkv_segment_t* segs, int n_segs, int num_q_h
     float* pacc = static_cast<float*>(workspace);
     float* pm = pacc + W * num_q_heads * head_dim;
     float* pl = pm + W * num_q_heads;
-    static thread_local bool carved = false;
+    // function attributes are per device: set them the first time this thread launches on a device
+    static thread_local bool carved_on[64] = {};
+    int device = 0;
+    PKV_CUDA_TRY(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return PKV_E_LIMIT;
+    bool& carved = carved_on[device];
     if (!carved) {
         // keep the SM's shared-memory split where the tensor-core kernel wants it, so alternating kernels do not
         // force a reconfiguration between launches
         cudaFuncSetAttribute(merge_partials_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-        cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)generic_smem_bytes(kMaxHeadDim));
+        PKV_CUDA_TRY(cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)generic_smem_bytes(kMaxHeadDim)));
         carved = true;
     }
     const int G = num_q_heads / num_kv_heads;
