@@ -458,7 +458,7 @@ DecodePlan plan_decode(const pkv_segment_t* segs, int n_segs, int Hq, int Hkv, i
             }
             d.split_len = ceil_div(tiles, ctas);
             // a CTA range that starts on a multiple of four tiles keeps the key scale rows 16-byte aligned
-            if (s.kind != PKV_SEG_FP16 && s.num_splits <= 0 && d.split_len > 4) d.split_len = (d.split_len + 3) / 4 * 4;
+            if (s.kind == PKV_SEG_KIVI && s.num_splits <= 0 && d.split_len > 4) d.split_len = (d.split_len + 3) / 4 * 4;
             d.n_splits = (int)ceil_div(tiles, d.split_len);
             d.work_begin = plan.fast_work;
             plan.fast_work += d.n_splits;

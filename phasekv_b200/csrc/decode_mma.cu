@@ -931,16 +931,18 @@ __device__ __forceinline__ void per_token_q(const char* q_s /* [8][kQRowBytes] *
     }
 }
 
-template <int BITS>
+// NGRP = 2: the whole 64-token tile; NGRP = 1: only its 32-token half `g_off`.
+template <int BITS, int NGRP>
 __device__ __forceinline__ void per_token_scores(const char* ka, const unsigned (&qb)[8][2], const float (&qs)[2][4],
-                                                 float c24, int lane, float (&sacc)[4][4]) {
+                                                 float c24, int lane, float (&sacc)[NGRP * 2][4], int g_off) {
     using C = Cfg<BITS>;
     constexpr int kRow = C::VWPT * 4;
     const int g = lane >> 2, t = lane & 3;
     const unsigned mask = BITS == 2 ? 0x00030003u << (2 * t) : BITS == 4 ? 0x000F000Fu << (4 * (t & 1)) : 0x00FF00FFu;
     const int sh = BITS == 4 ? 8 * (t >> 1) : 0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {  // i = 2G + j: tokens 32G + 4g + 2j and the one after
+    for (int ii = 0; ii < NGRP * 2; ++ii) {  // i = 2G + j: tokens 32G + 4g + 2j and the one after
+        const int i = NGRP == 2 ? ii : 2 * g_off + ii;
         const int tok = 32 * (i >> 1) + 4 * g + 2 * (i & 1);
         const char* ra = ka + (tok + tok / 8) * kRow;  // one pad row per 8 tokens; tok is even, so tok + 1 is in the same block
         const char* rb = ra + kRow;
@@ -979,7 +981,7 @@ __device__ __forceinline__ void per_token_scores(const char* ka, const unsigned 
             out[2] = fmaf(ks_b, acc[2], fmaf(kz_b, qs[0][G], out[2]));
             out[3] = fmaf(ks_b, acc[3], fmaf(kz_b, qs[1][G], out[3]));
         }
-        sacc[i][0] = out[0], sacc[i][1] = out[1], sacc[i][2] = out[2], sacc[i][3] = out[3];
+        sacc[ii][0] = out[0], sacc[ii][1] = out[1], sacc[ii][2] = out[2], sacc[ii][3] = out[3];
     }
 }
 
@@ -1013,10 +1015,22 @@ __device__ __forceinline__ void run_cta_per_token(const CtaCtx& a, const SegDev&
     };
     WarpState st;
     init_state(st);
-    const bool mine = wid < W && tile0 + wid < tile1;
+    // Warp w takes tiles w, w + W, ...  When the last round has at most W / 2 tiles it is dealt out in 32-token halves
+    // (warp w: half w & 1 of tile w >> 1 of that round; each warp stages the tile for itself), so that the tail of a
+    // CTA's range costs half a tile time instead of a whole one.
+    const int n_tiles = (int)(tile1 - tile0);
+    const int full_rounds = n_tiles / W, rem = n_tiles - full_rounds * W;
+    const bool halves = rem > 0 && 2 * rem <= W;
+    const int my_full = wid < W ? full_rounds + ((!halves && wid < rem) ? 1 : 0) : 0;  // whole tiles of this warp
+    const bool my_half = halves && wid < 2 * rem;
+    auto tile_of = [&](int it) {  // the it-th tile this warp stages (whole tiles first, then its half tile)
+        return it < my_full ? tile0 + wid + (long long)it * W : tile0 + (long long)full_rounds * W + (wid >> 1);
+    };
+    const int my_count = my_full + (my_half ? 1 : 0);
+    const bool mine = my_count > 0;
     const bool early = !sg.fresh;
     if (!early) cudaGridDependencySynchronize();
-    if (mine) issue(tile0 + wid, 0);
+    if (mine) issue(tile_of(0), 0);
     cp_async_commit();
     if (early) cudaGridDependencySynchronize();
     // q of the GQA group (zero rows for heads >= G), and per head and channel group the sum of q
@@ -1044,16 +1058,23 @@ __device__ __forceinline__ void run_cta_per_token(const CtaCtx& a, const SegDev&
         qs[1][G] = reinterpret_cast<const float*>(smem_c + kOffQAbs)[4 * (2 * t + 1) + G] * c_qk;
     }
     const LaneSel<BITS> ls(g);
-    int it = 0;
-    for (long long tile = tile0 + wid; mine && tile < tile1; tile += W, ++it) {
-        if (tile + W < tile1) issue(tile + W, (it + 1) & 1);
+    for (int it = 0; it < my_count; ++it) {
+        const long long tile = tile_of(it);
+        if (it + 1 < my_count) issue(tile_of(it + 1), (it + 1) & 1);
         cp_async_commit();
         cp_async_wait<1>();
         __syncwarp();
         const char* stage = smem_c + ring + (it & 1) * kStage;
-        float sacc[4][4];
-        per_token_scores<BITS>(stage, qb, qs, c_qk * 16777216.f, lane, sacc);
-        softmax_pv<BITS, 2>(sacc, stage + C::VSTAGE_BYTES, st, ls, lane, valid_of(tile), 0, 0);
+        const int nv = valid_of(tile);
+        if (it < my_full) {
+            float sacc[4][4];
+            per_token_scores<BITS, 2>(stage, qb, qs, c_qk * 16777216.f, lane, sacc, 0);
+            softmax_pv<BITS, 2>(sacc, stage + C::VSTAGE_BYTES, st, ls, lane, nv, 0, 0);
+        } else if (32 * (wid & 1) < nv) {  // (a half without a single token contributes nothing)
+            float sacc[2][4];
+            per_token_scores<BITS, 1>(stage, qb, qs, c_qk * 16777216.f, lane, sacc, wid & 1);
+            softmax_pv<BITS, 1>(sacc, stage + C::VSTAGE_BYTES, st, ls, lane, nv, 0, wid & 1);
+        }
         __syncwarp();
     }
     cp_async_wait<0>();
