@@ -465,7 +465,7 @@ class BatchDecodePlan:
         sms = _device_sm_count(self.device)
         nv.check(L.pkv_decode_batch_plan(arr, off, self.batch, num_attention_heads, hkv, hd, sms, None, 0,
                                          ctypes.byref(tb), ctypes.byref(wb)))
-        self.table_host = torch.empty(tb.value, dtype=torch.uint8).pin_memory()
+        self.table_host = torch.empty(tb.value, dtype=torch.uint8, pin_memory=True)
         nv.check(L.pkv_decode_batch_plan(arr, off, self.batch, num_attention_heads, hkv, hd, sms,
                                          self.table_host.data_ptr(), tb.value, ctypes.byref(tb), ctypes.byref(wb)))
         self.workspace_bytes = int(wb.value)
@@ -526,7 +526,7 @@ def fused_phasekv_chunk_decode(q: torch.Tensor, tiers, num_attention_heads: int)
             out[i] = _launch_decode(q[i], arr, len(segs), int(need.value), hkv, True, False)[0]
     else:
         nv.check(rc)
-        table_host = torch.empty(tb.value, dtype=torch.uint8).pin_memory()
+        table_host = torch.empty(tb.value, dtype=torch.uint8, pin_memory=True)  # from torch's cached pinned blocks
         nv.check(L.pkv_decode_chunk_plan(arr, len(segs), n, num_attention_heads, hkv, hd, sms, table_host.data_ptr(),
                                          tb.value, ctypes.byref(tb), ctypes.byref(wb)))
         with torch.cuda.device(dev):
