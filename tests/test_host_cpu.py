@@ -255,3 +255,17 @@ def test_adapter_and_cooling_entry_points_check_arguments_first():
     assert cool(n_layers=0) == nv.PKV_E_LIMIT
     assert cool(bits=3) == nv.PKV_E_BITS
     assert cool(keep=17) == nv.PKV_E_SHAPE and cool(hot_len=49) == nv.PKV_E_SHAPE
+
+
+def test_hardware_spec_has_the_planner_fields(tmp_path):
+    """planner.HardwareSpec of the reference (planner.py:43-59): name, peak_flops, hbm_bandwidth, ridge_intensity."""
+    from phasekv_b200.hardware import HardwareSpec, b200
+    spec = b200()
+    assert spec.name == "B200" and spec.hbm_bandwidth > 6e12 and spec.peak_flops > 1e15
+    assert abs(spec.ridge_intensity - spec.peak_flops / spec.hbm_bandwidth) < 1e-9
+    # decode attention over 2-bit KV (37 FLOP per byte) is bandwidth-bound on this GPU, as on the reference's
+    assert 37 < spec.ridge_intensity and 37 < HardwareSpec("RTX 4080 SUPER", 50.0e12, 736.0e9).ridge_intensity
+    path = tmp_path / "peaks.json"
+    path.write_text(json.dumps({"hbm_gbs": 6555.8, "bf16_tflops": 1500.0}))
+    measured = b200(str(path))
+    assert measured.hbm_bandwidth == 6555.8e9 and measured.peak_flops == 1.5e15 and "measured" in measured.name
