@@ -1205,6 +1205,19 @@ def measure_decode(ctx, args):
         "clocks": clocks.summary(),
     }
     if rank == 0 and world == 1 and not args.no_extras:
+        # latency of ONE call issued on an idle GPU and waited for (not a replay): launch, two kernels, host wake-up
+        one = []
+        for i in range(25):
+            arr, n = native.calls[i % len(native.calls)]
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            native.nv.check(native.L.pkv_decode_attention(
+                ls.q[0].data_ptr(), arr, n, ls.shape.num_q_heads, ls.shape.num_kv_heads, ls.shape.head_dim,
+                1.0 / (ls.shape.head_dim ** 0.5), native.sms, native.ws.data_ptr(), native.ws.numel(),
+                native.out[0].data_ptr(), None, None, None, native.nv.stream_of(device)))
+            torch.cuda.synchronize()
+            one.append((time.perf_counter() - t0) * 1e6)
+        line["single_call_latency_us"] = sorted(one[5:])[len(one[5:]) // 2]
         # parity spot check of the timed configuration against the CPU oracle (layer built from CPU bits)
         oracle, s, segs, hk, hv, q = cpu_layer_inputs(args.prompt)
         from phasekv_b200.kernels.attention_triton import fused_phasekv_decode
