@@ -55,3 +55,27 @@ def test_prompt_selection_refuses_bad_arguments_before_any_launch():
         args.update(bad)
         with pytest.raises(ValueError):
             prompt_tier.select_prompt_indices(args.pop("attentions"), **args)
+
+
+def test_compressor_reads_and_validates_its_configuration():
+    """compressor.py:41-100 of the reference: defaults, the extra dictionary, and the refusals of _validate()."""
+    import types
+
+    import pytest
+
+    from phasekv_b200.compressor import PhaseKVCompressor
+    c = PhaseKVCompressor(types.SimpleNamespace(prefill_keep_ratio=None, decode_keep_ratio=None, recent_window=None,
+                                                sink_tokens=4, bits=None, extra={}))
+    assert (c.prefill_keep_ratio, c.decode_keep_ratio, c.recent_window, c.sink_tokens) == (0.5, 1.0, 32, 4)
+    assert (c.prompt_bits, c.cold_bits, c.group_size, c.lazy_g, c.obs_window, c.pool_kernel, c.pooling) == (2, 4, 32, 16, 32, 7, "maxpool")
+    assert c.requires_attention and c.physically_evicts
+    c = PhaseKVCompressor(types.SimpleNamespace(bits=4, extra={"prompt_bits": 3, "cold_bits": 8, "lazy_g": 5}))
+    assert (c.prompt_bits, c.cold_bits, c.lazy_g) == (3, 8, 5) and c.state.prompt_bits == 3 and c.state.cold_bits == 8
+    c.state.prompt_len_phys = 9
+    c.reset()
+    assert c.state.prompt_len_phys == 0 and c.describe()["phasekv"]["lazy_g"] == 5
+    for bad in (dict(bits=5), dict(extra={"cold_bits": 6}), dict(prefill_keep_ratio=0.0), dict(decode_keep_ratio=1.2),
+                dict(recent_window=0), dict(extra={"group_size": 0}), dict(extra={"lazy_g": -1}), dict(extra={"obs_window": 0}),
+                dict(extra={"use_planner": True}), dict(extra={"target_memory_ratio": 0.3})):
+        with pytest.raises(ValueError):
+            PhaseKVCompressor(types.SimpleNamespace(**bad))
