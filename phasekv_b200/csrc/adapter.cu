@@ -35,6 +35,11 @@ struct RopeArgs {
 // grid (Hq + 2 * Hkv, n_tokens): one block per (token, head vector); thread d handles dimension d and its partner.
 template <class T, class R>
 __global__ void __launch_bounds__(kRopeThreads) rope_append_kernel(const RopeArgs a) {
+    // Launched as a programmatic dependent: everything this kernel reads may come from the previous kernel of the
+    // stream, so it waits for it first; the next kernel (decode attention) may then become resident and prefetch its
+    // packed segments while this one runs (it waits for this grid before it reads q or the float16 tier).
+    cudaGridDependencySynchronize();
+    cudaTriggerProgrammaticLaunchCompletion();
     const int t = blockIdx.y, h = blockIdx.x;
     const int half = a.hd >> 1;
     const long long slot = a.slot + (a.slot_dev ? (long long)*a.slot_dev : 0);
@@ -68,14 +73,21 @@ __global__ void __launch_bounds__(kRopeThreads) rope_append_kernel(const RopeArg
 
 template <class T>
 int launch_rope(const RopeArgs& a, int rope_dtype, cudaStream_t s) {
-    const dim3 grid((unsigned)(a.Hq + 2 * a.Hkv), (unsigned)a.n_tokens);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(a.Hq + 2 * a.Hkv), (unsigned)a.n_tokens);
+    cfg.blockDim = dim3(kRopeThreads);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     switch (rope_dtype) {
-        case PKV_DTYPE_F16: rope_append_kernel<T, __half><<<grid, kRopeThreads, 0, s>>>(a); break;
-        case PKV_DTYPE_BF16: rope_append_kernel<T, __nv_bfloat16><<<grid, kRopeThreads, 0, s>>>(a); break;
-        case PKV_DTYPE_F32: rope_append_kernel<T, float><<<grid, kRopeThreads, 0, s>>>(a); break;
+        case PKV_DTYPE_F16: PKV_CUDA_TRY(cudaLaunchKernelEx(&cfg, rope_append_kernel<T, __half>, a)); break;
+        case PKV_DTYPE_BF16: PKV_CUDA_TRY(cudaLaunchKernelEx(&cfg, rope_append_kernel<T, __nv_bfloat16>, a)); break;
+        case PKV_DTYPE_F32: PKV_CUDA_TRY(cudaLaunchKernelEx(&cfg, rope_append_kernel<T, float>, a)); break;
         default: return PKV_E_LAYOUT;
     }
-    PKV_LAUNCH_CHECK();
     return PKV_OK;
 }
 
